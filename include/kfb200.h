@@ -1,0 +1,114 @@
+/* kfb200 -- C ABI of the B200 (sm_100a) kernels behind KernelForge's two inference paths.
+ *
+ * This header is the drop-in boundary.  It replaces the reference's pybind11 module
+ * `kernelforge._C` (csrc/bindings.cpp:12-28) and the torch entry points below it
+ * (csrc/attention/attn_v4.cu:10-51, csrc/gemm/dequant_gemv.cu:21-36,
+ * csrc/gemm/dequant_gemm_tc.cu:7-28) with plain-C entry points: raw device pointers,
+ * sizes and a stream, no torch types.
+ *
+ * Conventions, all functions:
+ *   - return KFB_OK (0) or a negative kfb_status; never throw, abort, exit or trap;
+ *     kfb_last_error() gives the message of the last failure on the calling thread;
+ *   - the caller owns every buffer (inputs, outputs, workspaces); unless a function says
+ *     otherwise it allocates nothing, frees nothing and never synchronises, so a call can be
+ *     captured in a CUDA graph;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default
+ *     stream) of the device that is current on the calling thread;
+ *   - data pointers must be 16-byte aligned (the reference demands the same,
+ *     csrc/attention/attn_v4.cu:26-31, csrc/gemm/dequant_gemv.cu:17-18);
+ *   - thread-safe; the only shared state is a mutex-guarded one-time set-up of kernel
+ *     attributes and a small cache of TMA tensor maps.
+ */
+#ifndef KFB200_H
+#define KFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum kfb_status {
+  KFB_OK = 0,
+  KFB_ERR_INVALID = -1,     /* bad shape / size / flag                                  */
+  KFB_ERR_ALIGNMENT = -2,   /* a pointer or stride is not 16-byte aligned               */
+  KFB_ERR_UNSUPPORTED = -3, /* legal for the reference but outside what this build runs */
+  KFB_ERR_WORKSPACE = -4,   /* workspace pointer NULL or too small                      */
+  KFB_ERR_CUDA = -5,        /* a CUDA runtime / driver call failed (see kfb_last_error) */
+  KFB_ERR_DEVICE = -6       /* the current device is not compute capability 10.x        */
+} kfb_status;
+
+typedef enum kfb_dtype { KFB_F16 = 0, KFB_BF16 = 1, KFB_F32 = 2 } kfb_dtype;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int kfb_version(void);
+/* Message of the last failed call on this thread ("" if none).  Never NULL. */
+const char* kfb_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * INT4 weight format (kernelforge/quantize.py).  packed: int32 [N, K/8], nibble position i
+ * (bits 4i..4i+3) of word j holds q[8j + (0,2,4,6,1,3,5,7)[i]] + 8; scales: fp16 [N, K/G].
+ * ------------------------------------------------------------------------------------- */
+
+/* quantize_weight (kernelforge/quantize.py:100-105 = quantize_int4 :61-71 + pack_int4 :74-85),
+ * bit-exact: scale = fp16(max(absmax/7, 2^-14)), 1 for an all-zero group;
+ * q = clamp(rint(w / scale), -8, 7) in IEEE fp32.  w: [N, K] of w_dtype, G in {64,128}. */
+int kfb_quantize_pack(const void* w, int w_dtype, int N, int K, int group,
+                      void* packed, void* scales, void* stream);
+
+/* unpack_int4 (kernelforge/quantize.py:88-97): packed -> int8 [N, K] in [-8, 7]. */
+int kfb_unpack_int4(const void* packed, int N, int K, void* q_out, void* stream);
+
+/* pack_int4 (kernelforge/quantize.py:74-85): int8 [N, K] in [-8, 7] -> packed.  Values are
+ * masked to 4 bits; range checking is the caller's job (the Python layer does it). */
+int kfb_pack_int4(const void* q, int N, int K, void* packed, void* stream);
+
+/* dequantize (kernelforge/quantize.py:108-114): out [N, K]; KFB_F32 = exact q*scale,
+ * KFB_F16 = one fp16 multiply half(q)*scale. */
+int kfb_dequantize(const void* packed, const void* scales, int N, int K, int group,
+                   void* out, int out_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * INT4 weight-only linear  y[M, N] = x[M, K] @ W_hat[N, K]^T,  x and y fp16.
+ * ------------------------------------------------------------------------------------- */
+
+/* int4_gemv (csrc/gemm/dequant_gemv.cu:21-36, kernel csrc/gemm/dequant_gemv_kernel.cuh:38-109):
+ * 1 <= M <= 8, any N >= 1, K % group == 0, group in {64,128}.  CUDA-core weight stream,
+ * FP32 accumulation, one rounding to fp16.  No workspace.
+ * flags: bit 0 = launch with programmatic dependent launch (the weight prefetch of this
+ * call may overlap the tail of the previous kernel on the stream; x is read and y written
+ * only after the previous kernel has completed). */
+int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y,
+                  int M, int N, int K, int group, int flags, void* stream);
+
+/* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
+ * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),
+ * K % group == 0.  Weights are dequantised into swizzled shared memory and multiplied on
+ * the tcgen05 tensor cores with FP32 accumulation in TMEM.  Split-K partial sums go through
+ * `ws` (FP32, fixed-order reduce => deterministic). */
+size_t kfb_int4_gemm_ws_bytes(int M, int N, int K, int group);
+int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y,
+                  int M, int N, int K, int group, void* ws, size_t ws_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused attention forward  O = softmax(scale * Q K^T + causal mask) V
+ * (kernelforge/ops.py:258-274 -> csrc/attention/attn_v4.cu:10-51, kernel attn_v4_kernel.cuh:43-214).
+ *   q, o: [B, H, Nq, D] contiguous; k, v: [B, Hk, Nk, D]; dtype KFB_F16 or KFB_BF16;
+ *   D in {64, 128}; H % Hk == 0; causal => Nq <= Nk, key j visible to query i iff
+ *   j <= i + (Nk - Nq).
+ *   kv_strides: NULL for contiguous k/v, else {batch, head, row} strides IN ELEMENTS shared by
+ *   k and v (each a multiple of 8; the D axis must be dense), so a KV-cache view
+ *   cache[:, :, :Nk] needs no copy.
+ *   Prefill (Nq > 1): TMA-staged swizzled tiles, tcgen05 MMA, accumulators in TMEM.
+ *   Decode (Nq == 1): split-KV kernel; partial (o, m, l) per split go through `ws`.
+ * ------------------------------------------------------------------------------------- */
+size_t kfb_flash_attn_ws_bytes(int B, int H, int Hk, int Nq, int Nk, int D);
+int kfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int dtype,
+                       int B, int H, int Hk, int Nq, int Nk, int D, int causal, float scale,
+                       const int64_t* kv_strides, void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KFB200_H */

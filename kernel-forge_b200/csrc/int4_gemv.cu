@@ -1,0 +1,280 @@
+// INT4 weight-only GEMV for M = 1..8 on sm_100a:  y[m, n] = sum_k x[m, k] * q[n, k] * s[n, k / G].
+//
+// Replaces dequant_gemv_kernel of the reference (csrc/gemm/dequant_gemv_kernel.cuh:38-109).
+// The kernel is HBM-bound (0.516 B per weight at G = 128) and uses no tensor cores:
+//   * a lane streams one 16-byte chunk (32 weights) of each of its R rows per step with
+//     L1-bypassing 128-bit loads; consecutive lanes read consecutive chunks, so a warp step
+//     covers 512 contiguous bytes of every row it owns;
+//   * nibbles are turned into exact fp16 integers with the magic-number trick the packed
+//     layout was designed for (kernelforge/quantize.py:18-23, csrc/gemm/int4.cuh:20-27):
+//     (w & 0x000F000F) | 0x6400 6400 = 1024 + u, (w & 0x00F000F0) | 0x64006400 = 1024 + 16u,
+//     one HSUB2 / HFMA2 each gives the pair (q[2i], q[2i+1]) -- 1 shift + 4 LOP3 + 4 half2 ops
+//     per 8 weights;
+//   * products are accumulated in FP32 with the sm_100 mixed-precision FMA
+//     (fma.rn.f32.f16: fp16 x fp16 + fp32, the product is exact), the per-group scale is
+//     applied in FP32 once per 32-weight chunk (32 divides G), then a warp-shuffle reduction
+//     and ONE rounding to fp16.  Result = FP32 dot product of the exact dequantised weights.
+// K can be split across the warps of a CTA (fixed-order shared-memory reduce: deterministic).
+#include "common.cuh"
+
+namespace kfb {
+namespace gemv {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+  uint4 v;
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint4 ldg_cached(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Programmatic dependent launch: both are no-ops when the kernel was launched normally.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// 8 packed weights -> 4 half2 (q[2i], q[2i+1]), exact integers in [-8, 7].
+__device__ __forceinline__ void unpack8(uint32_t w, uint32_t (&q)[4]) {
+  constexpr uint32_t kMagic = 0x64006400u;                     // half2(1024, 1024)
+  const __half2 k1032 = u32_as_h2(0x64086408u);                // half2(1032, 1032)
+  const __half2 kSixteenth = u32_as_h2(0x2C002C00u);           // half2(1/16, 1/16)
+  const __half2 kMinus72 = u32_as_h2(0xD480D480u);             // half2(-72, -72)
+  const uint32_t h = w >> 8;
+  q[0] = h2_as_u32(__hsub2(u32_as_h2((w & 0x000F000Fu) | kMagic), k1032));               // (1024+u) - 1032
+  q[1] = h2_as_u32(__hfma2(u32_as_h2((w & 0x00F000F0u) | kMagic), kSixteenth, kMinus72));  // (1024+16u)/16 - 72
+  q[2] = h2_as_u32(__hsub2(u32_as_h2((h & 0x000F000Fu) | kMagic), k1032));
+  q[3] = h2_as_u32(__hfma2(u32_as_h2((h & 0x00F000F0u) | kMagic), kSixteenth, kMinus72));
+}
+
+// acc += a.lo * b.lo + a.hi * b.hi with fp16 inputs and an FP32 accumulator (exact products).
+__device__ __forceinline__ float dot2_acc(uint32_t a, uint32_t b, float acc) {
+  asm("{\n\t"
+      ".reg .b16 al, ah, bl, bh;\n\t"
+      "mov.b32 {al, ah}, %1;\n\t"
+      "mov.b32 {bl, bh}, %2;\n\t"
+      "fma.rn.f32.f16 %0, al, bl, %0;\n\t"
+      "fma.rn.f32.f16 %0, ah, bh, %0;\n\t"
+      "}"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+  return acc;
+}
+
+// FP32 dot product of one unpacked 16-byte weight chunk (16 half2) with 32 activations.
+__device__ __forceinline__ float dot32(const uint32_t (&q)[16], const uint4 (&xv)[4]) {
+  float p0 = 0.f, p1 = 0.f;  // two chains for ILP
+  const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv);
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    p0 = dot2_acc(q[i], xs[i], p0);
+    p1 = dot2_acc(q[i + 1], xs[i + 1], p1);
+  }
+  return p0 + p1;
+}
+
+__device__ __forceinline__ void unpack32(const uint4& wv, uint32_t (&q)[16]) {
+  uint32_t t[4];
+  unpack8(wv.x, t); q[0] = t[0]; q[1] = t[1]; q[2] = t[2]; q[3] = t[3];
+  unpack8(wv.y, t); q[4] = t[0]; q[5] = t[1]; q[6] = t[2]; q[7] = t[3];
+  unpack8(wv.z, t); q[8] = t[0]; q[9] = t[1]; q[10] = t[2]; q[11] = t[3];
+  unpack8(wv.w, t); q[12] = t[0]; q[13] = t[1]; q[14] = t[2]; q[15] = t[3];
+}
+
+// M: activation rows; R: weight rows per warp; G: group size.
+// `ksplit_log2`: 2^ksplit_log2 warps of a CTA share one row tile and split its K chunks.
+template <int M, int R, int G>
+__global__ void __launch_bounds__(kThreads)
+int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed, const __half* __restrict__ scales,
+                 __half* __restrict__ y, int N, int K, int ksplit_log2) {
+  __shared__ float red[kWarps][M * R];
+  pdl_launch_dependents();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksplit = 1 << ksplit_log2;
+  const int tile = blockIdx.x * (kWarps >> ksplit_log2) + (warp >> ksplit_log2);
+  const int kpart = warp & (ksplit - 1);
+  const int r0 = tile * R;
+  const int KC = K >> 5;  // 16-byte chunks per packed row
+  const int SG = K / G;   // scales per row
+  constexpr int kChunksPerGroup = G / 32;
+
+  float acc[M][R];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
+
+  bool waited = false;
+  if (r0 < N) {
+    const uint4* wrow[R];
+    const __half* srow[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = min(r0 + r, N - 1);  // rows past N are computed on a clamped row and never stored
+      wrow[r] = packed + (size_t)row * KC;
+      srow[r] = scales + (size_t)row * SG;
+    }
+    for (int c = kpart * 32 + lane; c < KC; c += 32 * ksplit) {
+      uint4 wv[R];
+      float sc[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) wv[r] = ldg_stream(wrow[r] + c);
+#pragma unroll
+      for (int r = 0; r < R; ++r) sc[r] = __half2float(srow[r][c / kChunksPerGroup]);
+      if (!waited) {  // weights and scales are constants and may be fetched before the
+        pdl_wait();   // previous kernel has finished; x may be its output
+        waited = true;
+      }
+      const uint4* xc = reinterpret_cast<const uint4*>(x) + (size_t)c * 4;
+      if constexpr (M <= 2) {
+        // activations resident, rows unpacked one at a time
+        uint4 xv[M][4];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          uint32_t q[16];
+          unpack32(wv[r], q);
+#pragma unroll
+          for (int m = 0; m < M; ++m) acc[m][r] = fmaf(sc[r], dot32(q, xv[m]), acc[m][r]);
+        }
+      } else {
+        // weights resident (unpacked once), activations streamed per m
+        uint32_t q[R][16];
+#pragma unroll
+        for (int r = 0; r < R; ++r) unpack32(wv[r], q[r]);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          uint4 xv[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[m][r] = fmaf(sc[r], dot32(q[r], xv), acc[m][r]);
+        }
+      }
+    }
+  }
+  if (!waited) pdl_wait();  // y may still be read by the previous kernel
+
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float v = acc[m][r];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      acc[m][r] = v;
+    }
+
+  if (ksplit_log2 == 0) {
+    if (lane == 0 && r0 < N) {
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (r0 + r < N) y[(size_t)m * N + r0 + r] = __float2half_rn(acc[m][r]);
+    }
+    return;
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int r = 0; r < R; ++r) red[warp][m * R + r] = acc[m][r];
+  }
+  __syncthreads();
+  if (kpart == 0 && lane < M * R && r0 < N) {
+    const int m = lane / R, r = lane % R;
+    float v = 0.f;
+    for (int p = 0; p < ksplit; ++p) v += red[warp + p][lane];  // fixed order
+    if (r0 + r < N) y[(size_t)m * N + r0 + r] = __float2half_rn(v);
+  }
+}
+
+template <int M, int R, int G>
+int launch(const void* x, const void* packed, const void* scales, void* y, int N, int K, int ksplit_log2, int flags,
+           cudaStream_t stream) {
+  const int tiles = ceil_div(N, R);
+  const int grid = ceil_div(tiles, kWarps >> ksplit_log2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & 1) ? 1 : 0;
+  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_gemv_kernel<M, R, G>, (const __half*)x, (const uint4*)packed,
+                                  (const __half*)scales, (__half*)y, N, K, ksplit_log2));
+  return KFB_OK;
+}
+
+template <int M, int G>
+int pick_rows(const void* x, const void* packed, const void* scales, void* y, int N, int K, int flags,
+              cudaStream_t stream) {
+  // K split inside the CTA: aim at about two 16-byte chunks per lane, never less than one.
+  const int KC = K / 32;
+  int ksplit_log2 = 0;
+  while (ksplit_log2 < 3 && KC / (32 << ksplit_log2) >= 4) ++ksplit_log2;
+  // Rows per warp: as many as the register budget allows while the grid still fills the SMs.
+  const int sms = sm_count();
+  constexpr int kMaxR = (M <= 2) ? 4 : 2;
+  int R = kMaxR;
+  while (R > 1 && ceil_div(ceil_div(N, R), kWarps >> ksplit_log2) < 2 * sms) R >>= 1;
+  if constexpr (kMaxR == 4) {
+    if (R == 4) return launch<M, 4, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+  }
+  if (R == 2) return launch<M, 2, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+  return launch<M, 1, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+}
+
+template <int G>
+int pick_m(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int flags,
+           cudaStream_t stream) {
+  switch (M) {
+    case 1: return pick_rows<1, G>(x, packed, scales, y, N, K, flags, stream);
+    case 2: return pick_rows<2, G>(x, packed, scales, y, N, K, flags, stream);
+    case 3: return pick_rows<3, G>(x, packed, scales, y, N, K, flags, stream);
+    case 4: return pick_rows<4, G>(x, packed, scales, y, N, K, flags, stream);
+    case 5: return pick_rows<5, G>(x, packed, scales, y, N, K, flags, stream);
+    case 6: return pick_rows<6, G>(x, packed, scales, y, N, K, flags, stream);
+    case 7: return pick_rows<7, G>(x, packed, scales, y, N, K, flags, stream);
+    default: return pick_rows<8, G>(x, packed, scales, y, N, K, flags, stream);
+  }
+}
+
+}  // namespace gemv
+}  // namespace kfb
+
+using namespace kfb;
+
+extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                             int group, int flags, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (M < 1 || M > 8) return fail(KFB_ERR_INVALID, "int4_gemv handles M in [1, 8], got M=%d", M);
+  if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
+  if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
+  if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
+  if (flags & ~1) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
+  cudaStream_t s = (cudaStream_t)stream;
+  return group == 128 ? gemv::pick_m<128>(x, packed, scales, y, M, N, K, flags, s)
+                      : gemv::pick_m<64>(x, packed, scales, y, M, N, K, flags, s);
+}

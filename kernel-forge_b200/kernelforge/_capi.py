@@ -1,0 +1,100 @@
+"""ctypes binding of libkfb200.so, the C-ABI library declared in include/kfb200.h.
+
+Takes the place of the reference's pybind11 module `kernelforge._C` (csrc/bindings.cpp:12-28).
+There is no fallback: if the library has not been built, the first kernel call raises
+ImportError, exactly as the reference does for a missing `_C` (kernelforge/ops.py:23-28).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libkfb200.so")
+_lib = None
+_load_error: Exception | None = None
+
+KFB_F16, KFB_BF16, KFB_F32 = 0, 1, 2
+_DTYPE_CODE = {torch.float16: KFB_F16, torch.bfloat16: KFB_BF16, torch.float32: KFB_F32}
+
+_SIGNATURES = {
+    "kfb_version": (c_int, []),
+    "kfb_last_error": (c_char_p, []),
+    "kfb_quantize_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "kfb_unpack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "kfb_pack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "kfb_dequantize": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "kfb_int4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "kfb_int4_gemm_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "kfb_int4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                              c_void_p]),
+    "kfb_flash_attn_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "kfb_flash_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_float, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
+}
+
+
+def exported_symbols() -> tuple[str, ...]:
+    """Every function include/kfb200.h declares."""
+    return tuple(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libkfb200.so on first use.  Raises ImportError when it is not built."""
+    global _lib, _load_error
+    if _lib is None:
+        try:
+            handle = ctypes.CDLL(_LIB_PATH)
+            for name, (res, args) in _SIGNATURES.items():
+                fn = getattr(handle, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = handle
+        except (OSError, AttributeError) as exc:
+            _load_error = exc
+            raise ImportError(
+                f"libkfb200.so is not built or incomplete ({exc}). Run `python kernel-forge_b200/build.py`."
+            ) from exc
+    return _lib
+
+
+def check(rc: int) -> None:
+    """Turns a kfb_status into the exception type the reference raises for that class of error."""
+    if rc == 0:
+        return
+    msg = lib().kfb_last_error().decode("utf-8", "replace")
+    if rc in (-1, -2):  # invalid argument / alignment: std::invalid_argument -> ValueError in the reference
+        raise ValueError(msg)
+    raise RuntimeError(f"kfb200 error {rc}: {msg}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    return _DTYPE_CODE[dtype]
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class on_device:
+    """Makes `device` current for the duration of a library call (the C ABI launches on the current device)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False

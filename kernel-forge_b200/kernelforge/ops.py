@@ -1,0 +1,253 @@
+"""Python entry points of the B200 kernels: the operator surface of KernelForge's two inference paths.
+
+Public names, argument meaning, validation rules, exception types and message wording follow the
+reference's stable API (kernelforge/ops.py:171-302): `flash_attn`, `int4_linear`, `int4_matmul`,
+`int4_gemv`, `int4_gemm`, `GEMV_MAX_M`, and the two `torch.library` custom ops
+`kernelforge::flash_attn` / `kernelforge::int4_matmul` with their fake (meta) kernels, so the ops
+trace under torch.compile and capture in CUDA graphs.  Below the operator surface everything is
+new: tensors are handed as raw pointers to libkfb200.so (include/kfb200.h), hand-written sm_100a
+kernels.  Inference only: no backward pass is defined.  There is no CPU or PyTorch fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _capi
+
+ATTN_HEAD_DIMS = (64, 128)
+ATTN_V1_HEAD_DIMS = ATTN_HEAD_DIMS  # the reference's name for the same tuple (kernelforge/modules.py:87 reads it)
+TC_ATTN_DTYPES = (torch.float16, torch.bfloat16)
+INT4_GROUP_SIZES = (64, 128)
+
+
+def _resolve_scale(scale: float | None, head_dim: int) -> float:
+    if scale is None:
+        return 1.0 / math.sqrt(head_dim)
+    if scale <= 0:
+        raise ValueError(f"scale must be positive, got {scale}")
+    return float(scale)
+
+
+# ---------------------------------------------------------------------------
+# INT4 weight-only linear
+# ---------------------------------------------------------------------------
+
+def _check_int4(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int) -> None:
+    if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.float16 or x.dim() != 2:
+        raise TypeError("x must be a 2-D fp16 CUDA tensor [M, K]")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    if packed.dtype != torch.int32 or scales.dtype != torch.float16:
+        raise TypeError("packed must be int32 and scales fp16 (see kernelforge.quantize)")
+    k = x.shape[1]
+    if k % group_size != 0:
+        raise ValueError(f"K={k} is not a multiple of group_size={group_size}")
+    if packed.shape[1] * 8 != k:
+        raise ValueError(f"packed has K/8={packed.shape[1]} columns but x has K={k}")
+
+
+def _check_int4_storage(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int) -> None:
+    # what the reference re-checks in C++ (csrc/gemm/dequant_gemv.cu:5-19)
+    if group_size not in INT4_GROUP_SIZES:
+        raise ValueError(f"group_size must be one of {INT4_GROUP_SIZES}, got {group_size}")
+    if packed.device != x.device or scales.device != x.device:
+        raise ValueError("x, packed and scales must be on the same CUDA device")
+    if packed.dim() != 2 or not packed.is_contiguous() or not scales.is_contiguous():
+        raise ValueError("packed must be a contiguous [N, K/8] tensor and scales contiguous")
+    if tuple(scales.shape) != (packed.shape[0], x.shape[1] // group_size):
+        raise ValueError(f"scales must be [N, K/group_size] = {(packed.shape[0], x.shape[1] // group_size)}, "
+                         f"got {tuple(scales.shape)}")
+
+
+def _gemv_launch(x, packed, scales, group_size: int, flags: int = 0) -> torch.Tensor:
+    m, k = x.shape
+    n = packed.shape[0]
+    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    if n == 0:
+        return y
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(),
+                                              m, n, k, group_size, flags, _capi.stream_ptr(x.device)))
+    return y
+
+
+def _gemm_launch(x, packed, scales, group_size: int) -> torch.Tensor:
+    m, k = x.shape
+    n = packed.shape[0]
+    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    if n == 0 or m == 0:
+        return y
+    lib = _capi.lib()
+    ws_bytes = lib.kfb_int4_gemm_ws_bytes(m, n, k, group_size)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(lib.kfb_int4_gemm(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(), m, n, k,
+                                      group_size, ws.data_ptr(), ws_bytes, _capi.stream_ptr(x.device)))
+    return y
+
+
+def int4_gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """Fused INT4 dequant GEMV for M in [1, 8]: x [M, K] fp16 @ W_hat^T -> [M, N] fp16."""
+    _check_int4(x, packed, scales, group_size)
+    if not 1 <= x.shape[0] <= 8:
+        raise ValueError(f"int4_gemv handles M in [1, 8], got M={x.shape[0]}")
+    _check_int4_storage(x, packed, scales, group_size)
+    return _gemv_launch(x, packed, scales, int(group_size))
+
+
+# Largest M served by the GEMV; from M = GEMV_MAX_M + 1 on the tensor-core GEMM is used.  The
+# reference measured 7 on its GPU (kernelforge/ops.py:193, bench/sweep_int4_dispatch.py:47-57).
+GEMV_MAX_M = 8
+
+
+def int4_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """Fused INT4 dequant GEMM on the tcgen05 tensor cores, any M, N a multiple of 64."""
+    _check_int4(x, packed, scales, group_size)
+    if packed.shape[0] % 64 != 0:
+        raise ValueError(f"int4_gemm needs N to be a multiple of 64, got N={packed.shape[0]}")
+    _check_int4_storage(x, packed, scales, group_size)
+    return _gemm_launch(x, packed, scales, int(group_size))
+
+
+def int4_gemm_ragged(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """The same GEMM without the N % 64 rule of the reference wrapper: output-feature shards
+    (N/8 = 32, 192, 1120 rows) are not multiples of 64 and the kernel handles them."""
+    _check_int4(x, packed, scales, group_size)
+    _check_int4_storage(x, packed, scales, group_size)
+    return _gemm_launch(x, packed, scales, int(group_size))
+
+
+def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """y = x @ W_hat^T for INT4 weights from kernelforge.quantize, choosing the kernel by M.
+
+    M <= GEMV_MAX_M: the bandwidth-bound GEMV (CUDA cores, FP32 accumulation).
+    Larger M: the tensor-core GEMM.
+    """
+    if x.shape[0] <= GEMV_MAX_M:
+        return int4_gemv(x, packed, scales, group_size)
+    return int4_gemm(x, packed, scales, group_size)
+
+
+# ---------------------------------------------------------------------------
+# Attention
+# ---------------------------------------------------------------------------
+
+def _check_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, strided_kv: bool = False) -> None:
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor")
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be 4-D [B, heads, N, D], got shape {tuple(t.shape)}")
+        if t.dtype not in TC_ATTN_DTYPES:
+            raise TypeError(f"{name} must be fp16 or bf16, got {t.dtype}")
+        if not t.is_contiguous() and not (strided_kv and name != "q"):
+            raise ValueError(f"{name} must be contiguous (call .contiguous() first)")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError(f"q, k, v must share a dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+    if k.shape != v.shape:
+        raise ValueError(f"k and v must have the same shape, got {tuple(k.shape)} and {tuple(v.shape)}")
+    (b, h, nq, d), (bk, hk, nk, dk) = q.shape, k.shape
+    if b != bk or d != dk:
+        raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} must match in batch and head dim")
+    if d not in ATTN_HEAD_DIMS:
+        raise ValueError(f"head dim must be one of {ATTN_HEAD_DIMS}, got {d}")
+    if h % hk != 0:
+        raise ValueError(f"query heads ({h}) must be a multiple of key/value heads ({hk})")
+    if causal and nq > nk:
+        raise ValueError(f"causal attention needs Nq <= Nk (queries are the last Nq positions), got {nq} > {nk}")
+
+
+def _attn_launch(q, k, v, causal: bool, scale: float, kv_strides=None) -> torch.Tensor:
+    b, h, nq, d = q.shape
+    hk, nk = k.shape[1], k.shape[2]
+    o = torch.empty_like(q)
+    if q.numel() == 0:
+        return o
+    if nk == 0:
+        raise ValueError("attention needs at least one key (Nk >= 1)")
+    lib = _capi.lib()
+    ws_bytes = lib.kfb_flash_attn_ws_bytes(b, h, hk, nq, nk, d)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
+    strides = None
+    if kv_strides is not None:
+        strides = (ctypes.c_int64 * 3)(*kv_strides)
+    with _capi.on_device(q.device):
+        _capi.check(lib.kfb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                           _capi.dtype_code(q.dtype), b, h, hk, nq, nk, d, int(causal), scale, strides,
+                                           ws.data_ptr() if ws is not None else None, ws_bytes,
+                                           _capi.stream_ptr(q.device)))
+    return o
+
+
+@torch.library.custom_op("kernelforge::flash_attn", mutates_args=())
+def _flash_attn_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, scale: float) -> torch.Tensor:
+    return _attn_launch(q, k, v, causal, scale)
+
+
+@_flash_attn_op.register_fake
+def _(q, k, v, causal, scale):
+    return torch.empty_like(q)
+
+
+def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+               scale: float | None = None) -> torch.Tensor:
+    """Fused attention forward, the stable entry point.
+
+    q: [B, H, Nq, D], k and v: [B, Hk, Nk, D], fp16 or bf16, contiguous, D in {64, 128}.
+    H must be a multiple of Hk (grouped-query attention, no K/V copies). Nq may be smaller
+    than Nk (decode or chunked prefill against a KV cache): with causal=True, query i is
+    treated as position Nk - Nq + i and sees keys 0 .. Nk - Nq + i.
+    Returns [B, H, Nq, D] in the input dtype. Inference only (no backward).
+    """
+    _check_attn(q, k, v, causal)
+    return _flash_attn_op(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
+
+
+def flash_attn_kv_view(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+                       scale: float | None = None) -> torch.Tensor:
+    """flash_attn for K/V that are strided views of a cache, e.g. `cache[:, :, :L]` of a
+    [B, Hk, Lmax, D] buffer: the kernel reads the view in place (the reference copies it with
+    .contiguous(), kernelforge/modules.py:95).  Views whose D axis is not dense, whose strides
+    differ between k and v, or are not multiples of 8 elements, are copied first."""
+    _check_attn(q, k, v, causal, strided_kv=True)
+    if k.is_contiguous() and v.is_contiguous():
+        return _flash_attn_op(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
+    if k.stride() != v.stride() or k.stride(3) != 1 or any(s % 8 for s in k.stride()[:3]):
+        return _flash_attn_op(q, k.contiguous(), v.contiguous(), bool(causal), _resolve_scale(scale, q.shape[-1]))
+    return _attn_launch(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]), kv_strides=k.stride()[:3])
+
+
+# ---------------------------------------------------------------------------
+# int4_linear: the nn.Linear-shaped entry point
+# ---------------------------------------------------------------------------
+
+@torch.library.custom_op("kernelforge::int4_matmul", mutates_args=())
+def _int4_matmul_op(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int) -> torch.Tensor:
+    return int4_matmul(x, packed, scales, group_size)
+
+
+@_int4_matmul_op.register_fake
+def _(x, packed, scales, group_size):
+    return x.new_empty(x.shape[0], packed.shape[0])
+
+
+def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
+                bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ W_hat^T (+ bias) for INT4 weights from kernelforge.quantize. x: [..., K] fp16.
+
+    Leading dimensions are flattened into M, so [B, T, K] works like nn.Linear. The kernel is
+    chosen by M (int4_matmul). Inference only (no backward).
+    """
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    _check_int4(x2, packed, scales, group_size)
+    y = _int4_matmul_op(x2, packed, scales, int(group_size))
+    if bias is not None:
+        y = y + bias
+    return y.reshape(*lead, packed.shape[0])

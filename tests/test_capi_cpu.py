@@ -1,0 +1,105 @@
+"""CPU-side checks of the boundary: the C-ABI library loads and exports everything the header declares,
+and the package's host logic (CPU-tensor quantiser, validators, custom-op registration) behaves like the
+reference's (kernelforge/quantize.py, kernelforge/ops.py:171-302).  No kernel is launched here."""
+
+import ctypes
+import re
+import glob
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, GOLDEN
+from kernelforge import _capi, ops
+from kernelforge import quantize as kq
+
+
+def _declared_functions():
+    text = (ROOT / "include" / "kfb200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(kfb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_functions()
+    assert len(names) >= 10
+    handle = ctypes.CDLL(str(ROOT / "kernel-forge_b200" / "kernelforge" / "libkfb200.so"))
+    for name in names:
+        assert hasattr(handle, name), f"{name} is declared in include/kfb200.h but not exported"
+    assert sorted(_capi.exported_symbols()) == names  # the ctypes table binds exactly the header
+    assert _capi.lib().kfb_version() >= 100
+    assert _capi.lib().kfb_last_error() is not None
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(str(GOLDEN / "quant_*.npz"))), ids=lambda p: p.split("/")[-1])
+def test_cpu_tensor_quantizer_matches_reference_bits(path):
+    z = np.load(path)
+    group = int(z["group"])
+    w = torch.from_numpy(z["w"])
+    if "_f16" in path:
+        w = w.half()
+    elif "_bf16" in path:
+        w = w.bfloat16()
+    qw = kq.quantize_weight(w, group)
+    assert np.array_equal(qw.packed.numpy(), z["packed"])
+    assert np.array_equal(qw.scales.numpy().view(np.uint16), z["scales"].view(np.uint16))
+    assert np.array_equal(kq.unpack_int4(qw.packed).numpy(), z["q"])
+    assert np.array_equal(kq.dequantize(qw, torch.float32).numpy(), z["deq32"])
+    assert np.array_equal(kq.dequantize(qw, torch.float16).numpy().view(np.uint16), z["deq16"].view(np.uint16))
+    assert qw.nbytes == z["packed"].size * 4 + z["scales"].size * 2 and qw.shape == tuple(z["w"].shape)
+
+
+def test_bit_layout_known_answer():
+    q = torch.arange(0, 8, dtype=torch.int8).reshape(1, 8)
+    word = kq.pack_int4(q).item() & 0xFFFFFFFF
+    assert [(word >> (4 * i)) & 0xF for i in range(8)] == [8, 10, 12, 14, 9, 11, 13, 15]
+
+
+def test_quantization_error_stats():
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(256, 1024, generator=g) * 0.02
+    for group in (64, 128):
+        qw = kq.quantize_weight(w, group)
+        step = qw.scales.float().repeat_interleave(group, dim=1)
+        assert ((kq.dequantize(qw, torch.float32) - w).abs() <= 0.5 * step + 1e-8).all()
+        stats = kq.quantization_error(w, qw)
+        assert stats["rel_fro_err"] < 0.15 and stats["bits_per_weight"] == pytest.approx(4 + 16 / group)
+
+
+def test_quantizer_rejections():
+    with pytest.raises(ValueError, match="not a multiple of group_size"):
+        kq.quantize_weight(torch.randn(16, 200), 128)
+    with pytest.raises(ValueError, match="group_size"):
+        kq.quantize_weight(torch.randn(16, 256), 32)
+    with pytest.raises(ValueError, match="2-D"):
+        kq.quantize_weight(torch.randn(4, 16, 256), 128)
+    with pytest.raises(ValueError, match=r"\[-8, 7\]"):
+        kq.pack_int4(torch.full((1, 8), 9, dtype=torch.int8))
+    with pytest.raises(ValueError, match="multiple of 8"):
+        kq.pack_int4(torch.zeros(2, 12, dtype=torch.int8))
+
+
+def test_validators_reject_cpu_tensors_like_the_reference():
+    q = torch.randn(1, 2, 8, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.flash_attn(q, q, q)
+    with pytest.raises(TypeError, match="2-D fp16 CUDA tensor"):
+        ops.int4_linear(torch.randn(2, 256).half(), torch.zeros(8, 32, dtype=torch.int32),
+                        torch.ones(8, 2, dtype=torch.float16))
+    with pytest.raises(ValueError, match="positive"):
+        ops._resolve_scale(-1.0, 64)
+    assert ops._resolve_scale(None, 64) == pytest.approx(0.125)
+
+
+def test_custom_ops_registered_with_fakes():
+    assert hasattr(torch.ops.kernelforge, "flash_attn") and hasattr(torch.ops.kernelforge, "int4_matmul")
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        q = torch.empty(2, 8, 16, 64, dtype=torch.float16, device="cuda")
+        k = torch.empty(2, 2, 48, 64, dtype=torch.float16, device="cuda")
+        assert torch.ops.kernelforge.flash_attn(q, k, k, True, 0.125).shape == q.shape
+        x = torch.empty(3, 256, dtype=torch.float16, device="cuda")
+        p = torch.empty(40, 32, dtype=torch.int32, device="cuda")
+        s = torch.empty(40, 2, dtype=torch.float16, device="cuda")
+        assert torch.ops.kernelforge.int4_matmul(x, p, s, 128).shape == (3, 40)

@@ -1,0 +1,92 @@
+"""INT4 GEMV (M = 1..8) against the FP32 oracle `x.float() @ dequantize(qw, fp32).T`
+(reference grid: tests/test_gemm.py:48-79; golden vectors made by the reference itself)."""
+
+import glob
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from helpers import LAYER_SHAPES, assert_int4_close, int4_case
+from kernelforge import ops
+from kernelforge import quantize as kq
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(fn, m, n, k, group, what):
+    _, x, packed, scales, ref = int4_case(m, n, k, group, seed=m * 7 + n + k)
+    out = fn(torch.from_numpy(x).cuda(), torch.from_numpy(packed).cuda(), torch.from_numpy(scales).cuda(), group)
+    assert out.shape == (m, n) and out.dtype == torch.float16
+    return assert_int4_close(out, ref, what)
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("layer", list(LAYER_SHAPES))
+def test_gemv_layer_shapes(layer, m, group):
+    n, k = LAYER_SHAPES[layer]
+    run_case(ops.int4_gemv, m, n, k, group, f"{layer} m{m} g{group}")
+
+
+@pytest.mark.parametrize("n", [1, 7, 9, 129])
+def test_gemv_ragged_n(n):
+    run_case(ops.int4_gemv, 3, n, 256, 128, f"ragged_n{n}")
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(str(GOLDEN / "int4_linear_m[1-8]_*.npz"))), ids=lambda p: p.split("/")[-1])
+def test_gemv_golden(path):
+    z = np.load(path)
+    out = ops.int4_gemv(torch.from_numpy(z["x"]).cuda(), torch.from_numpy(z["packed"]).cuda(),
+                        torch.from_numpy(z["scales"]).cuda(), int(z["group"]))
+    assert_int4_close(out, z["ref"], path)
+
+
+def test_gemv_guard_band_and_determinism():
+    """Rows past N must not be written and two runs must agree bit for bit."""
+    _, x, packed, scales, ref = int4_case(3, 129, 256, 128, seed=5)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    a = ops.int4_gemv(xs, ps, ss, 128)
+    b = ops.int4_gemv(xs, ps, ss, 128)
+    assert torch.equal(a, b)
+    _, x, packed, scales, ref = int4_case(1, 5632, 2048, 128, seed=11)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    assert torch.equal(ops.int4_gemv(xs, ps, ss, 128), ops.int4_gemv(xs, ps, ss, 128))
+
+
+def test_gemv_linearity_full_size():
+    """Size-independent property at the benchmark shape: y(x1 + x2) = y(x1) + y(x2) up to fp16 rounding."""
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(5632, 2048, generator=g) * 0.02
+    qw = kq.quantize_weight(w.cuda(), 128)
+    x1 = (torch.randn(1, 2048, generator=g) * 0.5).half().cuda()
+    x2 = (torch.randn(1, 2048, generator=g) * 0.5).half().cuda()
+    y12 = ops.int4_gemv(x1 + x2, qw.packed, qw.scales, 128).float()
+    ysum = ops.int4_gemv(x1, qw.packed, qw.scales, 128).float() + ops.int4_gemv(x2, qw.packed, qw.scales, 128).float()
+    # x1 + x2 is rounded to fp16 once (rel 2^-11 per element), outputs are rounded to fp16
+    assert (y12 - ysum).abs().max().item() <= 4e-3 * ysum.abs().max().item()
+
+
+def test_gemv_rejections():
+    x = torch.randn(1, 200).half().cuda()
+    with pytest.raises(ValueError, match="not a multiple of group_size"):
+        ops.int4_gemv(x, torch.zeros(16, 25, dtype=torch.int32).cuda(), torch.ones(16, 2, dtype=torch.float16).cuda(), 128)
+    _, x, packed, scales, _ = int4_case(9, 64, 256, 128, seed=0)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    with pytest.raises(ValueError, match=r"M in \[1, 8\]"):
+        ops.int4_gemv(xs, ps, ss, 128)
+    with pytest.raises(ValueError, match="K/8"):
+        ops.int4_gemv(xs[:1, :128].contiguous(), ps, ss, 128)
+    with pytest.raises(TypeError, match="2-D fp16 CUDA tensor"):
+        ops.int4_gemv(xs[:1].float(), ps, ss, 128)
+
+
+def test_int4_linear_shapes_and_bias():
+    _, x, packed, scales, ref = int4_case(6, 72, 512, 64, seed=2)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    bias = torch.linspace(-1, 1, 72).half().cuda()
+    y = ops.int4_linear(xs.reshape(2, 3, 512), ps, ss, 64, bias)
+    assert y.shape == (2, 3, 72) and y.dtype == torch.float16
+    want = torch.from_numpy(ref).cuda().half() + bias
+    assert (y.reshape(6, 72).float() - want.float()).abs().max().item() <= 4e-3 * float(np.abs(ref).max() + 1)
