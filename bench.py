@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 KernelForge hot paths.  Prints ONE JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Headline workload (`flash_attn`): fused attention forward, MHA fp16, B=2 H=16 N=2048 D=64, non-causal,
+softmax scale 1/8 -- the configuration the reference quotes its attention TFLOPS on.  A step is one call
+of the hot path on one batch.  `value` is whole-job TFLOP/s with inputs resident in HBM (CUDA events on
+the launching stream, max over ranks); `e2e` is the same metric through `kernelforge.ops.flash_attn`
+with host buffers (pinned host -> device copies of q, k, v and the device -> host copy of o inside the
+timed region).  Other workloads of the metric are reported under `also` (INT4 GEMV at M=1 in GB/s,
+causal prefill, GQA decode attention) and can be made the headline with --workload.
+
+FLOP and byte counts are the reference's formulas: 4*B*H*Nq*Nk*D (halved when causal),
+kernelforge/bench_utils.py:193-196; packed + scales + x + y bytes, bench/bench_gemm.py:80,98.
+
+With N > 1 (torchrun, one rank per GPU) every rank runs the same per-GPU workload on its own batch
+(attention shards over batch x heads with no communication): weak scaling, no collective in the data path.
+
+`--impl reference` times the reference's FP32 CPU path (the numpy restatement in oracle/, all host
+threads) on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "kernel-forge_b200"))
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+# ----------------------------------------------------------------------------------------------
+# helpers
+# ----------------------------------------------------------------------------------------------
+
+def measured_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier_sync(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step_fn, steps: int, warmup: int, world: int) -> float:
+    """W untimed steps, then exactly K steps between two events on the current stream; ms, max over ranks."""
+    for i in range(warmup):
+        step_fn(i)
+    barrier_sync(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step_fn(warmup + i)
+    end.record()
+    barrier_sync(world)
+    return max_over_ranks(start.elapsed_time(end), world)
+
+
+# ----------------------------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------------------------
+
+def attn_sets(b, h, hk, nq, nk, d, n_sets, device, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    sets = []
+    for _ in range(n_sets):
+        q = torch.randn(b, h, nq, d, generator=g).half()
+        k = torch.randn(b, hk, nk, d, generator=g).half()
+        v = torch.randn(b, hk, nk, d, generator=g).half()
+        sets.append((q.to(device), k.to(device), v.to(device)))
+    return sets
+
+
+def bench_flash_attn(args, world, device, causal: bool, cfg=(2, 16, 16, 2048, 2048, 64)) -> dict:
+    from kernelforge import ops
+    b, h, hk, nq, nk, d = cfg
+    flops = 4.0 * b * h * nq * nk * d / (2 if causal else 1)
+    per_set = (2 * b * h * nq * d + 2 * b * hk * nk * d) * 2
+    n_sets = max(2, math.ceil(2 * L2_BYTES / per_set))  # rotating inputs: footprint > 2x L2, every step is L2-cold
+    sets = attn_sets(b, h, hk, nq, nk, d, n_sets, device)
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        ops.flash_attn(q, k, v, causal=causal)
+
+    with ClockSampler(device.index) as clocks:
+        ms = time_steps(step, args.steps, args.warmup, world)
+    tflops = world * flops * args.steps / (ms * 1e-3) / 1e12
+
+    # end to end through the public op with host buffers
+    hq, hk_, hv = (t.cpu().pin_memory() for t in sets[0])
+    ho = torch.empty_like(hq).pin_memory()
+    dq, dk, dv = (torch.empty_like(t) for t in sets[0])
+
+    def e2e_step(i):
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk_, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        ho.copy_(ops.flash_attn(dq, dk, dv, causal=causal), non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e = time_steps(e2e_step, e2e_steps, 3, world)
+    return {
+        "tflops": tflops, "ms_per_step": ms / args.steps, "flops_per_step": flops, "launches_per_step": 1,
+        "clocks": clocks.summary(), "n_sets": n_sets,
+        "e2e": {"value": world * flops * e2e_steps / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": hq.numel() * 2 + hk_.numel() * 2 + hv.numel() * 2,
+                "d2h_bytes_per_step": ho.numel() * 2},
+    }
+
+
+def bench_decode_attn(args, world, device, batch=8, nk=4096) -> dict:
+    from kernelforge import ops
+    h, hk, d = 32, 4, 64
+    nbytes = 2 * batch * hk * nk * d * 2 + 2 * batch * h * d * 2
+    n_sets = max(2, math.ceil(2 * L2_BYTES / nbytes))
+    sets = attn_sets(batch, h, hk, 1, nk, d, n_sets, device, seed=1)
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        ops.flash_attn(q, k, v, causal=True)
+
+    ms = time_steps(step, args.steps, args.warmup, world)
+    return {"gbs": world * nbytes * args.steps / (ms * 1e-3) / 1e9, "us_per_step": 1e3 * ms / args.steps,
+            "bytes_per_step": nbytes, "batch": batch, "nk": nk, "n_sets": n_sets}
+
+
+def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict:
+    """INT4 linear at M=1.  Three figures on the same algorithmic bytes: a CUDA graph of back-to-back calls
+    over distinct weight copies (what a decode step sees; every call reads L2-cold weights), the same with
+    programmatic dependent launch, and single event-timed calls (latency)."""
+    from kernelforge import _capi, ops
+    from kernelforge import quantize as kq
+    nbytes = n * k // 2 + 2 * n * (k // group) + 2 * m * k + 2 * m * n
+    copies = max(4, math.ceil(3 * L2_BYTES / nbytes))
+    g = torch.Generator().manual_seed(0)
+    qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), group)
+    packed = [qw.packed.clone() for _ in range(copies)]
+    scales = [qw.scales.clone() for _ in range(copies)]
+    x = torch.randn(m, k, generator=g).half().to(device)
+    ys = [torch.empty(m, n, dtype=torch.float16, device=device) for _ in range(copies)]
+    lib = _capi.lib()
+
+    def launch_all(flags, stream):
+        for i in range(copies):
+            _capi.check(lib.kfb_int4_gemv(x.data_ptr(), packed[i].data_ptr(), scales[i].data_ptr(), ys[i].data_ptr(),
+                                          m, n, k, group, flags, stream))
+
+    out = {"bytes_per_call": nbytes, "copies": copies}
+    side = torch.cuda.Stream(device)
+    for name, flags in (("graph", 0), ("graph_pdl", 1)):
+        try:
+            with torch.cuda.stream(side):
+                launch_all(flags, side.cuda_stream)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    launch_all(flags, side.cuda_stream)
+            ms = time_steps(lambda i: graph.replay(), args.steps, args.warmup, world)
+            out[name] = {"gbs": world * nbytes * copies * args.steps / (ms * 1e-3) / 1e9,
+                         "us_per_call": 1e3 * ms / (args.steps * copies)}
+        except Exception as exc:  # report, never hide
+            out[name] = {"error": repr(exc)[:200]}
+    # single calls, L2-cold weights (rotating copies), one event pair each
+    times = []
+    for i in range(args.warmup + 50):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        ops.int4_linear(x, packed[i % copies], scales[i % copies], group)
+        b.record()
+        b.synchronize()
+        if i >= args.warmup:
+            times.append(a.elapsed_time(b))
+    med = statistics.median(times)
+    out["single_call"] = {"gbs": nbytes / (med * 1e-3) / 1e9, "us_per_call": med * 1e3}
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU baseline (the oracle = restatement of the reference's FP32 CPU path)
+# ----------------------------------------------------------------------------------------------
+
+def cpu_attention_sample(budget_s: float, causal: bool, cfg=(2, 16, 16, 2048, 2048, 64)) -> dict:
+    from oracle import kf_oracle as ko
+    b, h, hk, nq, nk, d = cfg
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, 1, nq, d), dtype=np.float32).astype(np.float16)
+    k = rng.standard_normal((1, 1, nk, d), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((1, 1, nk, d), dtype=np.float32).astype(np.float16)
+    ko.attention(q, k, v, causal)  # warm-up
+    heads, t0 = 0, time.perf_counter()
+    while True:
+        ko.attention(q, k, v, causal)
+        heads += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or heads >= b * h:
+            break
+    flops_head = 4.0 * nq * nk * d / (2 if causal else 1)
+    return {"value": heads * flops_head / el / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{heads} of {b * h} (batch, head) slices of the workload in {el:.1f} s, numpy/BLAS threads"}
+
+
+# ----------------------------------------------------------------------------------------------
+# main
+# ----------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only"])
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    config = {"workload": "flash_attn fwd MHA fp16 B=2 H=16 N=2048 D=64 non-causal, scale 1/sqrt(64)",
+              "l2": "inputs rotate over distinct sets totalling > 2x the 126 MB L2",
+              "per_gpu": "same batch shape on every GPU (batch x heads shard, no communication)"}
+    base = {"metric": "flash_attn TFLOPS (% peak)", "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": config}
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        per_step = max(1.0, min(args.cpu_seconds, 120.0 / max(1, args.steps + args.warmup)))
+        vals = [cpu_attention_sample(per_step, False) for _ in range(args.warmup + args.steps)][args.warmup:]
+        v = statistics.mean(x["value"] for x in vals)
+        cb = dict(vals[-1], value=v)
+        line = dict(base, impl="reference", value=v, ms_per_step=None, cpu_baseline=cb, gpu_launches=0,
+                    e2e={"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        print(json.dumps(line))
+        return
+
+    world, rank, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+
+    fa = bench_flash_attn(args, world, device, causal=False)
+    also = {}
+    if args.workload == "flash_attn":
+        fc = bench_flash_attn(args, world, device, causal=True)
+        also["flash_attn_causal"] = {"tflops": fc["tflops"], "ms_per_step": fc["ms_per_step"],
+                                     "frac_of_peak": fc["tflops"] / world / peaks["bf16_tflops"]}
+        gv = bench_int4_gemv(args, world, device)
+        best = max((gv[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gv.get(k, {})), default=None)
+        also["int4_gemv_m1_5632x2048"] = dict(gv, roofline={
+            "bound": "hbm", "achieved": None if best is None else best / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": None if best is None else best / world / peaks["hbm_gbs"], "traffic": None,
+            "note": "achieved = sustained back-to-back calls on L2-cold weight copies; single_call is latency"})
+        for batch, nk in ((1, 4096), (8, 4096), (64, 4096), (8, 16384)):
+            dd = bench_decode_attn(args, world, device, batch, nk)
+            dd["frac_of_hbm"] = dd["gbs"] / world / peaks["hbm_gbs"]
+            also[f"decode_attn_b{batch}_nk{nk}"] = dd
+
+    line = dict(base)
+    line.update({
+        "value": fa["tflops"], "ms_per_step": fa["ms_per_step"], "e2e": fa["e2e"], "gpu_launches": args.steps,
+        "clocks": fa["clocks"],
+        "roofline": {"bound": "tensor", "achieved": fa["tflops"] / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": fa["tflops"] / world / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": f"{peak_kind} dense bf16 cuBLAS burst", "kernel": "attn_prefill_kernel<64,fp16>"},
+        "also": also,
+    })
+    if rank == 0:
+        line["cpu_baseline"] = cpu_attention_sample(args.cpu_seconds, False) if world == 1 else None
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

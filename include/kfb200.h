@@ -45,6 +45,11 @@ typedef enum kfb_dtype { KFB_F16 = 0, KFB_BF16 = 1, KFB_F32 = 2 } kfb_dtype;
 int kfb_version(void);
 /* Message of the last failed call on this thread ("" if none).  Never NULL. */
 const char* kfb_last_error(void);
+/* Reads the device status word of the current device into *out (synchronous 4-byte copy).
+ * Kernels never trap: every wait on an mbarrier is bounded, and a wait that expires records
+ * a non-zero code here and lets the kernel finish.  0 = no wait has ever expired.  (The
+ * reference has no counterpart; its errors surface as CUDA errors, csrc/common/check.cuh:11-24.) */
+int kfb_device_status(unsigned int* out);
 
 /* ---------------------------------------------------------------------------------------
  * INT4 weight format (kernelforge/quantize.py).  packed: int32 [N, K/8], nibble position i

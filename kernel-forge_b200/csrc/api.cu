@@ -49,6 +49,68 @@ int require_sm100() {
 
 }  // namespace kfb
 
+namespace kfb {
+
+__device__ unsigned int g_status_word = 0;
+
+namespace {
+unsigned int* g_status_ptr[64];
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+}  // namespace
+
+unsigned int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = static_cast<unsigned int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
+                       const uint64_t strides_bytes[3], const uint32_t box[4]) {
+  {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+        return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  }
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t bdim[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == KFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(out, dt, 4, const_cast<void*>(base), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu,%llu,%llu,%llu)", (int)r,
+                (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                (unsigned long long)dims[3]);
+  return KFB_OK;
+}
+
+}  // namespace kfb
+
+extern "C" int kfb_device_status(unsigned int* out) {
+  if (!out) return kfb::fail(KFB_ERR_INVALID, "null pointer");
+  unsigned int* p = kfb::device_status_word();
+  if (!p) return kfb::fail(KFB_ERR_CUDA, "cannot resolve the device status word");
+  KFB_CUDA_TRY(cudaMemcpy(out, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+  return KFB_OK;
+}
+
 extern "C" int kfb_version(void) { return 100; }
 
 extern "C" const char* kfb_last_error(void) { return kfb::error_buffer(); }

@@ -1,0 +1,29 @@
+// Internal interface between the attention C-ABI entry point (flash_attn.cu) and the two kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace kfb {
+namespace attn {
+
+struct Problem {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  int dtype;  // KFB_F16 / KFB_BF16
+  int B, H, Hk, Nq, Nk, D;
+  int causal;
+  float scale;
+  long long kv_stride_b, kv_stride_h, kv_stride_n;  // elements
+};
+
+// Prefill / general path: one CTA per 128 query rows, TMA + tcgen05 + TMEM (attn_prefill.cu).
+int launch_prefill(const Problem& p, cudaStream_t stream);
+
+// Decode path (Nq == 1): split-KV, one CTA per (batch, kv head, split) (attn_decode.cu).
+size_t decode_ws_bytes(int B, int H, int Hk, int Nk, int D);
+int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream);
+
+}  // namespace attn
+}  // namespace kfb

@@ -51,3 +51,15 @@ int require_sm100();
   } while (0)
 
 }  // namespace kfb
+
+// ---- per-device status word and TMA tensor maps (api.cu) ------------------------------------
+#include <cuda.h>
+namespace kfb {
+// Device address of the status word kernels write when a bounded wait expires (0 = fine).
+// The first call on a device resolves the symbol address; returns nullptr on failure.
+unsigned int* device_status_word();
+// Tiled 4-D tensor map with 128-byte swizzle over a 16-bit element tensor.
+// dims[0] is the innermost (dense) extent; strides_bytes[i] is the stride of dims[i+1].
+int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
+                       const uint64_t strides_bytes[3], const uint32_t box[4]);
+}  // namespace kfb

@@ -1,8 +1,51 @@
-// placeholder until the attention kernels land
-#include "common.cuh"
+// C-ABI entry point of the fused attention forward: argument checks and kernel choice.
+// Replaces the torch entry `attn_v4` of the reference (csrc/attention/attn_v4.cu:10-51).
+#include "attn.cuh"
+
 using namespace kfb;
-extern "C" size_t kfb_flash_attn_ws_bytes(int, int, int, int, int, int) { return 0; }
-extern "C" int kfb_flash_attn_fwd(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int,
-                                  float, const int64_t*, void*, size_t, void*) {
-  return fail(KFB_ERR_UNSUPPORTED, "flash_attn is not built in this library");
+
+namespace {
+
+int check_shape(int dtype, int B, int H, int Hk, int Nq, int Nk, int D, int causal) {
+  if (dtype != KFB_F16 && dtype != KFB_BF16) return fail(KFB_ERR_INVALID, "attention takes fp16 or bf16 tensors");
+  if (B < 1 || H < 1 || Hk < 1 || Nq < 1 || Nk < 1)
+    return fail(KFB_ERR_INVALID, "B, H, Hk, Nq, Nk must be >= 1 (got %d, %d, %d, %d, %d)", B, H, Hk, Nq, Nk);
+  if (D != 64 && D != 128) return fail(KFB_ERR_INVALID, "head dim must be one of (64, 128), got %d", D);
+  if (H % Hk) return fail(KFB_ERR_INVALID, "query heads (%d) must be a multiple of key/value heads (%d)", H, Hk);
+  if (causal && Nq > Nk) return fail(KFB_ERR_INVALID, "causal attention needs Nq <= Nk, got %d > %d", Nq, Nk);
+  return KFB_OK;
+}
+
+}  // namespace
+
+extern "C" size_t kfb_flash_attn_ws_bytes(int B, int H, int Hk, int Nq, int Nk, int D) {
+  if (B < 1 || H < 1 || Hk < 1 || Nq != 1 || Nk < 1 || (D != 64 && D != 128) || H % Hk) return 0;
+  return attn::decode_ws_bytes(B, H, Hk, Nk, D);
+}
+
+extern "C" int kfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int dtype, int B, int H,
+                                  int Hk, int Nq, int Nk, int D, int causal, float scale, const int64_t* kv_strides,
+                                  void* ws, size_t ws_bytes, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (int rc = check_shape(dtype, B, H, Hk, Nq, Nk, D, causal)) return rc;
+  if (!(scale > 0.0f)) return fail(KFB_ERR_INVALID, "scale must be positive, got %g", (double)scale);
+  if (!q || !k || !v || !o) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(KFB_ERR_ALIGNMENT, "q, k, v, o must be 16-byte aligned");
+  attn::Problem p;
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  p.dtype = dtype; p.B = B; p.H = H; p.Hk = Hk; p.Nq = Nq; p.Nk = Nk; p.D = D;
+  p.causal = causal ? 1 : 0;
+  p.scale = scale;
+  if (kv_strides) {
+    p.kv_stride_b = kv_strides[0]; p.kv_stride_h = kv_strides[1]; p.kv_stride_n = kv_strides[2];
+    if (p.kv_stride_n < D || p.kv_stride_h < 1 || p.kv_stride_b < 1 || (p.kv_stride_b % 8) || (p.kv_stride_h % 8) ||
+        (p.kv_stride_n % 8))
+      return fail(KFB_ERR_ALIGNMENT, "kv strides must be positive multiples of 8 elements with a row stride >= D");
+  } else {
+    p.kv_stride_n = D; p.kv_stride_h = (long long)Nk * D; p.kv_stride_b = (long long)Hk * Nk * D;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (Nq == 1) return attn::launch_decode(p, ws, ws_bytes, s);
+  return attn::launch_prefill(p, s);
 }

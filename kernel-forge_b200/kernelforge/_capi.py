@@ -23,6 +23,7 @@ _DTYPE_CODE = {torch.float16: KFB_F16, torch.bfloat16: KFB_BF16, torch.float32: 
 _SIGNATURES = {
     "kfb_version": (c_int, []),
     "kfb_last_error": (c_char_p, []),
+    "kfb_device_status": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "kfb_quantize_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "kfb_unpack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "kfb_pack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -68,6 +69,14 @@ def check(rc: int) -> None:
     if rc in (-1, -2):  # invalid argument / alignment: std::invalid_argument -> ValueError in the reference
         raise ValueError(msg)
     raise RuntimeError(f"kfb200 error {rc}: {msg}")
+
+
+def device_status(device: torch.device) -> int:
+    """The device status word: 0 unless a bounded wait inside a kernel has expired (synchronises)."""
+    out = ctypes.c_uint(0)
+    with on_device(device):
+        check(lib().kfb_device_status(ctypes.byref(out)))
+    return int(out.value)
 
 
 def dtype_code(dtype: torch.dtype) -> int:
