@@ -73,19 +73,41 @@ unsigned int* device_status_word() {
   return g_status_ptr[dev];
 }
 
+namespace {
+int resolve_encoder() {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return KFB_OK;
+}
+}  // namespace
+
+int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                       uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer) {
+  if (int rc = resolve_encoder()) return rc;
+  if (elem_bytes != 4) return fail(KFB_ERR_INVALID, "make_tmap_2d_plain handles 32-bit elements");
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstr[1] = {row_bytes};
+  cuuint32_t bdim[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled (2-D) failed with CUresult %d (dims %llu,%llu)", (int)r,
+                (unsigned long long)inner, (unsigned long long)outer);
+  return KFB_OK;
+}
+
 int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
                        const uint64_t strides_bytes[3], const uint32_t box[4]) {
-  {
-    std::lock_guard<std::mutex> lock(g_dev_mutex);
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-      if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
-        return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-  }
+  if (int rc = resolve_encoder()) return rc;
   cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
   cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
   cuuint32_t bdim[4] = {box[0], box[1], box[2], box[3]};

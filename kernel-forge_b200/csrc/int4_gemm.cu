@@ -1,7 +1,326 @@
-// placeholder until the tcgen05 GEMM lands
+// INT4 weight-only GEMM for sm_100a:  y[M, N] = x[M, K] @ W_hat[N, K]^T, any M, any N.
+//
+// Replaces dequant_gemm_tc_kernel + splitk_reduce of the reference
+// (csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162: mma.sync, 64x64 tiles, cp.async, N % 64 == 0).
+//
+// The product is computed transposed, y^T = W_hat x^T, so the 128 weight rows of a tile fill the
+// M = 128 dimension of tcgen05.mma and the batch is the MMA N (16..256): small batches are not
+// padded up to a 128-row tile.  One CTA per (128 output features, batch tile, K split):
+//   warp 4  (1 thread)  TMA: the packed int32 tile (128 rows x 8 words = 64 k) and the fp16 x tile
+//                       (batch rows x 64 k, 128-byte swizzle) of each K block, mbarrier ring;
+//   warps 0-3 (128 thr) dequantise: thread r unpacks row r (magic-number nibble unpack, exact q,
+//                       one fp16 multiply by the group scale = the reference's fp16(q*s),
+//                       dequant_gemm_tc_kernel.cuh:100-112) and stores it as a K-major row of the
+//                       128-byte-swizzled A tile; fence.proxy.async; then, at the end, the epilogue:
+//                       TMEM -> registers -> fp16 y (or FP32 split-K partials), coalesced along N;
+//   warp 5  (1 thread)  tcgen05.mma.kind::f16 A[smem] x B[smem] -> FP32 accumulator in TMEM.
+// Split-K partial sums are reduced in split order by a second kernel (deterministic).
+// Rows past N and batch rows past M are zero-filled by TMA and never stored.
 #include "common.cuh"
+#include "sm100.cuh"
+
+namespace kfb {
+namespace gemm {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileN = 128;   // output features per CTA (MMA M)
+constexpr int kBlockK = 64;   // k per pipeline stage (one 128-byte swizzle row of fp16)
+constexpr int kThreads = 192;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+
+enum WaitCode : uint32_t { kWaitFree = 0x301, kWaitLoaded, kWaitAReady, kWaitAcc };
+
+template <int MT>
+struct Layout {
+  static constexpr int kStages = MT <= 64 ? 4 : 3;
+  static constexpr int kA = kTileN * kBlockK * 2;        // dequantised weights, 16 KB
+  static constexpr int kP = kTileN * (kBlockK / 8) * 4;  // packed words, 4 KB
+  static constexpr int kX = MT * kBlockK * 2;            // activations
+  static constexpr int kStage = kA + kP + kX;            // multiples of 1024
+  static constexpr int kBars = kStages * kStage;
+  static constexpr int kMisc = kBars + 3 * kStages * 8 + 8;
+  static constexpr int kBytes = kMisc + 16;
+  static constexpr int kAlloc = kBytes + 1024;
+  static constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+};
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// 8 packed weights -> 4 half2 of fp16(q * s) in k order
+__device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s2) {
+  constexpr uint32_t kMagic = 0x64006400u;
+  const __half2 k1032 = u32_as_h2(0x64086408u);
+  const __half2 kSixteenth = u32_as_h2(0x2C002C00u);
+  const __half2 kMinus72 = u32_as_h2(0xD480D480u);
+  const uint32_t h = w >> 8;
+  uint4 r;
+  r.x = h2_as_u32(__hmul2(__hsub2(u32_as_h2((w & 0x000F000Fu) | kMagic), k1032), s2));
+  r.y = h2_as_u32(__hmul2(__hfma2(u32_as_h2((w & 0x00F000F0u) | kMagic), kSixteenth, kMinus72), s2));
+  r.z = h2_as_u32(__hmul2(__hsub2(u32_as_h2((h & 0x000F000Fu) | kMagic), k1032), s2));
+  r.w = h2_as_u32(__hmul2(__hfma2(u32_as_h2((h & 0x00F000F0u) | kMagic), kSixteenth, kMinus72), s2));
+  return r;
+}
+
+// out: fp16 y [M, N] when splits == 1, else FP32 partial [splits][M][N]
+template <int MT>
+__global__ void __launch_bounds__(kThreads)
+int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                 const __half* __restrict__ scales, __half* __restrict__ y, float* __restrict__ partial, int M, int N,
+                 int K, int group, int kblocks_per_split, unsigned int* status) {
+  using L = Layout<MT>;
+  constexpr int S = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* loaded = reinterpret_cast<uint64_t*>(smem + L::kBars);  // TMA landed
+  uint64_t* a_ready = loaded + S;                                   // dequantised tile written
+  uint64_t* stage_free = a_ready + S;                               // MMAs of the stage retired
+  uint64_t* acc_done = stage_free + S;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+  const AbortCtx ctx{abort_word, status};
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kTileN;
+  const int m0 = blockIdx.y * MT;
+  const int split = blockIdx.z, splits = gridDim.z;
+  const int total_kblocks = K / kBlockK;
+  const int kb_begin = split * kblocks_per_split;
+  const int kb_end = min(total_kblocks, kb_begin + kblocks_per_split);
+  const int n_kb = kb_end - kb_begin;  // >= 1 by construction
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&loaded[s], 1);
+      mbar_init(&a_ready[s], 4);
+      mbar_init(&stage_free[s], 1);
+    }
+    mbar_init(acc_done, 1);
+    *abort_word = *reinterpret_cast<volatile unsigned int*>(status);
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(tmem_slot, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool dead_on_arrival = *abort_word != 0;
+
+  if (dead_on_arrival) {
+    // fall through to the teardown
+  } else if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_w);
+      tma_prefetch_desc(&tm_x);
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % S;
+        if (!mbar_wait(&stage_free[s], ((uint32_t)(i / S) & 1u) ^ 1u, ctx, kWaitFree)) break;
+        mbar_arrive_expect_tx(&loaded[s], L::kP + L::kX);
+        uint8_t* st = smem + s * L::kStage;
+        const int kb = kb_begin + i;
+        tma_load_2d(st + L::kA, &tm_w, &loaded[s], kb * (kBlockK / 8), n0);
+        tma_load_2d(st + L::kA + L::kP, &tm_x, &loaded[s], kb * kBlockK, m0);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(kTileN, MT, 0, 0, 0);
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % S;
+        const uint32_t ph = (uint32_t)(i / S) & 1u;
+        if (!mbar_wait(&a_ready[s], ph, ctx, kWaitAReady)) break;  // implies loaded[s]: the dequant warps waited on it
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * L::kStage);
+        const uint32_t b_addr = a_addr + L::kA + L::kP;
+#pragma unroll
+        for (int kk = 0; kk < kBlockK / 16; ++kk)
+          mma_ss(tmem_base, smem_desc_sw128(a_addr + kk * 32, 16, 1024), smem_desc_sw128(b_addr + kk * 32, 16, 1024),
+                 idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&stage_free[s]);
+      }
+      tc_commit(acc_done);
+    }
+  } else {
+    // ---------------------------------------------------------------- dequantise (thread = weight row)
+    const int r = threadIdx.x;
+    const int row = n0 + r;
+    const int groups = K / group;
+    const __half* srow = scales + (size_t)min(row, N - 1) * groups;
+    bool ok = true;
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % S;
+      const uint32_t ph = (uint32_t)(i / S) & 1u;
+      const int kb = kb_begin + i;
+      const __half sc = srow[(kb * kBlockK) / group];
+      ok = __all_sync(0xffffffffu, mbar_wait(&loaded[s], ph, ctx, kWaitLoaded));
+      if (!ok) break;
+      uint8_t* st = smem + s * L::kStage;
+      const uint4* pw = reinterpret_cast<const uint4*>(st + L::kA + r * 32);
+      const uint4 w0 = pw[0], w1 = pw[1];
+      const __half2 s2 = __half2half2(sc);
+      uint8_t* arow = st + r * 128;
+      const int x = r & 7;
+      *reinterpret_cast<uint4*>(arow + ((0 ^ x) << 4)) = dequant8(w0.x, s2);
+      *reinterpret_cast<uint4*>(arow + ((1 ^ x) << 4)) = dequant8(w0.y, s2);
+      *reinterpret_cast<uint4*>(arow + ((2 ^ x) << 4)) = dequant8(w0.z, s2);
+      *reinterpret_cast<uint4*>(arow + ((3 ^ x) << 4)) = dequant8(w0.w, s2);
+      *reinterpret_cast<uint4*>(arow + ((4 ^ x) << 4)) = dequant8(w1.x, s2);
+      *reinterpret_cast<uint4*>(arow + ((5 ^ x) << 4)) = dequant8(w1.y, s2);
+      *reinterpret_cast<uint4*>(arow + ((6 ^ x) << 4)) = dequant8(w1.z, s2);
+      *reinterpret_cast<uint4*>(arow + ((7 ^ x) << 4)) = dequant8(w1.w, s2);
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to tcgen05.mma
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_ready[s]);
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, ctx, kWaitAcc));
+    if (ok) {
+      tc_fence_after_sync();
+      const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
+      const bool row_ok = row < N;
+#pragma unroll
+      for (int c0 = 0; c0 < MT; c0 += 32) {
+        if (m0 + c0 < M) {  // uniform: skip batch columns that do not exist
+          uint32_t acc[32];
+          if constexpr (MT >= 32) {
+            tmem_ld_x32(tmem_base + lane_bits + c0, acc);
+          } else {
+            tmem_ld_x16(tmem_base + lane_bits + c0, acc);
+          }
+          tmem_wait_ld();
+          constexpr int kCols = MT >= 32 ? 32 : MT;
+#pragma unroll
+          for (int c = 0; c < kCols; ++c) {
+            const int m = m0 + c0 + c;
+            if (row_ok && m < M) {
+              if (splits == 1) y[(size_t)m * N + row] = __float2half_rn(__uint_as_float(acc[c]));
+              else partial[((size_t)split * M + m) * N + row] = __uint_as_float(acc[c]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (!dead_on_arrival && *abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+}
+
+// y[i] = fp16(sum over splits, in split order, of partial[s][i])
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ y,
+                                                            long long elems, int splits) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * elems + i];
+    y[i] = __float2half_rn(acc);
+  }
+}
+
+struct Plan {
+  int mt, m_tiles, n_tiles, splits, kblocks_per_split;
+};
+
+Plan make_plan(int M, int N, int K) {
+  Plan p;
+  p.mt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  p.m_tiles = ceil_div(M, p.mt);
+  p.n_tiles = ceil_div(N, kTileN);
+  const int kblocks = K / kBlockK;
+  const int tiles = p.m_tiles * p.n_tiles;
+  int splits = sm_count() / (tiles > 0 ? tiles : 1);
+  const int max_splits = kblocks / 4 > 0 ? kblocks / 4 : 1;  // at least 4 K blocks per split
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  p.kblocks_per_split = ceil_div(kblocks, splits);
+  p.splits = ceil_div(kblocks, p.kblocks_per_split);  // no empty split
+  return p;
+}
+
+template <int MT>
+int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const void* scales, void* y, float* partial,
+           int M, int N, int K, int group, unsigned int* status, cudaStream_t stream) {
+  using L = Layout<MT>;
+  auto kernel = int4_gemm_kernel<MT>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  KFB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    KFB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    configured[dev] = true;
+  }
+  const dim3 grid(p.n_tiles, p.m_tiles, p.splits);
+  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tw, tx, (const __half*)scales, (__half*)y, partial, M, N, K, group,
+                                               p.kblocks_per_split, status);
+  KFB_LAUNCH_CHECK("int4_gemm_kernel");
+  if (p.splits > 1) {
+    const long long elems = (long long)M * N;
+    long long blocks = (elems + 255) / 256;
+    const long long cap = (long long)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    splitk_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(partial, (__half*)y, elems, p.splits);
+    KFB_LAUNCH_CHECK("splitk_reduce_kernel");
+  }
+  return KFB_OK;
+}
+
+}  // namespace
+}  // namespace gemm
+}  // namespace kfb
+
 using namespace kfb;
-extern "C" size_t kfb_int4_gemm_ws_bytes(int, int, int, int) { return 0; }
-extern "C" int kfb_int4_gemm(const void*, const void*, const void*, void*, int, int, int, int, void*, size_t, void*) {
-  return fail(KFB_ERR_UNSUPPORTED, "int4_gemm is not built in this library");
+
+extern "C" size_t kfb_int4_gemm_ws_bytes(int M, int N, int K, int group) {
+  if (M < 1 || N < 1 || K < 64 || (group != 64 && group != 128) || K % group) return 0;
+  const gemm::Plan p = gemm::make_plan(M, N, K);
+  return p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;
+}
+
+extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                             int group, void* ws, size_t ws_bytes, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (M < 1) return fail(KFB_ERR_INVALID, "int4_gemm needs M >= 1, got M=%d", M);
+  if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
+  if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
+  if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
+  const gemm::Plan p = gemm::make_plan(M, N, K);
+  const size_t need = p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;
+  if (need > 0 && (!ws || ws_bytes < need))
+    return fail(KFB_ERR_WORKSPACE, "int4_gemm needs a %zu-byte workspace for %d K splits, got %zu", need, p.splits, ws_bytes);
+  if (need > 0 && !aligned16(ws)) return fail(KFB_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
+  unsigned int* status = device_status_word();
+  if (!status) return fail(KFB_ERR_CUDA, "cannot resolve the device status word");
+
+  CUtensorMap tw, tx;
+  // packed int32 [N, K/8] seen as 32-bit elements, box 8 words x 128 rows, no swizzle
+  if (int rc = make_tmap_2d_plain(&tw, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, 8, 128)) return rc;
+  // x fp16 [M, K], box 64 k x MT rows, 128-byte swizzle (reuse the 4-D helper with unit outer dims)
+  const uint64_t xd[4] = {(uint64_t)K, (uint64_t)M, 1, 1};
+  const uint64_t xs[3] = {(uint64_t)K * 2, (uint64_t)M * K * 2, (uint64_t)M * K * 2};
+  const uint32_t xb[4] = {64, (uint32_t)p.mt, 1, 1};
+  if (int rc = make_tmap_4d_sw128(&tx, x, KFB_F16, xd, xs, xb)) return rc;
+
+  cudaStream_t s = (cudaStream_t)stream;
+  float* partial = static_cast<float*>(ws);
+  switch (p.mt) {
+    case 16: return gemm::launch<16>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+    case 32: return gemm::launch<32>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+    case 64: return gemm::launch<64>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+    case 128: return gemm::launch<128>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+    default: return gemm::launch<256>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+  }
 }
