@@ -297,16 +297,44 @@ def cpu_attention_sample(budget_s: float, causal: bool, cfg=(2, 16, 16, 2048, 20
 # main
 # ----------------------------------------------------------------------------------------------
 
+def single_kernel_main(args):
+    """One kernel, few launches: the command profiler captures are taken from."""
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    if args.workload == "int4_gemv":
+        n, k = (int(v) for v in args.shape.split(",")) if args.shape else (5632, 2048)
+        r = bench_int4_gemv(args, 1, device, 1, n, k)
+        best = max((r[x]["gbs"] for x in ("graph", "graph_pdl") if "gbs" in r.get(x, {})), default=0.0)
+        print(json.dumps({"metric": "int4_linear M=1 HBM GB/s (% peak)", "unit": "GB/s", "value": best, "n_gpus": 1,
+                          "config": {"workload": f"int4_gemv M=1 N={n} K={k} g128"}, "detail": r,
+                          "roofline": {"bound": "hbm", "achieved": best, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": best / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind}}))
+    else:
+        b, nk = (int(v) for v in args.shape.split(",")) if args.shape else (8, 4096)
+        r = bench_decode_attn(args, 1, device, b, nk)
+        print(json.dumps({"metric": "decode attention HBM GB/s (% peak)", "unit": "GB/s", "value": r["gbs"], "n_gpus": 1,
+                          "config": {"workload": f"decode attn Hq=32 Hkv=4 D=64 B={b} Nk={nk}"}, "detail": r,
+                          "roofline": {"bound": "hbm", "achieved": r["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": r["gbs"] / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only"])
+    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "decode_attn"],
+                    help="flash_attn = headline + every other workload under `also`; the others run one kernel only "
+                         "(small, for profiler captures)")
+    ap.add_argument("--shape", default=None, help="override: B,H,N,D (attention) / N,K (int4_gemv) / B,NK (decode_attn)")
+    ap.add_argument("--causal", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload in ("int4_gemv", "decode_attn"):
+        return single_kernel_main(args)
 
     config = {"workload": "flash_attn fwd MHA fp16 B=2 H=16 N=2048 D=64 non-causal, scale 1/sqrt(64)",
               "l2": "inputs rotate over distinct sets totalling > 2x the 126 MB L2",
@@ -332,7 +360,12 @@ def main():
     torch.cuda.set_device(device)
     peaks, peak_kind = measured_peaks()
 
-    fa = bench_flash_attn(args, world, device, causal=False)
+    cfg = (2, 16, 16, 2048, 2048, 64)
+    if args.shape:
+        b_, h_, n_, d_ = (int(v) for v in args.shape.split(","))
+        cfg = (b_, h_, h_, n_, n_, d_)
+        config["workload"] = f"flash_attn fwd MHA fp16 B={b_} H={h_} N={n_} D={d_} {'causal' if args.causal else 'non-causal'} (override)"
+    fa = bench_flash_attn(args, world, device, causal=args.causal, cfg=cfg)
     also = {}
     if args.workload == "flash_attn":
         fc = bench_flash_attn(args, world, device, causal=True)
@@ -359,7 +392,8 @@ def main():
         "also": also,
     })
     if rank == 0:
-        line["cpu_baseline"] = cpu_attention_sample(args.cpu_seconds, False) if world == 1 else None
+        full = args.workload == "flash_attn" and not args.shape
+        line["cpu_baseline"] = cpu_attention_sample(args.cpu_seconds, False) if (world == 1 and full) else None
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

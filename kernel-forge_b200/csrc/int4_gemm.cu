@@ -125,7 +125,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         uint8_t* st = smem + s * L::kStage;
         const int kb = kb_begin + i;
         tma_load_2d(st + L::kA, &tm_w, &loaded[s], kb * (kBlockK / 8), n0);
-        tma_load_2d(st + L::kA + L::kP, &tm_x, &loaded[s], kb * kBlockK, m0);
+        tma_load_4d(st + L::kA + L::kP, &tm_x, &loaded[s], kb * kBlockK, m0, 0, 0);  // tm_x is a 4-D map
       }
     }
   } else if (warp == kMmaWarp) {

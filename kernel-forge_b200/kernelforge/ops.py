@@ -101,7 +101,10 @@ def int4_gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group
 
 # Largest M served by the GEMV; from M = GEMV_MAX_M + 1 on the tensor-core GEMM is used.  The
 # reference measured 7 on its GPU (kernelforge/ops.py:193, bench/sweep_int4_dispatch.py:47-57).
-GEMV_MAX_M = 8
+# On B200, summed over the four layer shapes (5632x2048, 2048x2048, 8960x1536, 1536x8960) under a
+# CUDA graph, the GEMV takes 17.0 / 24.3 / 38.5 / 66.1 us at M = 1 / 2 / 4 / 8 and the GEMM a flat
+# 38-40 us up to M = 16, so the crossover sits between M = 4 and M = 5.
+GEMV_MAX_M = 4
 
 
 def int4_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
