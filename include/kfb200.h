@@ -113,6 +113,27 @@ int kfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int
                        int B, int H, int Hk, int Nq, int Nk, int D, int causal, float scale,
                        const int64_t* kv_strides, void* ws, size_t ws_bytes, void* stream);
 
+/* Decode attention (Nq == 1, one query per head at the last cache position) for callers that
+ * cannot allocate device memory: a server whose memory pool already owns the whole GPU, code
+ * between cudaStreamBeginCapture and EndCapture (cudaMalloc is not allowed there), a host runtime
+ * without a device allocator.  This entry point has no counterpart in the reference.
+ * It computes exactly what kfb_flash_attn_fwd computes for Nq == 1, but the split-KV partial
+ * results go through a 4 MiB array that is part of the library image (each GPU that loads the
+ * library holds those 4 MiB until the process exits) instead of a caller workspace; the call
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - A problem whose split plan needs more than 4 MiB (kfb_flash_attn_ws_bytes tells) is refused
+ *     with KFB_ERR_WORKSPACE.  On a 148-SM B200 every D = 64 plan fits; at D = 128 plans with
+ *     more than 504 (batch x kv-head x split) partials do not.  B*Hk >= 2*SMs needs no scratch.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to be cleared between calls
+ *     (each call overwrites every value it later reads), but two calls that can overlap on the
+ *     GPU -- different streams, or graph branches without a dependency -- race on it: serialise
+ *     them.  kv_strides as for kfb_flash_attn_fwd. */
+int kfb_flash_attn_decode_noalloc(const void* q, const void* k, const void* v, void* o, int dtype,
+                                  int B, int H, int Hk, int Nk, int D, float scale,
+                                  const int64_t* kv_strides, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

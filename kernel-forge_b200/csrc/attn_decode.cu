@@ -407,3 +407,90 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stre
 
 }  // namespace attn
 }  // namespace kfb
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// The split-KV kernel above hands its per-split partial results (O, m, l) from the first kernel to
+// the merge kernel through a workspace that the caller normally allocates.  Some callers cannot do
+// that: a serving loop that has already handed all device memory to its KV-cache pool, code running
+// inside a CUDA-graph capture (cudaMalloc is illegal there), or a host runtime that simply has no
+// allocator of its own.  For them the partials live in the fixed array below, which is part of the
+// library image: every GPU that loads the library holds these kMaxScratchBytes until the process
+// exits, whether or not the entry point is ever called.
+//
+// In host code the NAME of a __device__ array is only a host-side stand-in, not a device address,
+// so the address is resolved once per device with cudaGetSymbolAddress (that device being current)
+// and that pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace kfb {
+namespace attn {
+namespace {
+
+constexpr size_t kMaxScratchBytes = 4u << 20;  // 4 MiB: up to 992 (group, split) partials at D = 64, 504 at D = 128
+static __device__ __align__(256) unsigned char g_decode_scratch[kMaxScratchBytes];
+
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[64] = {nullptr};
+
+// Device address of g_decode_scratch on the current device (resolved on the first call per device).
+int static_scratch(void** out) {
+  int dev = 0;
+  KFB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(KFB_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(KFB_ERR_CUDA, "cudaGetSymbolAddress(decode scratch) failed: %s", cudaGetErrorString(e));
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return KFB_OK;
+}
+
+}  // namespace
+}  // namespace attn
+}  // namespace kfb
+
+extern "C" int kfb_flash_attn_decode_noalloc(const void* q, const void* k, const void* v, void* o, int dtype, int B,
+                                             int H, int Hk, int Nk, int D, float scale, const int64_t* kv_strides,
+                                             void* stream) {
+  using namespace kfb;
+  if (int rc = require_sm100()) return rc;
+  if (dtype != KFB_F16 && dtype != KFB_BF16) return fail(KFB_ERR_INVALID, "attention takes fp16 or bf16 tensors");
+  if (B < 1 || H < 1 || Hk < 1 || Nk < 1) return fail(KFB_ERR_INVALID, "B, H, Hk, Nk must be >= 1");
+  if (D != 64 && D != 128) return fail(KFB_ERR_INVALID, "head dim must be one of (64, 128), got %d", D);
+  if (H % Hk) return fail(KFB_ERR_INVALID, "query heads (%d) must be a multiple of key/value heads (%d)", H, Hk);
+  if (!(scale > 0.0f)) return fail(KFB_ERR_INVALID, "scale must be positive, got %g", (double)scale);
+  if (!q || !k || !v || !o) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(KFB_ERR_ALIGNMENT, "q, k, v, o must be 16-byte aligned");
+  const size_t need = attn::decode_ws_bytes(B, H, Hk, Nk, D);
+  if (need > attn::kMaxScratchBytes)
+    return fail(KFB_ERR_WORKSPACE,
+                "this problem needs %zu bytes of split-KV scratch but the built-in array holds %zu; "
+                "use kfb_flash_attn_fwd with a caller-provided workspace",
+                need, attn::kMaxScratchBytes);
+  attn::Problem p;
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  p.dtype = dtype; p.B = B; p.H = H; p.Hk = Hk; p.Nq = 1; p.Nk = Nk; p.D = D;
+  p.causal = 0;  // a single query at the last position sees every key
+  p.scale = scale;
+  if (kv_strides) {
+    p.kv_stride_b = kv_strides[0]; p.kv_stride_h = kv_strides[1]; p.kv_stride_n = kv_strides[2];
+    if (p.kv_stride_n < D || p.kv_stride_h < 1 || p.kv_stride_b < 1 || (p.kv_stride_b % 8) || (p.kv_stride_h % 8) ||
+        (p.kv_stride_n % 8))
+      return fail(KFB_ERR_ALIGNMENT, "kv strides must be positive multiples of 8 elements with a row stride >= D");
+  } else {
+    p.kv_stride_n = D; p.kv_stride_h = (long long)Nk * D; p.kv_stride_b = (long long)Hk * Nk * D;
+  }
+  void* scratch = nullptr;
+  if (int rc = attn::static_scratch(&scratch)) return rc;
+  // Every partial the merge kernel reads is written by the split kernel of the same call, so
+  // nothing left in the array by an earlier call is ever consumed and nothing needs clearing.
+  return attn::launch_decode(p, scratch, attn::kMaxScratchBytes, (cudaStream_t)stream);
+}
