@@ -203,19 +203,26 @@ def bench_flash_attn(args, world, device, causal: bool, cfg=(2, 16, 16, 2048, 20
 
 
 def bench_decode_attn(args, world, device, batch=8, nk=4096) -> dict:
+    """GQA decode attention (Hq=32, Hkv=4, D=64, q_len 1).  One CUDA graph holds one call per input set
+    (sets total > 2x L2, so every call reads its K/V from HBM); a step replays the graph.  Launching from a
+    graph removes the Python / ctypes overhead of ~50 us per call, which otherwise hides the kernel."""
     from kernelforge import ops
     h, hk, d = 32, 4, 64
     nbytes = 2 * batch * hk * nk * d * 2 + 2 * batch * h * d * 2
     n_sets = max(2, math.ceil(2 * L2_BYTES / nbytes))
     sets = attn_sets(batch, h, hk, 1, nk, d, n_sets, device, seed=1)
-
-    def step(i):
-        q, k, v = sets[i % n_sets]
-        ops.flash_attn(q, k, v, causal=True)
-
-    ms = time_steps(step, args.steps, args.warmup, world)
-    return {"gbs": world * nbytes * args.steps / (ms * 1e-3) / 1e9, "us_per_step": 1e3 * ms / args.steps,
-            "bytes_per_step": nbytes, "batch": batch, "nk": nk, "n_sets": n_sets}
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        for q, k, v in sets[:2]:
+            ops.flash_attn(q, k, v, causal=True)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            outs = [ops.flash_attn(q, k, v, causal=True) for q, k, v in sets]
+    ms = time_steps(lambda i: graph.replay(), args.steps, args.warmup, world)
+    calls = args.steps * n_sets
+    return {"gbs": world * nbytes * calls / (ms * 1e-3) / 1e9, "us_per_call": 1e3 * ms / calls,
+            "bytes_per_call": nbytes, "batch": batch, "nk": nk, "n_sets": n_sets}
 
 
 def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict:
@@ -269,6 +276,20 @@ def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict
     return out
 
 
+def bench_sharded_linear(args, world, device, m=128, n=8960, k=1536, group=128) -> dict:
+    """int4_linear sharded over output features: local N/world rows + one NCCL all-gather of [M, N/world]."""
+    import torch.distributed as dist
+    from kernelforge import parallel as kp
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(0)
+    qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), group)
+    lin = kp.ShardedInt4Linear.from_full(qw)
+    x = torch.randn(m, k, generator=g).half().to(device)
+    ms = time_steps(lambda i: lin(x), args.steps, args.warmup, world)
+    return {"us_per_call": 1e3 * ms / args.steps, "tflops": 2.0 * m * n * k * args.steps / (ms * 1e-3) / 1e12,
+            "rows_per_rank": n // world, "collective": "nccl all_gather_into_tensor"}
+
+
 # ----------------------------------------------------------------------------------------------
 # CPU baseline (the oracle = restatement of the reference's FP32 CPU path)
 # ----------------------------------------------------------------------------------------------
@@ -282,15 +303,16 @@ def cpu_attention_sample(budget_s: float, causal: bool, cfg=(2, 16, 16, 2048, 20
     v = rng.standard_normal((1, 1, nk, d), dtype=np.float32).astype(np.float16)
     ko.attention(q, k, v, causal)  # warm-up
     heads, t0 = 0, time.perf_counter()
-    while True:
+    while True:  # (batch, head) slices are independent and identical in cost: time as many as fit the budget
         ko.attention(q, k, v, causal)
         heads += 1
         el = time.perf_counter() - t0
-        if el >= budget_s or heads >= b * h:
+        if el >= budget_s:
             break
     flops_head = 4.0 * nq * nk * d / (2 if causal else 1)
     return {"value": heads * flops_head / el / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{heads} of {b * h} (batch, head) slices of the workload in {el:.1f} s, numpy/BLAS threads"}
+            "seconds": el,
+            "sample": f"{heads} (batch, head) slices (the workload has {b * h}) in {el:.1f} s, numpy/BLAS threads"}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -350,7 +372,8 @@ def main():
         vals = [cpu_attention_sample(per_step, False) for _ in range(args.warmup + args.steps)][args.warmup:]
         v = statistics.mean(x["value"] for x in vals)
         cb = dict(vals[-1], value=v)
-        line = dict(base, impl="reference", value=v, ms_per_step=None, cpu_baseline=cb, gpu_launches=0,
+        ms_step = 1e3 * statistics.mean(x["seconds"] for x in vals)
+        line = dict(base, impl="reference", value=v, ms_per_step=ms_step, cpu_baseline=cb, gpu_launches=0,
                     e2e={"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
         print(json.dumps(line))
         return
@@ -377,6 +400,14 @@ def main():
             "bound": "hbm", "achieved": None if best is None else best / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": None if best is None else best / world / peaks["hbm_gbs"], "traffic": None,
             "note": "achieved = sustained back-to-back calls on L2-cold weight copies; single_call is latency"})
+        gs = bench_int4_gemv(args, world, device, 1, 5632 * 32, 2048)
+        sbest = max((gs[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gs.get(k, {})), default=None)
+        also["int4_gemv_m1_stream_180224x2048"] = dict(gs, roofline={
+            "bound": "hbm", "achieved": None if sbest is None else sbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": None if sbest is None else sbest / world / peaks["hbm_gbs"], "traffic": None,
+            "note": "same kernel on 32 stacked copies of the 5632x2048 weight: the streaming regime of the GEMV"})
+        if world > 1:
+            also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
         for batch, nk in ((1, 4096), (8, 4096), (64, 4096), (8, 16384)):
             dd = bench_decode_attn(args, world, device, batch, nk)
             dd["frac_of_hbm"] = dd["gbs"] / world / peaks["hbm_gbs"]

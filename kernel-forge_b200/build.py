@@ -28,6 +28,10 @@ NVCC_FLAGS = [
 ]
 
 
+# per-source extra flags
+EXTRA_FLAGS: dict[str, list[str]] = {}
+
+
 def _nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -36,7 +40,7 @@ def _nvcc() -> str:
 
 
 def _deps_mtime() -> float:
-    hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [PKG_ROOT.parent / "include" / "kfb200.h"]
+    hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [PKG_ROOT.parent / "include" / "kfb200.h", Path(__file__)]
     return max(p.stat().st_mtime for p in hdrs if p.exists())
 
 
@@ -44,7 +48,7 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
     obj = BUILD / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, _deps_mtime()):
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *EXTRA_FLAGS.get(src.name, []), "-c", str(src), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     (BUILD / (src.stem + ".ptxas.txt")).write_text(res.stderr)
     if res.returncode != 0:

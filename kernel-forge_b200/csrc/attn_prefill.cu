@@ -3,31 +3,35 @@
 // Replaces attn_v4_kernel of the reference (csrc/attention/attn_v4_kernel.cuh:43-214), which is an
 // mma.sync / ldmatrix / cp.async kernel.  This one is built on the Blackwell execution model:
 //
-//   * one CTA per 128 query rows of one (batch, head); 192 threads in three roles:
+//   * one CTA per 128 query rows of one (batch, head), two CTAs resident per SM (each takes 256 of
+//     the 512 TMEM columns), so the softmax of one tile runs under the tensor-core work of the other;
+//   * 192 threads in three roles:
 //       warp 4  (1 thread)  TMA producer: Q once, K and V tiles of 128 keys through mbarrier rings,
 //                           128-byte-swizzled shared-memory tiles (a D=64 row is exactly 128 bytes)
-//       warp 5  (1 thread)  tcgen05.mma issuer: S = Q K^T (SS form, both operands K-major) into one of
-//                           two TMEM buffers, O += P V (TS form: P is read from TMEM, V is the
-//                           MN-major shared-memory operand, so V needs no transpose)
+//       warp 5  (1 thread)  tcgen05.mma issuer: S = Q K^T (SS form, both operands K-major) into
+//                           TMEM, O += P V (TS form: P is read from TMEM, V is the MN-major
+//                           shared-memory operand, so V needs no transpose)
 //       warps 0-3 (128 thr) softmax: thread r owns query row r = TMEM lane r, so row max / row sum
-//                           need no shuffles; base-2 online softmax with FP32 statistics; P is
-//                           rounded to the I/O type and written back to TMEM; O is rescaled in TMEM
-//                           only when some row maximum of the warp moved; epilogue O / l -> global
-//   * S(j+1) = Q K^T is issued before the softmax of tile j finishes (S is double-buffered), so
-//     the tensor pipe works under the softmax;
+//                           need no shuffles.  Two passes over S in TMEM (max, then exp), several
+//                           independent partial max / sum chains; P is rounded to the I/O type
+//                           and written over the S columns it was computed from; epilogue O / l.
+//   * lazy rescale: the running base of a row only moves when the new maximum exceeds it by more
+//     than 8 (a factor 256, far inside fp16/fp32 range); O in TMEM is rescaled only then.  O and l
+//     always share one base, so the quotient O / l is unaffected;
 //   * causal: tiles above the diagonal are never loaded or multiplied (loop bound), masking only
 //     on the diagonal / ragged tiles; query tiles are scheduled heaviest-first;
 //   * GQA: kv head = h / (H / Hk); TMA zero-fills rows past Nq / Nk, those keys are masked.
 //
-// TMEM columns (512 allocated, 1 CTA per SM): S0 [0,128) S1 [128,256) P0 [256,320) P1 [320,384)
-// O [384, 384 + D).
+// TMEM columns of a CTA (256 allocated): S [0,128) with P (16-bit, 64 columns) aliased on
+// S [0,64); O [128, 128 + D).
 //
 // Numerics (as the reference, attn_v4_kernel.cuh:133-213): scores accumulate in FP32; x = s *
-// (scale * log2 e); masked = -inf; base = max(m_old, rowmax) (0 when still -inf); p = 2^(x - base);
-// the row sum adds the unrounded p, the PV product uses p rounded to fp16/bf16; O / l rounded once.
-// 2^x is ex2.approx.ftz.f32.
+// (scale * log2 e); masked = -inf; p = 2^(x - base); the row sum adds the unrounded p, the PV
+// product uses p rounded to fp16/bf16; O / l rounded once.  2^x is ex2.approx.ftz.f32.
 #include "attn.cuh"
 #include "sm100.cuh"
+
+#include <cstdlib>
 
 namespace kfb {
 namespace attn {
@@ -40,9 +44,10 @@ constexpr int kBlockN = 128;
 constexpr int kThreads = 192;
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColP = 256, kColO = 384;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColP = 0, kColO = 128;
 constexpr int kHalfBytes = kBlockN * 128;  // one 64-column half of a tile: 128 rows x 128 bytes
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum WaitCode : uint32_t {
   kWaitQ = 0x101, kWaitKEmpty, kWaitKFull, kWaitVEmpty, kWaitVFull, kWaitSFull, kWaitPReady, kWaitPvDone
@@ -50,17 +55,19 @@ enum WaitCode : uint32_t {
 
 template <int D>
 struct Layout {
-  static constexpr int kStages = D == 64 ? 4 : 2;
+  // The dependency chain of one CTA is serial (QK -> softmax -> PV -> next QK), so one tile of
+  // look-ahead is all that can be used; the second resident CTA hides the rest.
+  static constexpr int kStages = D == 64 ? 2 : 1;
   static constexpr int kTile = kBlockN * D * 2;
   static constexpr int kQ = 0;
   static constexpr int kK = kTile;
   static constexpr int kV = kK + kStages * kTile;
   static constexpr int kBars = kV + kStages * kTile;
-  static constexpr int kNumBars = 4 * kStages + 6;
+  static constexpr int kNumBars = 4 * kStages + 4;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kBytes = kMisc + 16;
   static constexpr int kAlloc = kBytes + 1024;  // room to align the tiles to 1024 bytes
-  static_assert(2 * kAlloc > 227 * 1024, "a second CTA on the SM would block in tcgen05.alloc");
+  static_assert(2 * kAlloc <= 227 * 1024, "two CTAs must fit on one SM");
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -80,11 +87,68 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// Row maximum of the 128 scores of this thread's row.  The four 32-column TMEM loads are issued
+// back to back (the data of chunk c+1 is in flight while chunk c is reduced); eight independent
+// max chains.  kMask: columns past `limit` (causal diagonal / ragged tile) count as -inf.
+template <bool kMask>
+__device__ __forceinline__ float row_max(uint32_t s_tmem, int limit) {
+  float mx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+  uint32_t v[2][32];
+  tmem_ld_x32(s_tmem, v[0]);
+  tmem_wait_ld_regs(v[0]);
+#pragma unroll
+  for (int c = 0; c < kBlockN / 32; ++c) {
+    if (c + 1 < kBlockN / 32) tmem_ld_x32(s_tmem + (c + 1) * 32, v[(c + 1) & 1]);  // in flight during chunk c
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float x = __uint_as_float(v[c & 1][i]);
+      if (kMask && c * 32 + i > limit) x = -INFINITY;
+      mx[i & 7] = fmaxf(mx[i & 7], x);
+    }
+    if (c + 1 < kBlockN / 32) tmem_wait_ld_regs(v[(c + 1) & 1]);
+  }
+  return fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+}
+
+// p = 2^(x * scale - base) for the 128 scores of the row, rounded to the I/O type and stored to
+// TMEM columns [16c, 16c+16) of `p_tmem` (which may alias the S columns: chunk c of P only covers
+// columns that chunk <= c of S has already been read from).  Returns the FP32 sum of the unrounded p.
+template <bool kMask, bool kBf16>
+__device__ __forceinline__ float exp_and_store(uint32_t s_tmem, uint32_t p_tmem, int limit, float scale_log2, float base) {
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t v[2][32];
+  tmem_ld_x32(s_tmem, v[0]);
+  tmem_wait_ld_regs(v[0]);
+#pragma unroll
+  for (int c = 0; c < kBlockN / 32; ++c) {
+    if (c + 1 < kBlockN / 32) tmem_ld_x32(s_tmem + (c + 1) * 32, v[(c + 1) & 1]);  // in flight during chunk c
+    uint32_t p16[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float x0 = __uint_as_float(v[c & 1][2 * i]), x1 = __uint_as_float(v[c & 1][2 * i + 1]);
+      if (kMask && c * 32 + 2 * i > limit) x0 = -INFINITY;
+      if (kMask && c * 32 + 2 * i + 1 > limit) x1 = -INFINITY;
+      const float p0 = ex2(fmaf(x0, scale_log2, -base));
+      const float p1 = ex2(fmaf(x1, scale_log2, -base));
+      sum[i & 3] += p0 + p1;
+      p16[i] = pack2<kBf16>(p0, p1);
+    }
+    tmem_st_x16(p_tmem + c * 16, p16);
+    if (c + 1 < kBlockN / 32) tmem_wait_ld_regs(v[(c + 1) & 1]);
+  }
+  return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
 template <int D, bool kBf16>
-__global__ void __launch_bounds__(kThreads, 1)
+// Two CTAs are resident per SM (168 registers x 192 threads x 2 = 64512 <= 65536; 83 / 99 KB of
+// shared memory each; 256 TMEM columns each): the softmax of one runs under the MMAs of the other.
+// Measured at B=2 H=16 N=2048 D=64: 402 TFLOP/s with two resident CTAs, 206 with one.
+__global__ void __launch_bounds__(kThreads, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, void* __restrict__ o_ptr, int H, int Hk, int Nq, int Nk,
-                    int causal, float scale_log2, unsigned int* status) {
+                    int causal, float scale_log2, int serialize, unsigned int* status, unsigned long long* trace) {
   using L = Layout<D>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -96,8 +160,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* v_full = k_empty + S;
   uint64_t* v_empty = v_full + S;
   uint64_t* s_full = v_empty + S;
-  uint64_t* p_ready = s_full + 2;
-  uint64_t* pv_done = p_ready + 2;
+  uint64_t* p_ready = s_full + 1;
+  uint64_t* pv_done = p_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile uint32_t* abort_word = tmem_slot + 1;
   const AbortCtx ctx{abort_word, status};
@@ -120,10 +184,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(&p_ready[0], 128);
-    mbar_init(&p_ready[1], 128);
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
     *abort_word = *reinterpret_cast<volatile unsigned int*>(status);  // a wait expired earlier on this device:
     fence_mbar_init();                                                // do no work, return at once
@@ -137,6 +199,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool dead_on_arrival = *abort_word != 0;
+  // optional timeline of CTA (0,0,0) for tuning: 16 clock stamps per key tile
+  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int j, int k) {
+    if (tracing && j < 64) trace[j * 16 + k] = clock64();
+  };
 
   if (dead_on_arrival) {
     // fall through to the teardown
@@ -176,104 +243,98 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (!mbar_wait(&k_full[s], (uint32_t)(j / S) & 1u, ctx, kWaitKFull)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(smem + L::kK + s * L::kTile);
-        const uint32_t d_tmem = tmem_base + kColS + (uint32_t)(j & 1) * 128u;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (uint32_t)(kk / 4) * kHalfBytes + (uint32_t)(kk % 4) * 32u;
-          mma_ss(d_tmem, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk,
-                 kk > 0 ? 1u : 0u);
+          mma_ss(tmem_base + kColS, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024),
+                 idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc_commit(&k_empty[s]);
-        tc_commit(&s_full[j & 1]);
+        tc_commit(s_full);
         return true;
       };
       bool ok = mbar_wait(q_full, 0, ctx, kWaitQ);
       ok = ok && issue_qk(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles && !issue_qk(j + 1)) break;
-        if (!mbar_wait(&p_ready[j & 1], (uint32_t)(j >> 1) & 1u, ctx, kWaitPReady)) break;
+        if (!mbar_wait(p_ready, (uint32_t)j & 1u, ctx, kWaitPReady)) break;
+        stamp(j, 8);
         const int s = j % S;
         if (!mbar_wait(&v_full[s], (uint32_t)(j / S) & 1u, ctx, kWaitVFull)) break;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + L::kV + s * L::kTile);
-        const uint32_t p_tmem = tmem_base + kColP + (uint32_t)(j & 1) * 64u;
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // 16 keys per step: 16 rows of 128 bytes; the second 64-column block of V is kHalfBytes away
-          mma_ts(tmem_base + kColO, p_tmem + (uint32_t)kk * 8u, smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024),
-                 idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem_base + kColO, tmem_base + kColP + (uint32_t)kk * 8u,
+                 smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&v_empty[s]);
         tc_commit(pv_done);
+        stamp(j, 9);
+        if (j + 1 < n_tiles) {
+          // S(j+1) overwrites the columns P(j) lives in.  tcgen05.mma instructions of one thread execute in
+          // issue order, so PV(j) has read P before QK(j+1) writes; `serialize` (KFB_ATTN_SERIALIZE=1, a
+          // debugging aid) waits for PV(j) explicitly instead.
+          if (serialize && !mbar_wait(pv_done, (uint32_t)j & 1u, ctx, kWaitPvDone)) break;
+          stamp(j, 10);
+          if (!issue_qk(j + 1)) break;
+          stamp(j, 11);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue (warps 0-3)
     const int row = threadIdx.x;  // query row inside the tile == TMEM lane
     const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t s_tmem = tmem_base + kColS + lane_bits;
+    const uint32_t o_tmem = tmem_base + kColO + lane_bits;
+    float m_base = -INFINITY;  // the base O and l are currently expressed in (log2 units)
+    float l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int buf = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], (uint32_t)(j >> 1) & 1u, ctx, kWaitSFull));
+      // every lane polls: measured faster than one polling lane plus a shuffle (416 vs 346 TFLOP/s)
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, (uint32_t)j & 1u, ctx, kWaitSFull));
       if (!ok) break;
+      if (threadIdx.x == 0) stamp(j, 0);
       tc_fence_after_sync();
-      float s[kBlockN];
-      const uint32_t s_tmem = tmem_base + kColS + (uint32_t)buf * 128u + lane_bits;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-      tmem_wait_ld();
-
+      // S(j) complete implies PV(j-1) complete (the issuer orders them), so O may be touched here.
       const int k0 = j * kBlockN;
       const bool need_mask = (k0 + kBlockN > Nk) || (causal && (k0 + kBlockN - 1 > q0 + causal_off));
-      if (need_mask) {
-        int limit = Nk - 1;
-        if (causal) limit = min(limit, q0 + row + causal_off);
-#pragma unroll
-        for (int i = 0; i < kBlockN; ++i)
-          if (k0 + i > limit) s[i] = -INFINITY;
-      }
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < kBlockN; ++i) mx = fmaxf(mx, s[i]);
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      const float base = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2(m_run - base);
-      float sum = 0.f;
-      uint32_t p16[kBlockN / 2];
-#pragma unroll
-      for (int i = 0; i < kBlockN / 2; ++i) {
-        const float p0 = ex2(fmaf(s[2 * i], scale_log2, -base));
-        const float p1 = ex2(fmaf(s[2 * i + 1], scale_log2, -base));
-        sum += p0 + p1;
-        p16[i] = pack2<kBf16>(p0, p1);
-      }
-      l_run = fmaf(l_run, alpha, sum);
-      m_run = m_new;
+      int limit = Nk - 1;
+      if (causal) limit = min(limit, q0 + row + causal_off);
+      limit -= k0;  // last visible column of this tile for this row
 
-      if (j > 0) {
-        // O holds tiles 0..j-1 once PV(j-1) has completed; P[buf] was last read by PV(j-2)
-        ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, ctx, kWaitPvDone));
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+      // ---- pass 1: row maximum
+      const float m_tile = (need_mask ? row_max<true>(s_tmem, limit) : row_max<false>(s_tmem, limit)) * scale_log2;
+      if (threadIdx.x == 0) stamp(j, 1);
+      // lazy rescale: move the base only when the maximum outgrew it by more than the threshold
+      const bool grow = m_tile > m_base + kRescaleThreshold || m_base == -INFINITY;
+      float alpha = 1.0f;
+      if (grow && m_tile != -INFINITY) {
+        alpha = ex2(m_base - m_tile);  // 0 when m_base is still -inf
+        m_base = m_tile;
+      }
+      const float base = (m_base == -INFINITY) ? 0.f : m_base;
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_x32(tmem_base + kColO + lane_bits + c * 32, o);
-            tmem_wait_ld();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(o_tmem + c * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_x32(tmem_base + kColO + lane_bits + c * 32, o);
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(o_tmem + c * 32, o);
         }
       }
-      const uint32_t p_tmem = tmem_base + kColP + (uint32_t)buf * 64u + lane_bits;
-      tmem_st_x32(p_tmem, *reinterpret_cast<uint32_t(*)[32]>(&p16[0]));
-      tmem_st_x32(p_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&p16[32]));
+      if (threadIdx.x == 0) stamp(j, 2);
+      // ---- pass 2: p = 2^(x - base), row sum, P written over the S columns already consumed
+      const float tile_sum = need_mask ? exp_and_store<true, kBf16>(s_tmem, tmem_base + kColP + lane_bits, limit, scale_log2, base)
+                                       : exp_and_store<false, kBf16>(s_tmem, tmem_base + kColP + lane_bits, limit, scale_log2, base);
+      l_run = fmaf(l_run, alpha, tile_sum);
       tmem_wait_st();
+      if (threadIdx.x == 0) stamp(j, 3);
       tc_fence_before_sync();
-      mbar_arrive(&p_ready[buf]);
+      mbar_arrive(p_ready);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, ctx, kWaitPvDone));
     if (ok) {
@@ -284,7 +345,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
-        tmem_ld_x32(tmem_base + kColO + lane_bits + c * 32, o);
+        tmem_ld_x32(o_tmem + c * 32, o);
         tmem_wait_ld();
         if (store) {
           uint32_t packed[16];
@@ -313,6 +374,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
+unsigned long long* g_trace = nullptr;  // tuning aid, set through kfb_debug_set_attn_trace
+
 template <int D, bool kBf16>
 int launch(const Problem& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, unsigned int* status,
            cudaStream_t stream) {
@@ -323,11 +386,19 @@ int launch(const Problem& p, const CUtensorMap& tq, const CUtensorMap& tk, const
   KFB_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     KFB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    KFB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    if (getenv("KFB_DEBUG")) {
+      int nb = 0;
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, kThreads, L::kAlloc);
+      fprintf(stderr, "[kfb200] attn_prefill_kernel<%d,%d>: %d bytes smem, %d CTAs/SM\n", D, (int)kBf16, L::kAlloc, nb);
+    }
     configured[dev] = true;
   }
   const dim3 grid(ceil_div(p.Nq, kBlockM), p.H, p.B);
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, status);
+  static const int serialize = [] { const char* e = getenv("KFB_ATTN_SERIALIZE"); return e ? atoi(e) : 0; }();
+  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, serialize,
+                                               status, g_trace);
   KFB_LAUNCH_CHECK("attn_prefill_kernel");
   return KFB_OK;
 }
@@ -355,3 +426,8 @@ int launch_prefill(const Problem& p, cudaStream_t stream) {
 
 }  // namespace attn
 }  // namespace kfb
+
+// Tuning aid (not part of the public header): device buffer of 64 x 16 clock stamps written by CTA (0,0,0).
+extern "C" void kfb_debug_set_attn_trace(void* device_buffer) {
+  kfb::attn::g_trace = static_cast<unsigned long long*>(device_buffer);
+}

@@ -14,6 +14,9 @@
 //     (fma.rn.f32.f16: fp16 x fp16 + fp32, the product is exact), the per-group scale is
 //     applied in FP32 once per 32-weight chunk (32 divides G), then a warp-shuffle reduction
 //     and ONE rounding to fp16.  Result = FP32 dot product of the exact dequantised weights.
+//     For M <= 2 the kernel is issue-bound on B200 (INT and half2 ops issue at half the FP32 rate),
+//     so there the half2 conversions are skipped: the masked 1024+u / 1024+16u forms feed the FMA
+//     directly and the offsets are subtracted per chunk using sums of x shared by all rows.
 // K can be split across the warps of a CTA (fixed-order shared-memory reduce: deterministic).
 #include "common.cuh"
 
@@ -140,18 +143,45 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
       }
       const uint4* xc = reinterpret_cast<const uint4*>(x) + (size_t)c * 4;
       if constexpr (M <= 2) {
-        // activations resident, rows unpacked one at a time
+        // Decode path.  The kernel is issue-bound, so the nibbles are NOT converted to q: the masked
+        // forms A = 1024 + u (nibble pairs 0, 2) and B = 1024 + 16u (pairs 1, 3) go straight into the
+        // FP32 mixed-precision FMA (products of two 11-bit significands are exact in FP32) and the
+        // offsets are removed per 32-weight chunk with the class sums of x, shared by all R rows:
+        //   sum q x = (sum_A (1024+u) x - 1032 SxA) + (sum_B (1024+16u) x / 16 - 72 SxB).
         uint4 xv[M][4];
+        float sxa[M], sxb[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m)
+        for (int m = 0; m < M; ++m) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+          const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
+          float a = 0.f, b = 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            a = dot2_acc(0x3C003C00u, xs[i], a);      // half2(1, 1)
+            b = dot2_acc(0x3C003C00u, xs[i + 1], b);
+          }
+          sxa[m] = a * -1032.0f;
+          sxb[m] = b * -72.0f;
+        }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          uint32_t q[16];
-          unpack32(wv[r], q);
+          const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
 #pragma unroll
-          for (int m = 0; m < M; ++m) acc[m][r] = fmaf(sc[r], dot32(q, xv[m]), acc[m][r]);
+          for (int m = 0; m < M; ++m) {
+            const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
+            float pa = 0.f, pb = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              constexpr uint32_t kMagic = 0x64006400u;
+              const uint32_t w = wr[j], h = w >> 8;
+              pa = dot2_acc((w & 0x000F000Fu) | kMagic, xs[4 * j + 0], pa);
+              pb = dot2_acc((w & 0x00F000F0u) | kMagic, xs[4 * j + 1], pb);
+              pa = dot2_acc((h & 0x000F000Fu) | kMagic, xs[4 * j + 2], pa);
+              pb = dot2_acc((h & 0x00F000F0u) | kMagic, xs[4 * j + 3], pb);
+            }
+            acc[m][r] = fmaf(sc[r], (pa + sxa[m]) + fmaf(pb, 0.0625f, sxb[m]), acc[m][r]);
+          }
         }
       } else {
         // weights resident (unpacked once), activations streamed per m
@@ -235,10 +265,13 @@ int pick_rows(const void* x, const void* packed, const void* scales, void* y, in
   while (ksplit_log2 < 3 && KC / (32 << ksplit_log2) >= 4) ++ksplit_log2;
   // Rows per warp: as many as the register budget allows while the grid still fills the SMs.
   const int sms = sm_count();
-  constexpr int kMaxR = (M <= 2) ? 4 : 2;
+  constexpr int kMaxR = (M == 1) ? 8 : (M == 2) ? 4 : 2;
   int R = kMaxR;
   while (R > 1 && ceil_div(ceil_div(N, R), kWarps >> ksplit_log2) < 2 * sms) R >>= 1;
-  if constexpr (kMaxR == 4) {
+  if constexpr (kMaxR == 8) {
+    if (R == 8) return launch<M, 8, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+  }
+  if constexpr (kMaxR >= 4) {
     if (R == 4) return launch<M, 4, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
   }
   if (R == 2) return launch<M, 2, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);

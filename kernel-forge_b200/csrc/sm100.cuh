@@ -62,6 +62,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+  // no suspend-time hint: with a 20 us hint the wake-up after completion cost about 1000 clocks
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -73,6 +74,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+
+// Warp-collective wait: lane 0 waits, the other lanes sleep at the warp barrier instead of polling.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const struct AbortCtx& ctx, uint32_t code);
 
 // Waits for the phase with the given parity.  Returns false (and raises the abort word) on
 // timeout or when another thread of the CTA has already aborted.
@@ -91,6 +95,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
   }
   return true;
+}
+
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t code) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctx, code) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  // every lane must itself observe the phase before it touches what the barrier protects
+  if (ok) ok = mbar_try_wait(bar, parity) ? 1u : (mbar_wait(bar, parity, ctx, code) ? 1u : 0u);
+  return __all_sync(0xffffffffu, ok != 0);
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -133,6 +146,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// wait::ld that also names the destination registers of the load it completes, so the compiler
+// cannot schedule a use of them above the wait (the load writes them asynchronously).
+__device__ __forceinline__ void tmem_wait_ld_regs(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // All tcgen05 operations issued so far by this thread arrive (once) on `bar` when they complete.

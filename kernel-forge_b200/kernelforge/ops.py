@@ -132,7 +132,9 @@ def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
     """
     if x.shape[0] <= GEMV_MAX_M:
         return int4_gemv(x, packed, scales, group_size)
-    return int4_gemm(x, packed, scales, group_size)
+    # the GEMM kernel takes any N; only the public int4_gemm wrapper keeps the reference's N % 64 rule,
+    # so an nn.Linear with an odd N that worked below the reference's crossover (M <= 7) keeps working
+    return int4_gemm_ragged(x, packed, scales, group_size)
 
 
 # ---------------------------------------------------------------------------

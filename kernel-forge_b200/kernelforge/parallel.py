@@ -1,0 +1,126 @@
+"""Multi-GPU use of the two hot paths, one process per GPU over torch.distributed.
+
+The reference is single-GPU (no distributed code at all).  The paths shard naturally:
+
+* attention is independent per (batch, head): `shard_attention_heads` gives each rank a block of
+  query heads together with the KV heads they read; no communication at all.
+* int4_linear shards over output features N: rank r keeps rows [lo_r, hi_r) of `packed` / `scales`,
+  computes y[:, lo_r:hi_r] with the same kernels (the GEMM takes any N: 8960/8 = 1120, 1536/8 = 192 and
+  256/8 = 32 rows are not multiples of 64) and ONE all-gather over NCCL / NVLink rebuilds y [M, N].
+
+Nothing here launches a kernel itself; the compute goes through `kernelforge.ops`.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from . import quantize as kq
+
+
+def row_bounds(n: int, world: int) -> list[tuple[int, int]]:
+    """Contiguous, near-equal split of n rows over `world` ranks (the first n % world ranks get one more)."""
+    base, extra = divmod(n, world)
+    out, lo = [], 0
+    for r in range(world):
+        hi = lo + base + (1 if r < extra else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+def shard_quantized_weight(qw: kq.QuantizedWeight, rank: int, world: int) -> kq.QuantizedWeight:
+    """Rows [lo, hi) of a quantised weight.  Groups run along K, so a row shard needs no requantisation."""
+    lo, hi = row_bounds(qw.shape[0], world)[rank]
+    return kq.QuantizedWeight(packed=qw.packed[lo:hi].contiguous(), scales=qw.scales[lo:hi].contiguous(),
+                              group_size=qw.group_size, shape=(hi - lo, qw.shape[1]))
+
+
+def shard_attention_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rank: int, world: int):
+    """This rank's (q, k, v) for head-parallel attention.
+
+    KV heads are split over ranks when Hk >= world (each rank takes its KV heads and their H/Hk query heads);
+    when world > Hk (e.g. 8 GPUs, 4 KV heads) the query heads of one KV head are split over world/Hk ranks and
+    that KV head is replicated.  Outputs concatenate along the head axis in rank order.
+    """
+    h, hk = q.shape[1], k.shape[1]
+    g = h // hk
+    if hk % world == 0:
+        per = hk // world
+        ks = slice(rank * per, (rank + 1) * per)
+        qs = slice(rank * per * g, (rank + 1) * per * g)
+    elif world % hk == 0 and g % (world // hk) == 0:
+        split = world // hk
+        kv = rank // split
+        gq = g // split
+        ks = slice(kv, kv + 1)
+        qs = slice(kv * g + (rank % split) * gq, kv * g + (rank % split + 1) * gq)
+    else:
+        raise ValueError(f"cannot split H={h}, Hk={hk} over {world} ranks without breaking a KV group")
+    return q[:, qs].contiguous(), k[:, ks].contiguous(), v[:, ks].contiguous()
+
+
+class ShardedInt4Linear(torch.nn.Module):
+    """Output-feature-parallel INT4 linear: local shard compute + one all-gather.
+
+    `matmul` is the local compute (default: the kernels, any N); tests on CPU ranks pass a stand-in so
+    the sharding and gather logic can run under gloo without a GPU.
+    """
+
+    def __init__(self, qw_full_shape: tuple[int, int], local: kq.QuantizedWeight, bias: torch.Tensor | None = None,
+                 group: dist.ProcessGroup | None = None,
+                 matmul: Callable[[torch.Tensor, torch.Tensor, torch.Tensor, int], torch.Tensor] | None = None):
+        super().__init__()
+        self.out_features, self.in_features = qw_full_shape
+        self.group_size = local.group_size
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.bounds = row_bounds(self.out_features, self.world)
+        assert local.shape[0] == self.bounds[self.rank][1] - self.bounds[self.rank][0]
+        self.register_buffer("packed", local.packed)
+        self.register_buffer("scales", local.scales)
+        self.register_buffer("bias", None if bias is None else bias.detach().half())
+        self._matmul = matmul or _local_int4_matmul
+
+    @classmethod
+    def from_full(cls, qw: kq.QuantizedWeight, bias=None, group=None, matmul=None) -> "ShardedInt4Linear":
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        return cls(qw.shape, shard_quantized_weight(qw, rank, world), bias, group, matmul)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y_local = self._matmul(x2, self.packed, self.scales, self.group_size)  # [M, n_local]
+        y = gather_columns(y_local, self.bounds, self.group)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, self.out_features)
+
+
+def _local_int4_matmul(x, packed, scales, group_size):
+    if x.shape[0] <= ops.GEMV_MAX_M:
+        return ops.int4_gemv(x, packed, scales, group_size)
+    return ops.int4_gemm_ragged(x, packed, scales, group_size)
+
+
+def gather_columns(y_local: torch.Tensor, bounds: list[tuple[int, int]], group=None) -> torch.Tensor:
+    """All-gather of column blocks: rank r contributes y[:, lo_r:hi_r]; returns the full [M, N] on every rank.
+
+    Equal blocks use one all_gather_into_tensor (a single NCCL collective); ragged blocks are padded to the
+    widest block first."""
+    world = len(bounds)
+    m = y_local.shape[0]
+    widths = [hi - lo for lo, hi in bounds]
+    wmax = max(widths)
+    send = y_local if y_local.shape[1] == wmax else torch.nn.functional.pad(y_local, (0, wmax - y_local.shape[1]))
+    flat = torch.empty(world * m, wmax, dtype=y_local.dtype, device=y_local.device)  # rank-major concatenation
+    dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
+    recv = flat.view(world, m, wmax)
+    if all(w == wmax for w in widths):
+        return recv.permute(1, 0, 2).reshape(m, world * wmax)
+    return torch.cat([recv[r, :, :w] for r, w in enumerate(widths)], dim=1)

@@ -1,0 +1,75 @@
+"""The N > 1 path on CPU: two gloo ranks run the sharding / gather logic of kernelforge.parallel.  The local
+compute is replaced by the oracle (CPU ranks cannot launch the kernels); what is tested is the host side: row
+bounds, shard slicing, the all-gather reassembly (equal and ragged blocks) and head-parallel attention shards."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _oracle_matmul(x, packed, scales, group):
+    from oracle import kf_oracle as ko
+    y = ko.int4_linear(x.numpy(), packed.numpy(), scales.numpy(), group)
+    return torch.from_numpy(y.astype(np.float16))
+
+
+def _worker(rank, world, port, n):
+    for p in (str(ROOT), str(ROOT / "kernel-forge_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from kernelforge import parallel as kp
+        from kernelforge import quantize as kq
+        from oracle import kf_oracle as ko
+        g = torch.Generator().manual_seed(0)
+        w = torch.randn(n, 256, generator=g) * 0.02
+        x = torch.randn(3, 256, generator=g).half()
+        qw = kq.quantize_weight(w, 128)
+        lin = kp.ShardedInt4Linear.from_full(qw, bias=torch.arange(n).float() / n, matmul=_oracle_matmul)
+        lo, hi = kp.row_bounds(n, world)[rank]
+        assert lin.packed.shape[0] == hi - lo and torch.equal(lin.packed, qw.packed[lo:hi])
+        y = lin(x.reshape(1, 3, 256))
+        ref = ko.int4_linear(x.numpy(), qw.packed.numpy(), qw.scales.numpy(), 128).astype(np.float16)
+        want = torch.from_numpy(ref) + (torch.arange(n).float() / n).half()
+        assert y.shape == (1, 3, n)
+        assert torch.equal(y.reshape(3, n), want), "gathered result differs from the unsharded computation"
+        # head-parallel attention shards: concatenating per-rank oracle outputs reproduces the full result
+        q = torch.randn(1, 8, 5, 64, generator=g).half()
+        k = torch.randn(1, 2, 9, 64, generator=g).half()
+        v = torch.randn(1, 2, 9, 64, generator=g).half()
+        ql, kl, vl = kp.shard_attention_heads(q, k, v, rank, world)
+        o_local = torch.from_numpy(ko.attention(ql.numpy(), kl.numpy(), vl.numpy(), True))
+        parts = [torch.empty_like(o_local) for _ in range(world)]
+        dist.all_gather(parts, o_local)
+        full = torch.from_numpy(ko.attention(q.numpy(), k.numpy(), v.numpy(), True))
+        assert torch.allclose(torch.cat(parts, dim=1), full, atol=1e-6)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n", [64, 129])  # equal blocks / ragged blocks
+def test_two_gloo_ranks(n):
+    port = 29500 + (os.getpid() % 2000) + n
+    mp.spawn(_worker, args=(2, port, n), nprocs=2, join=True)
+
+
+def test_row_bounds_and_head_shards():
+    from kernelforge import parallel as kp
+    assert kp.row_bounds(8960, 8) == [(i * 1120, (i + 1) * 1120) for i in range(8)]
+    assert kp.row_bounds(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    q = torch.zeros(1, 32, 1, 64); k = torch.zeros(1, 4, 7, 64)
+    for world in (2, 4, 8):
+        heads = [kp.shard_attention_heads(q, k, k, r, world) for r in range(world)]
+        assert sum(t[0].shape[1] for t in heads) == 32
+        assert all(t[0].shape[1] % t[1].shape[1] == 0 for t in heads)
+    with pytest.raises(ValueError, match="KV group"):
+        kp.shard_attention_heads(q, k, k, 0, 3)
