@@ -63,7 +63,7 @@ struct Layout {
   static constexpr int kK = kTile;
   static constexpr int kV = kK + kStages * kTile;
   static constexpr int kBars = kV + kStages * kTile;
-  static constexpr int kNumBars = 4 * kStages + 4;
+  static constexpr int kNumBars = 4 * kStages + 5;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kBytes = kMisc + 16;
   static constexpr int kAlloc = kBytes + 1024;  // room to align the tiles to 1024 bytes
@@ -114,9 +114,14 @@ __device__ __forceinline__ float row_max(uint32_t s_tmem, int limit) {
 
 // p = 2^(x * scale - base) for the 128 scores of the row, rounded to the I/O type and stored to
 // TMEM columns [16c, 16c+16) of `p_tmem` (which may alias the S columns: chunk c of P only covers
-// columns that chunk <= c of S has already been read from).  Returns the FP32 sum of the unrounded p.
+// columns that chunk <= c of S has already been read from).  Returns the FP32 row sum.
+// ex2.approx.f32 per element; the sum adds the unrounded p (the reference's rule).  (ex2.approx.f16x2 on
+// pairs was tried: no faster on B200 -- 409 vs 433 TFLOP/s -- and less accurate, so it is not used.)
+// After the first half of the row (64 keys) has been stored, `half_ready` is signalled so the
+// issuer can start the first four PV MMAs while the second half is computed.
 template <bool kMask, bool kBf16>
-__device__ __forceinline__ float exp_and_store(uint32_t s_tmem, uint32_t p_tmem, int limit, float scale_log2, float base) {
+__device__ __forceinline__ float exp_and_store(uint32_t s_tmem, uint32_t p_tmem, int limit, float scale_log2, float base,
+                                              uint64_t* half_ready) {
   float sum[4] = {0.f, 0.f, 0.f, 0.f};
   uint32_t v[2][32];
   tmem_ld_x32(s_tmem, v[0]);
@@ -130,21 +135,27 @@ __device__ __forceinline__ float exp_and_store(uint32_t s_tmem, uint32_t p_tmem,
       float x0 = __uint_as_float(v[c & 1][2 * i]), x1 = __uint_as_float(v[c & 1][2 * i + 1]);
       if (kMask && c * 32 + 2 * i > limit) x0 = -INFINITY;
       if (kMask && c * 32 + 2 * i + 1 > limit) x1 = -INFINITY;
-      const float p0 = ex2(fmaf(x0, scale_log2, -base));
-      const float p1 = ex2(fmaf(x1, scale_log2, -base));
+      x0 = fmaf(x0, scale_log2, -base);
+      x1 = fmaf(x1, scale_log2, -base);
+      const float p0 = ex2(x0), p1 = ex2(x1);
       sum[i & 3] += p0 + p1;
       p16[i] = pack2<kBf16>(p0, p1);
     }
     tmem_st_x16(p_tmem + c * 16, p16);
+    if (c == 1) {
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(half_ready);
+    }
     if (c + 1 < kBlockN / 32) tmem_wait_ld_regs(v[(c + 1) & 1]);
   }
   return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
-template <int D, bool kBf16>
 // Two CTAs are resident per SM (168 registers x 192 threads x 2 = 64512 <= 65536; 83 / 99 KB of
 // shared memory each; 256 TMEM columns each): the softmax of one runs under the MMAs of the other.
 // Measured at B=2 H=16 N=2048 D=64: 402 TFLOP/s with two resident CTAs, 206 with one.
+template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, void* __restrict__ o_ptr, int H, int Hk, int Nq, int Nk,
@@ -160,8 +171,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* v_full = k_empty + S;
   uint64_t* v_empty = v_full + S;
   uint64_t* s_full = v_empty + S;
-  uint64_t* p_ready = s_full + 1;
-  uint64_t* pv_done = p_ready + 1;
+  uint64_t* p_ready = s_full + 1;   // [0]: keys 0-63 of P stored, [1]: keys 64-127
+  uint64_t* pv_done = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile uint32_t* abort_word = tmem_slot + 1;
   const AbortCtx ctx{abort_word, status};
@@ -185,7 +196,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(&p_ready[0], 128);
+    mbar_init(&p_ready[1], 128);
     mbar_init(pv_done, 1);
     *abort_word = *reinterpret_cast<volatile unsigned int*>(status);  // a wait expired earlier on this device:
     fence_mbar_init();                                                // do no work, return at once
@@ -256,18 +268,25 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       bool ok = mbar_wait(q_full, 0, ctx, kWaitQ);
       ok = ok && issue_qk(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (!mbar_wait(p_ready, (uint32_t)j & 1u, ctx, kWaitPReady)) break;
+        if (!mbar_wait(&p_ready[0], (uint32_t)j & 1u, ctx, kWaitPReady)) break;
         stamp(j, 8);
         const int s = j % S;
         if (!mbar_wait(&v_full[s], (uint32_t)(j / S) & 1u, ctx, kWaitVFull)) break;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + L::kV + s * L::kTile);
+        bool halves_ok = true;
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          if (kk == kBlockN / 32) {  // second half of the keys: wait for the rest of P
+            halves_ok = mbar_wait(&p_ready[1], (uint32_t)j & 1u, ctx, kWaitPReady);
+            if (!halves_ok) break;
+            tc_fence_after_sync();
+          }
           // 16 keys per step: 16 rows of 128 bytes; the second 64-column block of V is kHalfBytes away
           mma_ts(tmem_base + kColO, tmem_base + kColP + (uint32_t)kk * 8u,
                  smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
+        if (!halves_ok) break;
         tc_commit(&v_empty[s]);
         tc_commit(pv_done);
         stamp(j, 9);
@@ -328,13 +347,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       if (threadIdx.x == 0) stamp(j, 2);
       // ---- pass 2: p = 2^(x - base), row sum, P written over the S columns already consumed
-      const float tile_sum = need_mask ? exp_and_store<true, kBf16>(s_tmem, tmem_base + kColP + lane_bits, limit, scale_log2, base)
-                                       : exp_and_store<false, kBf16>(s_tmem, tmem_base + kColP + lane_bits, limit, scale_log2, base);
+      const uint32_t p_tmem = tmem_base + kColP + lane_bits;
+      const float tile_sum = need_mask ? exp_and_store<true, kBf16>(s_tmem, p_tmem, limit, scale_log2, base, &p_ready[0])
+                                       : exp_and_store<false, kBf16>(s_tmem, p_tmem, limit, scale_log2, base, &p_ready[0]);
       l_run = fmaf(l_run, alpha, tile_sum);
       tmem_wait_st();
       if (threadIdx.x == 0) stamp(j, 3);
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[1]);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, ctx, kWaitPvDone));
     if (ok) {
