@@ -276,6 +276,42 @@ def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict
     return out
 
 
+def bench_decode_e2e(args, device, batch: int, prompt_len=512, new_tokens=256) -> dict:
+    """Greedy decode of a random-init TinyLlama-1.1B-architecture model (22 layers, hidden 2048, 32 heads, 4 KV heads,
+    head dim 64, SiLU MLP 5632, vocab 32000; weights ~ N(0, 0.02)), all decoder linears INT4 g128, fused attention,
+    static KV cache, one CUDA graph per decode step.  Prompt = uniform random token ids (stands in for the
+    reference's WikiText-2 prompt, which is not available offline).  tok/s = batch * steps / device time."""
+    from kernelforge.llama_decode import TINYLLAMA_1B, LlamaInt4Decoder
+    dec = LlamaInt4Decoder.random_init(TINYLLAMA_1B, device, batch, prompt_len + new_tokens + 8, seed=0)
+    ids = torch.randint(0, TINYLLAMA_1B.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(0))
+    t0 = time.perf_counter()
+    dec.prefill(ids)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    dec.capture()
+    for _ in range(3):
+        dec.graph.replay()  # warm-up steps (they advance the sequence like any other step)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = new_tokens - 3
+    a.record()
+    for _ in range(steps):
+        dec.graph.replay()
+    b.record()
+    b.synchronize()
+    ms = a.elapsed_time(b)
+    s = TINYLLAMA_1B
+    weight_bytes = s.layers * (2 * s.hidden * s.heads * s.head_dim + 2 * s.hidden * s.kv_heads * s.head_dim
+                               + 3 * s.hidden * s.intermediate) * (0.5 + 2 / 128) + s.vocab * s.hidden * 2
+    kv_bytes = s.layers * 2 * batch * s.kv_heads * (prompt_len + new_tokens / 2) * s.head_dim * 2
+    out = {"tok_per_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "batch": batch, "prompt": prompt_len,
+           "steps_timed": steps, "prefill_s": prefill_s, "bytes_per_step": weight_bytes + kv_bytes,
+           "hbm_gbs": (weight_bytes + kv_bytes) / (ms / steps * 1e-3) / 1e9}
+    del dec
+    torch.cuda.empty_cache()
+    return out
+
+
 def bench_sharded_linear(args, world, device, m=128, n=8960, k=1536, group=128) -> dict:
     """int4_linear sharded over output features: local N/world rows + one NCCL all-gather of [M, N/world]."""
     import torch.distributed as dist
@@ -361,7 +397,7 @@ def main():
     config = {"workload": "flash_attn fwd MHA fp16 B=2 H=16 N=2048 D=64 non-causal, scale 1/sqrt(64)",
               "l2": "inputs rotate over distinct sets totalling > 2x the 126 MB L2",
               "per_gpu": "same batch shape on every GPU (batch x heads shard, no communication)"}
-    base = {"metric": "flash_attn TFLOPS (% peak)", "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+    base = {"metric": "flash_attn TFLOPS (% peak) [headline]; int4_linear M=1 HBM GB/s and decode tok/s under `also`", "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": config}
 
@@ -408,6 +444,14 @@ def main():
             "note": "same kernel on 32 stacked copies of the 5632x2048 weight: the streaming regime of the GEMV"})
         if world > 1:
             also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
+        if world == 1:
+            for batch in (1, 32):
+                try:
+                    r = bench_decode_e2e(args, device, batch)
+                    r["frac_of_hbm"] = r["hbm_gbs"] / peaks["hbm_gbs"]
+                    also[f"decode_e2e_tinyllama_arch_b{batch}"] = r
+                except Exception as exc:  # report, never hide
+                    also[f"decode_e2e_tinyllama_arch_b{batch}"] = {"error": repr(exc)[:300]}
         for batch, nk in ((1, 4096), (8, 4096), (64, 4096), (8, 16384)):
             dd = bench_decode_attn(args, world, device, batch, nk)
             dd["frac_of_hbm"] = dd["gbs"] / world / peaks["hbm_gbs"]

@@ -113,6 +113,17 @@ int kfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int
                        int B, int H, int Hk, int Nq, int Nk, int D, int causal, float scale,
                        const int64_t* kv_strides, void* ws, size_t ws_bytes, void* stream);
 
+/* Decode attention (Nq == 1) against a STATIC KV cache: k, v are [B, Hk, Nk, D] buffers of capacity Nk
+ * of which only kv_len_dev[b] rows (a device int32 array of B entries) are valid; the rest is ignored.
+ * The length is read by the kernel, so one captured launch can be replayed from a CUDA graph while the
+ * cache grows -- what the reference could not do (its kernel takes the length from the tensor shape, so
+ * its graph-mode decode falls back to SDPA: bench/e2e_model.py:91-92, README.md:101).
+ * Workspace as for kfb_flash_attn_fwd with Nq == 1 (kfb_flash_attn_ws_bytes(B, H, Hk, 1, Nk, D)). */
+int kfb_flash_attn_decode_kvlen(const void* q, const void* k, const void* v, void* o, int dtype,
+                                int B, int H, int Hk, int Nk, int D, float scale,
+                                const int64_t* kv_strides, const int32_t* kv_len_dev,
+                                void* ws, size_t ws_bytes, void* stream);
+
 /* Decode attention (Nq == 1, one query per head at the last cache position) for callers that
  * cannot allocate device memory: a server whose memory pool already owns the whole GPU, code
  * between cudaStreamBeginCapture and EndCapture (cudaMalloc is not allowed there), a host runtime

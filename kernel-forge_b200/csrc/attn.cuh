@@ -16,6 +16,8 @@ struct Problem {
   int causal;
   float scale;
   long long kv_stride_b, kv_stride_h, kv_stride_n;  // elements
+  // decode only: device array of B valid lengths (<= Nk, the capacity of the cache); nullptr = all Nk keys
+  const int* kv_len_dev = nullptr;
 };
 
 // Prefill / general path: one CTA per 128 query rows, TMA + tcgen05 + TMEM (attn_prefill.cu).

@@ -105,7 +105,7 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const uint16_t* __restrict__ q, uint16_t* __restrict__ o, float* __restrict__ partial, int H, int Hk,
-                   int Nk, int keys_per_split, float scale_log2, unsigned int* status) {
+                   int Nk, int keys_per_split, float scale_log2, unsigned int* status, const int* __restrict__ kv_len) {
   using L = Layout<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -123,7 +123,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int h0 = hk * G + chunk * kRows;               // first query head of this CTA
   const int rows = min(kRows, G - chunk * kRows);      // real query heads
   const int key_begin = split * keys_per_split;
-  const int key_end = min(Nk, key_begin + keys_per_split);
+  // a static KV cache holds Nk rows of which only kv_len[b] are valid (read on the device, so the
+  // same launch can be replayed from a CUDA graph while the cache fills up)
+  const int valid = kv_len ? min(Nk, max(kv_len[b], 0)) : Nk;
+  const int key_end = min(valid, key_begin + keys_per_split);
   const int n_tiles = key_end > key_begin ? (key_end - key_begin + kTileKeys - 1) / kTileKeys : 0;
 
   if (threadIdx.x == 0) {
@@ -230,6 +233,20 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int i = 0; i < D / 8; ++i) {
           oacc[i][2 * r] *= alpha;
           oacc[i][2 * r + 1] *= alpha;
+        }
+      }
+      // Rows of V past key_end get p = 0, but 0 * NaN = NaN: with a device-side length those rows are
+      // whatever the cache buffer holds, so this warp zeroes them in its 16-key slice of the tile first.
+      {
+        const int first_bad = key_end - (key_begin + t * kTileKeys);  // tile-relative; >= 64 when all rows are valid
+        if (first_bad < kw + 16) {
+          const int r0 = max(first_bad, kw);
+          for (int i = lane; i < (kw + 16 - r0) * 8 * (D / 64); i += 32) {
+            const int row = r0 + i / (8 * (D / 64)), rem = i % (8 * (D / 64));
+            *reinterpret_cast<uint4*>(smem + s * L::kStage + L::kTile + (rem >> 3) * L::kHalf + row * 128 + (rem & 7) * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+          }
+          __syncwarp();
         }
       }
       // O[16 x D] += P[16 x 16 keys] V[16 keys x D]
@@ -362,7 +379,7 @@ int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const
   }
   const dim3 grid(plan.splits, p.Hk * plan.chunks, p.B);
   kernel<<<grid, kThreads, L::kAlloc, stream>>>(tk, tv, (const uint16_t*)p.q, (uint16_t*)p.o, partial, p.H, p.Hk, p.Nk,
-                                               plan.keys_per_split, p.scale * 1.4426950408889634f, status);
+                                               plan.keys_per_split, p.scale * 1.4426950408889634f, status, p.kv_len_dev);
   KFB_LAUNCH_CHECK("attn_decode_kernel");
   if (plan.splits > 1) {
     attn_decode_merge_kernel<D, kBf16><<<dim3(p.H, p.B), D, 0, stream>>>(partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits);

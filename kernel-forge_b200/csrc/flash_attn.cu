@@ -49,3 +49,30 @@ extern "C" int kfb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if (Nq == 1) return attn::launch_decode(p, ws, ws_bytes, s);
   return attn::launch_prefill(p, s);
 }
+
+// Decode attention against a static KV cache whose valid length lives on the device.
+extern "C" int kfb_flash_attn_decode_kvlen(const void* q, const void* k, const void* v, void* o, int dtype, int B, int H,
+                                           int Hk, int Nk, int D, float scale, const int64_t* kv_strides,
+                                           const int32_t* kv_len_dev, void* ws, size_t ws_bytes, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (int rc = check_shape(dtype, B, H, Hk, 1, Nk, D, 0)) return rc;
+  if (!(scale > 0.0f)) return fail(KFB_ERR_INVALID, "scale must be positive, got %g", (double)scale);
+  if (!q || !k || !v || !o || !kv_len_dev) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(KFB_ERR_ALIGNMENT, "q, k, v, o must be 16-byte aligned");
+  attn::Problem p;
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  p.dtype = dtype; p.B = B; p.H = H; p.Hk = Hk; p.Nq = 1; p.Nk = Nk; p.D = D;
+  p.causal = 0;
+  p.scale = scale;
+  p.kv_len_dev = kv_len_dev;
+  if (kv_strides) {
+    p.kv_stride_b = kv_strides[0]; p.kv_stride_h = kv_strides[1]; p.kv_stride_n = kv_strides[2];
+    if (p.kv_stride_n < D || p.kv_stride_h < 1 || p.kv_stride_b < 1 || (p.kv_stride_b % 8) || (p.kv_stride_h % 8) ||
+        (p.kv_stride_n % 8))
+      return fail(KFB_ERR_ALIGNMENT, "kv strides must be positive multiples of 8 elements with a row stride >= D");
+  } else {
+    p.kv_stride_n = D; p.kv_stride_h = (long long)Nk * D; p.kv_stride_b = (long long)Hk * Nk * D;
+  }
+  return attn::launch_decode(p, ws, ws_bytes, (cudaStream_t)stream);
+}

@@ -226,6 +226,37 @@ def flash_attn_kv_view(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal
     return _attn_launch(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]), kv_strides=k.stride()[:3])
 
 
+def flash_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
+                      scale: float | None = None) -> torch.Tensor:
+    """One decode step against a static KV cache.
+
+    q: [B, H, 1, D]; k_cache, v_cache: [B, Hk, Lmax, D] (contiguous or a strided view with a dense D axis);
+    kv_len: int32 CUDA tensor [B], the number of valid cache rows per sequence (the new token's K/V already
+    written).  The length is read on the device, so the call can be captured once in a CUDA graph and
+    replayed while the cache fills (the reference's graph-mode decode has to use SDPA instead,
+    bench/e2e_model.py:91-92).  Returns [B, H, 1, D]."""
+    _check_attn(q, k_cache, v_cache, False, strided_kv=True)
+    if q.shape[2] != 1:
+        raise ValueError(f"flash_attn_decode takes one query position per sequence, got Nq={q.shape[2]}")
+    if kv_len.dtype != torch.int32 or not kv_len.is_cuda or kv_len.numel() != q.shape[0]:
+        raise TypeError("kv_len must be an int32 CUDA tensor with one entry per batch item")
+    if k_cache.stride() != v_cache.stride() or k_cache.stride(3) != 1 or any(s % 8 for s in k_cache.stride()[:3]):
+        raise ValueError("k_cache and v_cache must share strides, with a dense D axis and strides that are multiples of 8")
+    b, h, _, d = q.shape
+    hk, nk = k_cache.shape[1], k_cache.shape[2]
+    o = torch.empty_like(q)
+    lib = _capi.lib()
+    ws_bytes = lib.kfb_flash_attn_ws_bytes(b, h, hk, 1, nk, d)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+    strides = (ctypes.c_int64 * 3)(*k_cache.stride()[:3])
+    with _capi.on_device(q.device):
+        _capi.check(lib.kfb_flash_attn_decode_kvlen(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), o.data_ptr(),
+                                                    _capi.dtype_code(q.dtype), b, h, hk, nk, d,
+                                                    _resolve_scale(scale, d), strides, kv_len.data_ptr(),
+                                                    ws.data_ptr(), ws_bytes, _capi.stream_ptr(q.device)))
+    return o
+
+
 # ---------------------------------------------------------------------------
 # int4_linear: the nn.Linear-shaped entry point
 # ---------------------------------------------------------------------------

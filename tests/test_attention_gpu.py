@@ -129,6 +129,42 @@ def test_kv_cache_view_is_read_in_place():
     assert np.abs(out.float().cpu().numpy() - attn_oracle(q2, k2, v2, True)).max() <= ATTN_ATOL[torch.float16]
 
 
+@pytest.mark.parametrize("b,h,hk,cap,d", [(2, 32, 4, 512, 64), (1, 8, 8, 256, 128), (3, 16, 2, 4096, 64)])
+def test_decode_with_device_side_length(b, h, hk, cap, d):
+    """Static cache of capacity `cap`; only kv_len[b] rows are valid, the rest holds garbage that must be ignored."""
+    q, k, v = qkv_case(b, h, hk, 1, cap, d, torch.float16, seed=cap + d)
+    lens = [cap, max(1, cap // 3), 1][:b] + [cap // 2] * max(0, b - 3)
+    kc, vc = k.clone(), v.clone()
+    for i, n in enumerate(lens):
+        kc[i, :, n:] = 1000.0       # poison what lies beyond the valid length
+        vc[i, :, n:] = float("nan")
+    out = ops.flash_attn_decode(q.cuda(), kc.cuda(), vc.cuda(), torch.tensor(lens, dtype=torch.int32).cuda())
+    assert torch.isfinite(out).all()
+    for i, n in enumerate(lens):
+        ref = attn_oracle(q[i:i + 1], k[i:i + 1, :, :n], v[i:i + 1, :, :n], True)
+        assert np.abs(out[i:i + 1].float().cpu().numpy() - ref).max() <= ATTN_ATOL[torch.float16]
+
+
+def test_decode_length_is_read_at_replay_time():
+    """One captured launch, replayed while the device-side length grows: the result follows the length."""
+    q, k, v = qkv_case(1, 8, 2, 1, 256, 64, torch.float16, seed=77)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    n = torch.tensor([10], dtype=torch.int32).cuda()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ops.flash_attn_decode(qc, kc, vc, n)
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            out = ops.flash_attn_decode(qc, kc, vc, n)
+    for length in (10, 11, 200, 256):
+        n.fill_(length)
+        g.replay()
+        torch.cuda.synchronize()
+        ref = attn_oracle(q, k[:, :, :length], v[:, :, :length], True)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= ATTN_ATOL[torch.float16]
+
+
 def test_determinism_and_status_word():
     q, k, v = qkv_case(1, 32, 4, 1, 4096, 64, torch.float16, seed=5)
     a = ops.flash_attn(q.cuda(), k.cuda(), v.cuda(), causal=True)
