@@ -368,6 +368,22 @@ def single_kernel_main(args):
                           "config": {"workload": f"int4_gemv M=1 N={n} K={k} g128"}, "detail": r,
                           "roofline": {"bound": "hbm", "achieved": best, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                        "frac": best / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind}}))
+    elif args.workload == "int4_gemm":
+        from kernelforge import ops
+        from kernelforge import quantize as kq
+        m, n, k = (int(v) for v in args.shape.split(",")) if args.shape else (1024, 8960, 1536)
+        g = torch.Generator().manual_seed(0)
+        copies = max(2, math.ceil(2 * L2_BYTES / (n * k // 2 + 2 * m * k + 2 * m * n)))
+        qws = [kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), 128) for _ in range(copies)]
+        xs = [torch.randn(m, k, generator=g).half().to(device) for _ in range(copies)]
+        ms = time_steps(lambda i: ops.int4_gemm_ragged(xs[i % copies], qws[i % copies].packed, qws[i % copies].scales, 128),
+                        args.steps, args.warmup, 1)
+        tf = 2.0 * m * n * k * args.steps / (ms * 1e-3) / 1e12
+        print(json.dumps({"metric": "int4_linear TFLOPS (% peak)", "unit": "TFLOP/s", "value": tf, "n_gpus": 1,
+                          "config": {"workload": f"int4_gemm M={m} N={n} K={k} g128", "l2": f"{copies} rotating weight/activation sets"},
+                          "ms_per_step": ms / args.steps,
+                          "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                       "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peak_kind}}))
     else:
         b, nk = (int(v) for v in args.shape.split(",")) if args.shape else (8, 4096)
         r = bench_decode_attn(args, 1, device, b, nk)
@@ -383,15 +399,15 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "decode_attn"],
+    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "int4_gemm", "decode_attn"],
                     help="flash_attn = headline + every other workload under `also`; the others run one kernel only "
                          "(small, for profiler captures)")
-    ap.add_argument("--shape", default=None, help="override: B,H,N,D (attention) / N,K (int4_gemv) / B,NK (decode_attn)")
+    ap.add_argument("--shape", default=None, help="override: B,H,N,D (attention) / N,K (int4_gemv) / M,N,K (int4_gemm) / B,NK (decode_attn)")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload in ("int4_gemv", "decode_attn"):
+    if args.workload in ("int4_gemv", "int4_gemm", "decode_attn"):
         return single_kernel_main(args)
 
     config = {"workload": "flash_attn fwd MHA fp16 B=2 H=16 N=2048 D=64 non-causal, scale 1/sqrt(64)",

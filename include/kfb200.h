@@ -133,8 +133,9 @@ int kfb_flash_attn_decode_kvlen(const void* q, const void* k, const void* v, voi
  * library holds those 4 MiB until the process exits) instead of a caller workspace; the call
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.
  *   - A problem whose split plan needs more than 4 MiB (kfb_flash_attn_ws_bytes tells) is refused
- *     with KFB_ERR_WORKSPACE.  On a 148-SM B200 every D = 64 plan fits; at D = 128 plans with
- *     more than 504 (batch x kv-head x split) partials do not.  B*Hk >= 2*SMs needs no scratch.
+ *     with KFB_ERR_WORKSPACE: the array holds 992 (batch x kv-head x split) partials at D = 64
+ *     and 504 at D = 128.  Small batches fit (B = 1..8 with 4 KV heads: at most 416 partials);
+ *     e.g. B = 32, Hk = 4, Nk = 16384 (1280 partials) does not.
  *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress);
  *     make that first call outside any stream capture.
  *   - All calls on a device share the one array.  Nothing in it has to be cleared between calls

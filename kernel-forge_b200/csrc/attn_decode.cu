@@ -349,17 +349,30 @@ struct SplitPlan {
   int chunks, splits, keys_per_split;
 };
 
-SplitPlan plan_splits(int B, int H, int Hk, int Nk) {
+SplitPlan plan_splits(int B, int H, int Hk, int Nk, int D) {
+  // Choose the number of key splits so that the grid fills whole waves of resident CTAs
+  // (3 per SM at D = 64, 1 at D = 128: shared memory) while every split keeps at least 2 tiles.
   SplitPlan p;
   const int G = H / Hk;
   p.chunks = ceil_div(G, kRows);
   const long long groups = (long long)B * Hk * p.chunks;
   const int tiles = ceil_div(Nk, kTileKeys);
-  const long long target = 2LL * sm_count();  // two CTAs per SM keep ~128 KB of loads in flight
-  long long want = groups >= target ? 1 : (target + groups - 1) / groups;
-  if (want > tiles) want = tiles;
-  if (want < 1) want = 1;
-  const int tiles_per_split = ceil_div(tiles, (int)want);
+  const long long slots = (long long)sm_count() * (D == 64 ? 3 : 1);
+  int best = 1;
+  double best_score = -1.0;
+  const int max_splits = tiles >= 4 ? (tiles / 2 < 128 ? tiles / 2 : 128) : 1;
+  for (int s = 1; s <= max_splits; ++s) {
+    const int per = ceil_div(tiles, s);
+    const int real = ceil_div(tiles, per);           // splits actually launched
+    if (real != s) continue;
+    const double waves = (double)(groups * real) / (double)slots;
+    const double full = waves <= 1.0 ? 1.0 : (double)(long long)(waves + 0.999999);
+    // time ~ full waves x tiles per split (+1 tile of fixed cost per CTA); lower is better
+    const double cost = full * (per + 1.0) + (waves <= 1.0 ? (1.0 - waves) * 0.01 : 0.0);
+    const double score = 1.0 / cost;
+    if (score > best_score * 1.0001) { best_score = score; best = real; }
+  }
+  const int tiles_per_split = ceil_div(tiles, best);
   p.keys_per_split = tiles_per_split * kTileKeys;
   p.splits = ceil_div(Nk, p.keys_per_split);
   return p;
@@ -391,7 +404,7 @@ int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const
 }  // namespace
 
 size_t decode_ws_bytes(int B, int H, int Hk, int Nk, int D) {
-  const SplitPlan plan = plan_splits(B, H, Hk, Nk);
+  const SplitPlan plan = plan_splits(B, H, Hk, Nk, D);
   if (plan.splits <= 1) return 0;
   return (size_t)B * Hk * plan.chunks * plan.splits * kRows * (D + 2) * sizeof(float);
 }
@@ -399,7 +412,7 @@ size_t decode_ws_bytes(int B, int H, int Hk, int Nk, int D) {
 int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
   if (p.Hk * ceil_div(p.H / p.Hk, kRows) > 65535 || p.B > 65535 || p.H > 65535)
     return fail(KFB_ERR_INVALID, "B, H and Hk * ceil(H/Hk/16) must each be <= 65535");
-  const SplitPlan plan = plan_splits(p.B, p.H, p.Hk, p.Nk);
+  const SplitPlan plan = plan_splits(p.B, p.H, p.Hk, p.Nk, p.D);
   const size_t need = decode_ws_bytes(p.B, p.H, p.Hk, p.Nk, p.D);
   if (need > 0 && (!ws || ws_bytes < need))
     return fail(KFB_ERR_WORKSPACE, "decode attention needs a %zu-byte workspace, got %zu", need, ws_bytes);

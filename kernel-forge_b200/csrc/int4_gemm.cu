@@ -27,15 +27,17 @@ using namespace sm100;
 
 constexpr int kTileN = 128;   // output features per CTA (MMA M)
 constexpr int kBlockK = 64;   // k per pipeline stage (one 128-byte swizzle row of fp16)
-constexpr int kThreads = 192;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
+constexpr int kDequantWarps = 8;  // two threads per weight row: four packed words each
+constexpr int kThreads = (kDequantWarps + 2) * 32;
+constexpr int kProducerWarp = kDequantWarps;
+constexpr int kMmaWarp = kDequantWarps + 1;
 
 enum WaitCode : uint32_t { kWaitFree = 0x301, kWaitLoaded, kWaitAReady, kWaitAcc };
 
 template <int MT>
 struct Layout {
-  static constexpr int kStages = MT <= 64 ? 4 : 3;
+  // TMA latency (~1400 clocks) + dequantisation + MMA of one K block must be covered by the other stages
+  static constexpr int kStages = MT <= 64 ? 4 : (MT == 128 ? 5 : 4);
   static constexpr int kA = kTileN * kBlockK * 2;        // dequantised weights, 16 KB
   static constexpr int kP = kTileN * (kBlockK / 8) * 4;  // packed words, 4 KB
   static constexpr int kX = MT * kBlockK * 2;            // activations
@@ -70,7 +72,7 @@ template <int MT>
 __global__ void __launch_bounds__(kThreads)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __half* __restrict__ scales, __half* __restrict__ y, float* __restrict__ partial, int M, int N,
-                 int K, int group, int kblocks_per_split, unsigned int* status) {
+                 int K, int group, int kblocks_per_split, unsigned int* status, unsigned long long* trace) {
   using L = Layout<MT>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -95,7 +97,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&loaded[s], 1);
-      mbar_init(&a_ready[s], 4);
+      mbar_init(&a_ready[s], kDequantWarps);
       mbar_init(&stage_free[s], 1);
     }
     mbar_init(acc_done, 1);
@@ -111,6 +113,11 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool dead_on_arrival = *abort_word != 0;
+  // optional timeline of CTA (0,0,0) for tuning: 8 clock stamps per K block
+  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int i, int k) {
+    if (tracing && i < 64) trace[i * 8 + k] = clock64();
+  };
 
   if (dead_on_arrival) {
     // fall through to the teardown
@@ -121,6 +128,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % S;
         if (!mbar_wait(&stage_free[s], ((uint32_t)(i / S) & 1u) ^ 1u, ctx, kWaitFree)) break;
+        stamp(i, 0);
         mbar_arrive_expect_tx(&loaded[s], L::kP + L::kX);
         uint8_t* st = smem + s * L::kStage;
         const int kb = kb_begin + i;
@@ -135,6 +143,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int s = i % S;
         const uint32_t ph = (uint32_t)(i / S) & 1u;
         if (!mbar_wait(&a_ready[s], ph, ctx, kWaitAReady)) break;  // implies loaded[s]: the dequant warps waited on it
+        stamp(i, 4);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * L::kStage);
         const uint32_t b_addr = a_addr + L::kA + L::kP;
@@ -143,71 +152,115 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           mma_ss(tmem_base, smem_desc_sw128(a_addr + kk * 32, 16, 1024), smem_desc_sw128(b_addr + kk * 32, 16, 1024),
                  idesc, (i > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&stage_free[s]);
+        stamp(i, 5);
       }
       tc_commit(acc_done);
     }
   } else {
-    // ---------------------------------------------------------------- dequantise (thread = weight row)
-    const int r = threadIdx.x;
+    // ---------------------------------------------------------------- dequantise (two threads per weight row)
+    const int r = threadIdx.x & 127;   // weight row inside the tile; a warp covers 32 consecutive rows
+    const int half = threadIdx.x >> 7; // which four of the eight packed words of a K block
     const int row = n0 + r;
     const int groups = K / group;
     const __half* srow = scales + (size_t)min(row, N - 1) * groups;
     bool ok = true;
+    // The group scale of a K block comes from global memory (L2 latency of several hundred clocks): it is
+    // fetched two K blocks ahead so that the load never sits on the critical path of a pipeline stage.
+    __half sc_ring[3];
+    sc_ring[0] = srow[(kb_begin * kBlockK) / group];
+    sc_ring[1] = srow[(min(kb_begin + 1, kb_end - 1) * kBlockK) / group];
     for (int i = 0; i < n_kb; ++i) {
       const int s = i % S;
       const uint32_t ph = (uint32_t)(i / S) & 1u;
-      const int kb = kb_begin + i;
-      const __half sc = srow[(kb * kBlockK) / group];
+      sc_ring[2] = srow[(min(kb_begin + i + 2, kb_end - 1) * kBlockK) / group];
+      const __half sc = sc_ring[0];
+      sc_ring[0] = sc_ring[1];
+      sc_ring[1] = sc_ring[2];
       ok = __all_sync(0xffffffffu, mbar_wait(&loaded[s], ph, ctx, kWaitLoaded));
       if (!ok) break;
+      if (threadIdx.x == 0) stamp(i, 1);
       uint8_t* st = smem + s * L::kStage;
-      const uint4* pw = reinterpret_cast<const uint4*>(st + L::kA + r * 32);
-      const uint4 w0 = pw[0], w1 = pw[1];
+      const uint4 w = *reinterpret_cast<const uint4*>(st + L::kA + r * 32 + half * 16);
       const __half2 s2 = __half2half2(sc);
       uint8_t* arow = st + r * 128;
-      const int x = r & 7;
-      *reinterpret_cast<uint4*>(arow + ((0 ^ x) << 4)) = dequant8(w0.x, s2);
-      *reinterpret_cast<uint4*>(arow + ((1 ^ x) << 4)) = dequant8(w0.y, s2);
-      *reinterpret_cast<uint4*>(arow + ((2 ^ x) << 4)) = dequant8(w0.z, s2);
-      *reinterpret_cast<uint4*>(arow + ((3 ^ x) << 4)) = dequant8(w0.w, s2);
-      *reinterpret_cast<uint4*>(arow + ((4 ^ x) << 4)) = dequant8(w1.x, s2);
-      *reinterpret_cast<uint4*>(arow + ((5 ^ x) << 4)) = dequant8(w1.y, s2);
-      *reinterpret_cast<uint4*>(arow + ((6 ^ x) << 4)) = dequant8(w1.z, s2);
-      *reinterpret_cast<uint4*>(arow + ((7 ^ x) << 4)) = dequant8(w1.w, s2);
+      const int x = r & 7, c = half * 4;
+      *reinterpret_cast<uint4*>(arow + (((c + 0) ^ x) << 4)) = dequant8(w.x, s2);
+      *reinterpret_cast<uint4*>(arow + (((c + 1) ^ x) << 4)) = dequant8(w.y, s2);
+      *reinterpret_cast<uint4*>(arow + (((c + 2) ^ x) << 4)) = dequant8(w.z, s2);
+      *reinterpret_cast<uint4*>(arow + (((c + 3) ^ x) << 4)) = dequant8(w.w, s2);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to tcgen05.mma
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_ready[s]);
+      if (threadIdx.x == 0) stamp(i, 2);
     }
     // ---------------------------------------------------------------- epilogue
+    // TMEM lane = weight row n, column = batch row m, but y is [M, N]: going straight to global memory
+    // would be 2-byte stores with a stride of N (measured: 60 % of the kernel time).  Each warpgroup
+    // (warps 0-3 / 4-7, which own alternate 32-column chunks) transposes its chunk through a shared
+    // memory tile [32 m][128 n] and writes rows of 128 outputs with 16-byte stores.
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, ctx, kWaitAcc));
+    if (threadIdx.x == 0) stamp(63, 6);
     if (ok) {
       tc_fence_after_sync();
-      const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
-      const bool row_ok = row < N;
+      const uint32_t lane_bits = (uint32_t)((warp & 3) * 32) << 16;
+      const int wg = warp >> 2;                    // 0 or 1
+      uint8_t* tile = smem + wg * L::kStage;       // every stage is free once acc_done has completed
+      const bool f32 = splits > 1;
+      const int n_valid = min(kTileN, N - n0);     // columns of this tile that exist
+      constexpr int kCols = MT >= 32 ? 32 : MT;
+      constexpr int kChunks = MT >= 32 ? MT / 32 : 1;
+#pragma unroll 1
+      for (int ch = wg; ch < kChunks; ch += 2) {
+        const int c0 = ch * 32;
+        if (m0 + c0 >= M) break;  // uniform per warpgroup: batch rows that do not exist
+        uint32_t acc[32];
+        if constexpr (MT >= 32) {
+          tmem_ld_x32(tmem_base + lane_bits + c0, acc);
+        } else {
+          tmem_ld_x16(tmem_base + lane_bits + c0, acc);
+        }
+        tmem_wait_ld();
+        if (f32) {
 #pragma unroll
-      for (int c0 = 0; c0 < MT; c0 += 32) {
-        if (m0 + c0 < M) {  // uniform: skip batch columns that do not exist
-          uint32_t acc[32];
-          if constexpr (MT >= 32) {
-            tmem_ld_x32(tmem_base + lane_bits + c0, acc);
-          } else {
-            tmem_ld_x16(tmem_base + lane_bits + c0, acc);
-          }
-          tmem_wait_ld();
-          constexpr int kCols = MT >= 32 ? 32 : MT;
+          for (int c = 0; c < kCols; ++c) reinterpret_cast<float*>(tile)[c * kTileN + r] = __uint_as_float(acc[c]);
+        } else {
 #pragma unroll
-          for (int c = 0; c < kCols; ++c) {
-            const int m = m0 + c0 + c;
-            if (row_ok && m < M) {
-              if (splits == 1) y[(size_t)m * N + row] = __float2half_rn(__uint_as_float(acc[c]));
-              else partial[((size_t)split * M + m) * N + row] = __uint_as_float(acc[c]);
+          for (int c = 0; c < kCols; ++c)
+            reinterpret_cast<__half*>(tile)[c * kTileN + r] = __float2half_rn(__uint_as_float(acc[c]));
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+        const int m_hi = min(kCols, M - (m0 + c0));  // batch rows of this chunk that exist
+        if (f32) {
+          float* dst = partial + ((size_t)split * M + m0 + c0) * N + n0;
+          if ((N & 3) == 0) {
+            for (int idx = r; idx < m_hi * 32; idx += 128) {
+              const int ml = idx >> 5, seg = idx & 31;
+              if (seg * 4 < n_valid)
+                *reinterpret_cast<uint4*>(dst + (size_t)ml * N + seg * 4) = reinterpret_cast<const uint4*>(tile)[ml * 32 + seg];
             }
+          } else {
+            for (int ml = 0; ml < m_hi; ++ml)
+              if (r < n_valid) dst[(size_t)ml * N + r] = reinterpret_cast<const float*>(tile)[ml * kTileN + r];
+          }
+        } else {
+          __half* dst = y + (size_t)(m0 + c0) * N + n0;
+          if ((N & 7) == 0) {
+            for (int idx = r; idx < m_hi * 16; idx += 128) {
+              const int ml = idx >> 4, seg = idx & 15;
+              if (seg * 8 < n_valid)
+                *reinterpret_cast<uint4*>(dst + (size_t)ml * N + seg * 8) = reinterpret_cast<const uint4*>(tile)[ml * 16 + seg];
+            }
+          } else {
+            for (int ml = 0; ml < m_hi; ++ml)
+              if (r < n_valid) dst[(size_t)ml * N + r] = reinterpret_cast<const __half*>(tile)[ml * kTileN + r];
           }
         }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");  // tile is reused by the next chunk
       }
     }
   }
 
+  if (threadIdx.x == 0) stamp(63, 7);
   if (!dead_on_arrival && *abort_word != 0) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -229,6 +282,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     y[i] = __float2half_rn(acc);
   }
 }
+
+unsigned long long* g_trace = nullptr;  // tuning aid, set through kfb_debug_set_gemm_trace
 
 struct Plan {
   int mt, m_tiles, n_tiles, splits, kblocks_per_split;
@@ -264,7 +319,7 @@ int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const vo
   }
   const dim3 grid(p.n_tiles, p.m_tiles, p.splits);
   kernel<<<grid, kThreads, L::kAlloc, stream>>>(tw, tx, (const __half*)scales, (__half*)y, partial, M, N, K, group,
-                                               p.kblocks_per_split, status);
+                                               p.kblocks_per_split, status, g_trace);
   KFB_LAUNCH_CHECK("int4_gemm_kernel");
   if (p.splits > 1) {
     const long long elems = (long long)M * N;
@@ -323,4 +378,9 @@ extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scal
     case 128: return gemm::launch<128>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
     default: return gemm::launch<256>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
   }
+}
+
+// Tuning aid (not part of the public header): device buffer of 64 x 8 clock stamps written by CTA (0,0,0).
+extern "C" void kfb_debug_set_gemm_trace(void* device_buffer) {
+  kfb::gemm::g_trace = static_cast<unsigned long long*>(device_buffer);
 }

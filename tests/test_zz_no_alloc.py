@@ -64,10 +64,10 @@ def test_noalloc_matches_workspace_entry_twice(b, h, hk, nk, d):
 
 
 def test_noalloc_rejects_sizes_beyond_the_array():
-    # 294 (batch, kv head) groups at D = 128, two splits each: 588 partials of 8320 bytes = 4.9 MB > the 4 MiB
+    # 128 (batch, kv head) groups split 10 ways at D = 64: 1280 partials of 4224 bytes = 5.4 MB > the 4 MiB
     # array.  The refusal must come before any launch.
     lib = _capi.lib()
-    b, h, hk, nk, d = 147, 32, 2, 8192, 128  # 294 groups < 2 * SMs -> 2 splits, 2 chunks of 16 heads each
+    b, h, hk, nk, d = 32, 32, 4, 16384, 64
     need = lib.kfb_flash_attn_ws_bytes(b, h, hk, 1, nk, d)
     if need <= (4 << 20):
         pytest.skip(f"plan needs only {need} bytes on this device")
