@@ -124,6 +124,28 @@ int kfb_flash_attn_decode_kvlen(const void* q, const void* k, const void* v, voi
                                 const int64_t* kv_strides, const int32_t* kv_len_dev,
                                 void* ws, size_t ws_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Fused element-wise steps of a Llama-architecture decode step (fp16).  The reference leaves these to
+ * Hugging Face / torch ops (it replaces only the linears and the attention function,
+ * kernelforge/modules.py:51-115); they are here because a batch-1 decode step is launch-bound.
+ * ------------------------------------------------------------------------------------- */
+
+/* s = x + residual (skipped when residual is NULL), written to sum_out when not NULL;
+ * y = fp16(fp16(s * rsqrt(mean(s^2) + eps)) * weight).  x, residual, y, sum_out: [rows, hidden]. */
+int kfb_add_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* sum_out,
+                    int rows, int hidden, float eps, void* stream);
+
+/* Rotary embedding + KV-cache write of one decode position.  qkv: [B, (H + 2*Hk) * D] (q heads, then k
+ * heads, then v heads, as produced by one fused q/k/v linear); cos_table, sin_table: fp32 [Lmax, D]
+ * (rotate-half convention); pos_dev: device int64, the position being written.  q_out: [B, H, D];
+ * k_cache, v_cache: [B, Hk, Lmax, D], row `pos` is written. */
+int kfb_rope_kv_write(const void* qkv, const void* cos_table, const void* sin_table, const void* pos_dev,
+                      void* q_out, void* k_cache, void* v_cache, int B, int H, int Hk, int D, int Lmax,
+                      void* stream);
+
+/* out[r, c] = fp16(fp16(silu(gate_up[r, c])) * gate_up[r, inter + c]); gate_up: [rows, 2 * inter]. */
+int kfb_silu_mul(const void* gate_up, void* out, int rows, int inter, void* stream);
+
 /* Decode attention (Nq == 1, one query per head at the last cache position) for callers that
  * cannot allocate device memory: a server whose memory pool already owns the whole GPU, code
  * between cudaStreamBeginCapture and EndCapture (cudaMalloc is not allowed there), a host runtime

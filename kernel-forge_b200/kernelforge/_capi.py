@@ -35,6 +35,10 @@ _SIGNATURES = {
     "kfb_flash_attn_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "kfb_flash_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_float, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
+    "kfb_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "kfb_rope_kv_write": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_void_p]),
+    "kfb_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "kfb_flash_attn_decode_kvlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_float, ctypes.POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
     "kfb_flash_attn_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -7,8 +7,11 @@ Here the step runs `ops.flash_attn_decode`, which reads the valid cache length f
 `ops.int4_linear` for the seven decoder linears of every layer; token ids, position and KV length all live
 on the device, so a step is a pure graph replay with no host synchronisation.
 
-Everything that is not one of the two hot paths (embedding, RMSNorm, RoPE, SiLU * up, residual adds, the
-fp16 lm_head, argmax) is plain torch, exactly as in the reference, where those stay Hugging Face / torch ops.
+Prefill uses torch for everything that is not one of the two hot paths (embedding, RMSNorm, RoPE, SiLU * up,
+residual adds, lm_head), as the reference does.  The decode step is launch-bound at batch 1, so there those
+element-wise steps run as three fused kernels (ops.add_rmsnorm, ops.rope_kv_write, ops.silu_mul) and q/k/v and
+gate/up are stored as one quantised matrix each: 11 kernels per layer instead of ~48 (2.39 -> 0.85 ms per step
+on the TinyLlama-1.1B architecture).  Embedding lookup, the fp16 lm_head and argmax stay torch.
 """
 
 from __future__ import annotations
@@ -60,9 +63,14 @@ class LlamaInt4Decoder:
         self.final_norm = f16(weights["final_norm"])
         self.layers = []
         for lw in weights["layers"]:
+            # q/k/v and gate/up share their input, so they are stored as ONE quantised matrix each (rows
+            # concatenated: groups run along K, so this is bit-identical to quantising them separately)
             self.layers.append({
                 "in_norm": f16(lw["in_norm"]), "post_norm": f16(lw["post_norm"]),
-                **{n: _Int4(f16(lw[n]), group) for n in ("q", "k", "v", "o", "gate", "up", "down")},
+                "qkv": _Int4(torch.cat([f16(lw["q"]), f16(lw["k"]), f16(lw["v"])], 0), group),
+                "o": _Int4(f16(lw["o"]), group),
+                "gate_up": _Int4(torch.cat([f16(lw["gate"]), f16(lw["up"])], 0), group),
+                "down": _Int4(f16(lw["down"]), group),
             })
         self.k_cache = torch.zeros(s.layers, batch, s.kv_heads, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
@@ -127,7 +135,9 @@ class LlamaInt4Decoder:
 
     def _mlp(self, L, x):
         h = self._rms(x, L["post_norm"])
-        return x + L["down"](torch.nn.functional.silu(L["gate"](h)) * L["up"](h))
+        gu = L["gate_up"](h)
+        inter = self.s.intermediate
+        return x + L["down"](torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:])
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -140,9 +150,11 @@ class LlamaInt4Decoder:
         cos, sin = self.cos[:t], self.sin[:t]
         for li, L in enumerate(self.layers):
             h = self._rms(x, L["in_norm"])
-            q = L["q"](h).view(b, t, s.heads, s.head_dim).transpose(1, 2)
-            k = L["k"](h).view(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
-            v = L["v"](h).view(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
+            qkv = L["qkv"](h)
+            nq, nkv = s.heads * s.head_dim, s.kv_heads * s.head_dim
+            q = qkv[..., :nq].reshape(b, t, s.heads, s.head_dim).transpose(1, 2)
+            k = qkv[..., nq:nq + nkv].reshape(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
+            v = qkv[..., nq + nkv:].reshape(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
             self.k_cache[li, :, :, :t] = k
             self.v_cache[li, :, :, :t] = v
@@ -158,21 +170,21 @@ class LlamaInt4Decoder:
     # ------------------------------------------------------------------ one decode step (graph body)
     @torch.no_grad()
     def _step(self):
+        """One decode step: 11 kernels per layer (norm, qkv, rope + cache write, attention x2, o, add + norm,
+        gate_up, silu * up, down; the last residual add is fused into the next layer's norm)."""
         s, b = self.s, self.b
-        x = self.embed[self.tok].unsqueeze(1)                      # [B, 1, hidden]
-        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)  # [1, D]
+        x = self.embed[self.tok]                                   # [B, hidden]
+        res = None                                                 # pending residual branch output
         for li, L in enumerate(self.layers):
-            h = self._rms(x, L["in_norm"])
-            q = L["q"](h).view(b, 1, s.heads, s.head_dim).transpose(1, 2)
-            k = L["k"](h).view(b, 1, s.kv_heads, s.head_dim).transpose(1, 2)
-            v = L["v"](h).view(b, 1, s.kv_heads, s.head_dim).transpose(1, 2)
-            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
-            self.k_cache[li].index_copy_(2, self.pos, k)
-            self.v_cache[li].index_copy_(2, self.pos, v)
-            a = ops.flash_attn_decode(q.contiguous(), self.k_cache[li], self.v_cache[li], self.kv_len)
-            x = x + L["o"](a.transpose(1, 2).reshape(b, 1, s.heads * s.head_dim))
-            x = self._mlp(L, x)
-        logits = (self._rms(x, self.final_norm) @ self.lm_head.T)[:, 0]
+            h, x = ops.add_rmsnorm(x, L["in_norm"], s.rms_eps, res)
+            qkv = L["qkv"](h)
+            q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], s.heads)
+            a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len)
+            o = L["o"](a.view(b, s.heads * s.head_dim))
+            h, x = ops.add_rmsnorm(x, L["post_norm"], s.rms_eps, o)
+            res = L["down"](ops.silu_mul(L["gate_up"](h)))
+        h, x = ops.add_rmsnorm(x, self.final_norm, s.rms_eps, res)
+        logits = h @ self.lm_head.T
         self.step_logits.copy_(logits)
         self.tok.copy_(logits.float().argmax(-1))
         self.pos.add_(1)

@@ -287,3 +287,43 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
     if bias is not None:
         y = y + bias
     return y.reshape(*lead, packed.shape[0])
+
+
+# ---------------------------------------------------------------------------
+# Fused element-wise steps of a decode step (not part of the reference's operator surface, which leaves
+# them to torch; used by kernelforge.llama_decode)
+# ---------------------------------------------------------------------------
+
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """(y, s): s = x + residual (x itself when residual is None), y = RMSNorm(s) * weight.  fp16 [rows, hidden]."""
+    rows, hidden = x.shape
+    y = torch.empty_like(x)
+    s = torch.empty_like(x) if residual is not None else x
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_add_rmsnorm(x.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                                weight.data_ptr(), y.data_ptr(),
+                                                s.data_ptr() if residual is not None else None, rows, hidden, eps,
+                                                _capi.stream_ptr(x.device)))
+    return y, s
+
+
+def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, heads: int) -> torch.Tensor:
+    """Rotates q and k of one decode position, writes k and v into row `pos` of the caches, returns q [B, H, 1, D]."""
+    b = qkv.shape[0]
+    hk, lmax, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    q = torch.empty(b, heads, 1, d, dtype=torch.float16, device=qkv.device)
+    with _capi.on_device(qkv.device):
+        _capi.check(_capi.lib().kfb_rope_kv_write(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(), q.data_ptr(),
+                                                  k_cache.data_ptr(), v_cache.data_ptr(), b, heads, hk, d, lmax,
+                                                  _capi.stream_ptr(qkv.device)))
+    return q
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for gate_up = [rows, 2 * inter] (gate | up)."""
+    rows, two = gate_up.shape
+    out = torch.empty(rows, two // 2, dtype=torch.float16, device=gate_up.device)
+    with _capi.on_device(gate_up.device):
+        _capi.check(_capi.lib().kfb_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two // 2, _capi.stream_ptr(gate_up.device)))
+    return out

@@ -1,0 +1,60 @@
+"""The three fused element-wise kernels of the decode step against their torch formulations (fp16 models)."""
+
+import pytest
+import torch
+
+from kernelforge import ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 2048), (32, 2048), (3, 1536), (2, 8192), (5, 256)])
+def test_add_rmsnorm(rows, hidden):
+    g = torch.Generator().manual_seed(hidden + rows)
+    x = torch.randn(rows, hidden, generator=g).half().cuda()
+    r = torch.randn(rows, hidden, generator=g).half().cuda()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).half().cuda()
+    for res in (None, r):
+        y, s = ops.add_rmsnorm(x, w, 1e-5, res)
+        s_ref = x if res is None else x + res
+        sf = s_ref.float()
+        y_ref = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
+        assert torch.equal(s, s_ref)
+        assert (y.float() - y_ref.float()).abs().max().item() <= 2e-3 * y_ref.float().abs().max().item()
+
+
+@pytest.mark.parametrize("b,h,hk,d", [(1, 32, 4, 64), (3, 8, 2, 128)])
+def test_rope_kv_write(b, h, hk, d):
+    g = torch.Generator().manual_seed(b + d)
+    lmax, pos = 40, 17
+    qkv = torch.randn(b, (h + 2 * hk) * d, generator=g).half().cuda()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    ang = torch.outer(torch.arange(lmax, dtype=torch.float32), inv)
+    ang = torch.cat([ang, ang], -1)
+    cos, sin = ang.cos().cuda(), ang.sin().cuda()
+    kc = torch.zeros(b, hk, lmax, d, dtype=torch.float16).cuda()
+    vc = torch.zeros_like(kc)
+    q = ops.rope_kv_write(qkv, cos, sin, torch.tensor([pos]).cuda(), kc, vc, h)
+
+    def rope(t):
+        tf = t.float()
+        rot = torch.cat([-tf[..., d // 2:], tf[..., :d // 2]], -1)
+        return (tf * cos[pos] + rot * sin[pos]).half()
+
+    qr = qkv[:, :h * d].view(b, h, d)
+    kr = qkv[:, h * d:(h + hk) * d].view(b, hk, d)
+    vr = qkv[:, (h + hk) * d:].view(b, hk, d)
+    assert (q[:, :, 0].float() - rope(qr).float()).abs().max().item() <= 2e-3
+    assert (kc[:, :, pos].float() - rope(kr).float()).abs().max().item() <= 2e-3
+    assert torch.equal(vc[:, :, pos], vr)
+    untouched = torch.ones(lmax, dtype=torch.bool)
+    untouched[pos] = False
+    assert kc[:, :, untouched].abs().max().item() == 0 and vc[:, :, untouched].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 5632), (32, 5632), (4, 8960)])
+def test_silu_mul(rows, inter):
+    gu = torch.randn(rows, 2 * inter, generator=torch.Generator().manual_seed(rows)).half().cuda()
+    out = ops.silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+    assert (out.float() - ref.float()).abs().max().item() <= 4e-3 * ref.float().abs().max().item()
