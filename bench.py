@@ -322,8 +322,17 @@ def bench_sharded_linear(args, world, device, m=128, n=8960, k=1536, group=128) 
     lin = kp.ShardedInt4Linear.from_full(qw)
     x = torch.randn(m, k, generator=g).half().to(device)
     ms = time_steps(lambda i: lin(x), args.steps, args.warmup, world)
-    return {"us_per_call": 1e3 * ms / args.steps, "tflops": 2.0 * m * n * k * args.steps / (ms * 1e-3) / 1e12,
-            "rows_per_rank": n // world, "collective": "nccl all_gather_into_tensor"}
+    out = {"us_per_call": 1e3 * ms / args.steps, "tflops": 2.0 * m * n * k * args.steps / (ms * 1e-3) / 1e12,
+           "rows_per_rank": n // world, "collective": "nccl all_gather_into_tensor"}
+    try:
+        fused = kp.FusedShardedInt4Linear.from_full(qw, max_m=m)
+        ms_f = time_steps(lambda i: fused(x), args.steps, args.warmup, world)
+        out["fused_peer_store"] = {"us_per_call": 1e3 * ms_f / args.steps,
+                                   "tflops": 2.0 * m * n * k * args.steps / (ms_f * 1e-3) / 1e12,
+                                   "how": "GEMM epilogue stores its tile into every rank's symmetric buffer"}
+    except Exception as exc:  # report, never hide
+        out["fused_peer_store"] = {"error": repr(exc)[:300]}
+    return out
 
 
 # ----------------------------------------------------------------------------------------------

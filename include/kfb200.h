@@ -96,6 +96,19 @@ size_t kfb_int4_gemm_ws_bytes(int M, int N, int K, int group);
 int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y,
                   int M, int N, int K, int group, void* ws, size_t ws_bytes, void* stream);
 
+/* int4_gemm for an output-feature-sharded linear, fused with the all-gather that follows it.
+ * The reference is single-GPU; this entry point has no counterpart there.
+ * This rank holds N_local rows of packed / scales and computes y[:, col0 : col0 + N_local]; the epilogue
+ * stores that block into ALL n_buffers output buffers (y_all[i]: fp16 [M, ld], the peer-mapped address of
+ * GPU i's full result, this GPU's own buffer included) with plain peer stores over NVLink, tile by tile
+ * as the tiles finish, so no separate all-gather kernel runs.  Stores only: nothing is loaded from a
+ * peer.  The caller orders the call against the peers (a barrier on the stream after the call, before
+ * anyone reads y; and no peer may still be reading a buffer that this call overwrites).
+ * Workspace: kfb_int4_gemm_ws_bytes(M, N_local, K, group). */
+int kfb_int4_gemm_allgather(const void* x, const void* packed, const void* scales, void* const* y_all,
+                            int n_buffers, int M, int N_local, int K, int group, int ld, int col0,
+                            void* ws, size_t ws_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Fused attention forward  O = softmax(scale * Q K^T + causal mask) V
  * (kernelforge/ops.py:258-274 -> csrc/attention/attn_v4.cu:10-51, kernel attn_v4_kernel.cuh:43-214).

@@ -34,6 +34,19 @@ constexpr int kMmaWarp = kDequantWarps + 1;
 
 enum WaitCode : uint32_t { kWaitFree = 0x301, kWaitLoaded, kWaitAReady, kWaitAcc };
 
+// Where the fp16 result goes.  Plain call: one buffer [M, N].  Output-feature-sharded call (fused
+// all-gather): `count` buffers [M, ld], one per GPU of the group (peer-mapped device pointers, this
+// GPU's own buffer included); this rank's N columns are stored at column `col0` of EVERY buffer with
+// plain peer stores from the epilogue, so the gather overlaps the computation tile by tile and no
+// separate collective kernel runs.  (Stores only: no load ever targets a peer's memory.)
+constexpr int kMaxPeers = 8;
+struct OutSpec {
+  __half* y[kMaxPeers];
+  int count;
+  int ld;    // row stride of every buffer, in elements
+  int col0;  // first column this rank writes
+};
+
 template <int MT>
 struct Layout {
   // TMA latency (~1400 clocks) + dequantisation + MMA of one K block must be covered by the other stages
@@ -71,7 +84,7 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s2) {
 template <int MT>
 __global__ void __launch_bounds__(kThreads)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                 const __half* __restrict__ scales, __half* __restrict__ y, float* __restrict__ partial, int M, int N,
+                 const __half* __restrict__ scales, const OutSpec out, float* __restrict__ partial, int M, int N,
                  int K, int group, int kblocks_per_split, unsigned int* status, unsigned long long* trace) {
   using L = Layout<MT>;
   constexpr int S = L::kStages;
@@ -243,16 +256,22 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
               if (r < n_valid) dst[(size_t)ml * N + r] = reinterpret_cast<const float*>(tile)[ml * kTileN + r];
           }
         } else {
-          __half* dst = y + (size_t)(m0 + c0) * N + n0;
-          if ((N & 7) == 0) {
-            for (int idx = r; idx < m_hi * 16; idx += 128) {
-              const int ml = idx >> 4, seg = idx & 15;
-              if (seg * 8 < n_valid)
-                *reinterpret_cast<uint4*>(dst + (size_t)ml * N + seg * 8) = reinterpret_cast<const uint4*>(tile)[ml * 16 + seg];
+          const bool vec = ((out.ld | out.col0) & 7) == 0;  // every row segment starts on a 16-byte boundary
+          for (int p = 0; p < out.count; ++p) {
+            __half* dst = out.y[p] + (size_t)(m0 + c0) * out.ld + out.col0 + n0;
+            if (vec) {
+              for (int idx = r; idx < m_hi * 16; idx += 128) {
+                const int ml = idx >> 4, seg = idx & 15;
+                if (seg * 8 + 8 <= n_valid) {
+                  *reinterpret_cast<uint4*>(dst + (size_t)ml * out.ld + seg * 8) = reinterpret_cast<const uint4*>(tile)[ml * 16 + seg];
+                } else {
+                  for (int e = seg * 8; e < n_valid; ++e) dst[(size_t)ml * out.ld + e] = reinterpret_cast<const __half*>(tile)[ml * kTileN + e];
+                }
+              }
+            } else {
+              for (int ml = 0; ml < m_hi; ++ml)
+                if (r < n_valid) dst[(size_t)ml * out.ld + r] = reinterpret_cast<const __half*>(tile)[ml * kTileN + r];
             }
-          } else {
-            for (int ml = 0; ml < m_hi; ++ml)
-              if (r < n_valid) dst[(size_t)ml * N + r] = reinterpret_cast<const __half*>(tile)[ml * kTileN + r];
           }
         }
         asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");  // tile is reused by the next chunk
@@ -273,13 +292,17 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   }
 }
 
-// y[i] = fp16(sum over splits, in split order, of partial[s][i])
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ y,
-                                                            long long elems, int splits) {
+// y[m, col0 + n] = fp16(sum over splits, in split order, of partial[s][m][n]), in every output buffer
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const OutSpec out,
+                                                            int M, int N, int splits) {
+  const long long elems = (long long)M * N;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (long long)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * elems + i];
-    y[i] = __float2half_rn(acc);
+    const long long m = i / N;
+    const int n = (int)(i - m * N);
+    const __half v = __float2half_rn(acc);
+    for (int p = 0; p < out.count; ++p) out.y[p][m * out.ld + out.col0 + n] = v;
   }
 }
 
@@ -306,7 +329,7 @@ Plan make_plan(int M, int N, int K) {
 }
 
 template <int MT>
-int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const void* scales, void* y, float* partial,
+int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const void* scales, const OutSpec& out, float* partial,
            int M, int N, int K, int group, unsigned int* status, cudaStream_t stream) {
   using L = Layout<MT>;
   auto kernel = int4_gemm_kernel<MT>;
@@ -318,7 +341,7 @@ int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const vo
     configured[dev] = true;
   }
   const dim3 grid(p.n_tiles, p.m_tiles, p.splits);
-  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tw, tx, (const __half*)scales, (__half*)y, partial, M, N, K, group,
+  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tw, tx, (const __half*)scales, out, partial, M, N, K, group,
                                                p.kblocks_per_split, status, g_trace);
   KFB_LAUNCH_CHECK("int4_gemm_kernel");
   if (p.splits > 1) {
@@ -326,7 +349,7 @@ int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const vo
     long long blocks = (elems + 255) / 256;
     const long long cap = (long long)sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    splitk_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(partial, (__half*)y, elems, p.splits);
+    splitk_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(partial, out, M, N, p.splits);
     KFB_LAUNCH_CHECK("splitk_reduce_kernel");
   }
   return KFB_OK;
@@ -344,13 +367,17 @@ extern "C" size_t kfb_int4_gemm_ws_bytes(int M, int N, int K, int group) {
   return p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;
 }
 
-extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
-                             int group, void* ws, size_t ws_bytes, void* stream) {
+namespace {
+
+int gemm_common(const void* x, const void* packed, const void* scales, const gemm::OutSpec& out, int M, int N, int K,
+                int group, void* ws, size_t ws_bytes, void* stream) {
   if (int rc = require_sm100()) return rc;
   if (M < 1) return fail(KFB_ERR_INVALID, "int4_gemm needs M >= 1, got M=%d", M);
   if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
   if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
-  if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!x || !packed || !scales) return fail(KFB_ERR_INVALID, "null pointer");
+  for (int i = 0; i < out.count; ++i)
+    if (!out.y[i] || !aligned16(out.y[i])) return fail(KFB_ERR_ALIGNMENT, "output buffers must be non-null and 16-byte aligned");
   if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
   const gemm::Plan p = gemm::make_plan(M, N, K);
   const size_t need = p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;
@@ -372,12 +399,41 @@ extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scal
   cudaStream_t s = (cudaStream_t)stream;
   float* partial = static_cast<float*>(ws);
   switch (p.mt) {
-    case 16: return gemm::launch<16>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
-    case 32: return gemm::launch<32>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
-    case 64: return gemm::launch<64>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
-    case 128: return gemm::launch<128>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
-    default: return gemm::launch<256>(p, tw, tx, scales, y, partial, M, N, K, group, status, s);
+    case 16: return gemm::launch<16>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 32: return gemm::launch<32>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 64: return gemm::launch<64>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 128: return gemm::launch<128>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    default: return gemm::launch<256>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
   }
+}
+
+}  // namespace
+
+extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                             int group, void* ws, size_t ws_bytes, void* stream) {
+  gemm::OutSpec out = {};
+  out.y[0] = static_cast<__half*>(y);
+  out.count = 1;
+  out.ld = N;
+  out.col0 = 0;
+  if (!y) return fail(KFB_ERR_INVALID, "null pointer");
+  return gemm_common(x, packed, scales, out, M, N, K, group, ws, ws_bytes, stream);
+}
+
+extern "C" int kfb_int4_gemm_allgather(const void* x, const void* packed, const void* scales, void* const* y_all,
+                                       int n_buffers, int M, int N_local, int K, int group, int ld, int col0, void* ws,
+                                       size_t ws_bytes, void* stream) {
+  if (n_buffers < 1 || n_buffers > gemm::kMaxPeers)
+    return fail(KFB_ERR_INVALID, "n_buffers must be in [1, %d], got %d", gemm::kMaxPeers, n_buffers);
+  if (!y_all) return fail(KFB_ERR_INVALID, "null pointer");
+  if (col0 < 0 || ld < col0 + N_local)
+    return fail(KFB_ERR_INVALID, "columns [%d, %d) do not fit in a row of %d", col0, col0 + N_local, ld);
+  gemm::OutSpec out = {};
+  for (int i = 0; i < n_buffers; ++i) out.y[i] = static_cast<__half*>(y_all[i]);
+  out.count = n_buffers;
+  out.ld = ld;
+  out.col0 = col0;
+  return gemm_common(x, packed, scales, out, M, N_local, K, group, ws, ws_bytes, stream);
 }
 
 // Tuning aid (not part of the public header): device buffer of 64 x 8 clock stamps written by CTA (0,0,0).

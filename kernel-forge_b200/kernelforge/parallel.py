@@ -124,3 +124,70 @@ def gather_columns(y_local: torch.Tensor, bounds: list[tuple[int, int]], group=N
     if all(w == wmax for w in widths):
         return recv.permute(1, 0, 2).reshape(m, world * wmax)
     return torch.cat([recv[r, :, :w] for r, w in enumerate(widths)], dim=1)
+
+
+class FusedShardedInt4Linear(torch.nn.Module):
+    """Output-feature-parallel INT4 linear whose all-gather is fused into the GEMM epilogue.
+
+    Every rank owns two result buffers [max_m, N] in symmetric memory (torch.distributed._symmetric_memory:
+    each buffer is mapped into every process of the group).  `kfb_int4_gemm_allgather` stores this rank's
+    column block into the current buffer of EVERY rank with plain peer stores over NVLink while the tiles are
+    still being produced; one tiny all-reduce on the stream then orders the ranks (when it has passed, every
+    rank's kernel -- and with it every store into this rank's buffer -- has completed).  The two buffers
+    alternate, so a rank that runs ahead never overwrites a result a slower peer is still reading (it cannot
+    get two calls ahead: its next all-reduce needs the peer).  Only stores cross the link, never loads.
+    """
+
+    def __init__(self, qw_full_shape: tuple[int, int], local: kq.QuantizedWeight, max_m: int,
+                 bias: torch.Tensor | None = None, group: dist.ProcessGroup | None = None):
+        super().__init__()
+        import torch.distributed._symmetric_memory as symm
+        self.out_features, self.in_features = qw_full_shape
+        self.group_size = local.group_size
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.bounds = row_bounds(self.out_features, self.world)
+        self.max_m = max_m
+        self.register_buffer("packed", local.packed)
+        self.register_buffer("scales", local.scales)
+        self.register_buffer("bias", None if bias is None else bias.detach().half())
+        dev = local.packed.device
+        self._bufs, self._ptrs = [], []
+        for _ in range(2):
+            t = symm.empty(max_m, self.out_features, dtype=torch.float16, device=dev)
+            hdl = symm.rendezvous(t, self.group.group_name)
+            self._bufs.append(t)
+            self._ptrs.append([int(p) for p in hdl.buffer_ptrs])
+        self._flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._turn = 0
+
+    @classmethod
+    def from_full(cls, qw: kq.QuantizedWeight, max_m: int, bias=None, group=None) -> "FusedShardedInt4Linear":
+        g = group if group is not None else dist.group.WORLD
+        return cls(qw.shape, shard_quantized_weight(qw, dist.get_rank(g), dist.get_world_size(g)), max_m, bias, g)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        import ctypes
+        from . import _capi
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        m, k = x2.shape
+        if m > self.max_m:
+            raise ValueError(f"M={m} exceeds the symmetric buffers (max_m={self.max_m})")
+        ops._check_int4(x2, self.packed, self.scales, self.group_size)
+        lo, hi = self.bounds[self.rank]
+        turn = self._turn
+        self._turn ^= 1
+        lib = _capi.lib()
+        ws_bytes = lib.kfb_int4_gemm_ws_bytes(m, hi - lo, k, self.group_size)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x2.device)
+        ptrs = (ctypes.c_void_p * self.world)(*self._ptrs[turn])
+        with _capi.on_device(x2.device):
+            _capi.check(lib.kfb_int4_gemm_allgather(x2.data_ptr(), self.packed.data_ptr(), self.scales.data_ptr(), ptrs,
+                                                    self.world, m, hi - lo, k, self.group_size, self.out_features, lo,
+                                                    ws.data_ptr(), ws_bytes, _capi.stream_ptr(x2.device)))
+        dist.all_reduce(self._flag, group=self.group)  # stream-ordered rendezvous: every rank's stores have landed
+        y = self._bufs[turn][:m]
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, self.out_features)
