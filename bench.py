@@ -465,7 +465,8 @@ def main():
         sbest = max((gs[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gs.get(k, {})), default=None)
         also["int4_gemv_m1_stream_180224x2048"] = dict(gs, roofline={
             "bound": "hbm", "achieved": None if sbest is None else sbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": None if sbest is None else sbest / world / peaks["hbm_gbs"], "traffic": None,
+            "frac": None if sbest is None else sbest / world / peaks["hbm_gbs"],
+            "traffic": 193566720,  # ncu: 190.36 MB read + 3.20 MB written per launch (profiles/int4_gemv_M1_N180224_K2048.md)
             "note": "same kernel on 32 stacked copies of the 5632x2048 weight: the streaming regime of the GEMV"})
         if world > 1:
             also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
@@ -487,7 +488,10 @@ def main():
         "value": fa["tflops"], "ms_per_step": fa["ms_per_step"], "e2e": fa["e2e"], "gpu_launches": args.steps,
         "clocks": fa["clocks"],
         "roofline": {"bound": "tensor", "achieved": fa["tflops"] / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": fa["tflops"] / world / peaks["bf16_tflops"], "traffic": None,
+                     "frac": fa["tflops"] / world / peaks["bf16_tflops"],
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload from the ncu
+                     # capture summarised in profiles/attn_prefill_B2_H16_N2048_D64.md (q, k, v read once = 25.2 MB)
+                     "traffic": 25219840 if (not args.shape and not args.causal) else None,
                      "peak_source": f"{peak_kind} dense bf16 cuBLAS burst", "kernel": "attn_prefill_kernel<64,fp16>"},
         "also": also,
     })

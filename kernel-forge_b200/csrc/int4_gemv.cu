@@ -76,6 +76,20 @@ __device__ __forceinline__ float dot2_acc(uint32_t a, uint32_t b, float acc) {
   return acc;
 }
 
+// Same with the activation pair already split into two 16-bit registers (done once per chunk and
+// shared by all rows of the warp instead of once per row).
+__device__ __forceinline__ float dot2_acc_split(uint32_t a, unsigned short bl, unsigned short bh, float acc) {
+  asm("{\n\t"
+      ".reg .b16 al, ah;\n\t"
+      "mov.b32 {al, ah}, %1;\n\t"
+      "fma.rn.f32.f16 %0, al, %2, %0;\n\t"
+      "fma.rn.f32.f16 %0, ah, %3, %0;\n\t"
+      "}"
+      : "+f"(acc)
+      : "r"(a), "h"(bl), "h"(bh));
+  return acc;
+}
+
 // FP32 dot product of one unpacked 16-byte weight chunk (16 half2) with 32 activations.
 __device__ __forceinline__ float dot32(const uint32_t (&q)[16], const uint4 (&xv)[4]) {
   float p0 = 0.f, p1 = 0.f;  // two chains for ILP
@@ -149,17 +163,20 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
         // offsets are removed per 32-weight chunk with the class sums of x, shared by all R rows:
         //   sum q x = (sum_A (1024+u) x - 1032 SxA) + (sum_B (1024+16u) x / 16 - 72 SxB).
         uint4 xv[M][4];
+        unsigned short xl[M][16], xh[M][16];
         float sxa[M], sxb[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
           const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) asm("mov.b32 {%0, %1}, %2;" : "=h"(xl[m][i]), "=h"(xh[m][i]) : "r"(xs[i]));
           float a = 0.f, b = 0.f;
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
-            a = dot2_acc(0x3C003C00u, xs[i], a);      // half2(1, 1)
-            b = dot2_acc(0x3C003C00u, xs[i + 1], b);
+            a = dot2_acc_split(0x3C003C00u, xl[m][i], xh[m][i], a);      // half2(1, 1)
+            b = dot2_acc_split(0x3C003C00u, xl[m][i + 1], xh[m][i + 1], b);
           }
           sxa[m] = a * -1032.0f;
           sxb[m] = b * -72.0f;
@@ -169,16 +186,15 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
           const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
 #pragma unroll
           for (int m = 0; m < M; ++m) {
-            const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               constexpr uint32_t kMagic = 0x64006400u;
               const uint32_t w = wr[j], h = w >> 8;
-              pa = dot2_acc((w & 0x000F000Fu) | kMagic, xs[4 * j + 0], pa);
-              pb = dot2_acc((w & 0x00F000F0u) | kMagic, xs[4 * j + 1], pb);
-              pa = dot2_acc((h & 0x000F000Fu) | kMagic, xs[4 * j + 2], pa);
-              pb = dot2_acc((h & 0x00F000F0u) | kMagic, xs[4 * j + 3], pb);
+              pa = dot2_acc_split((w & 0x000F000Fu) | kMagic, xl[m][4 * j + 0], xh[m][4 * j + 0], pa);
+              pb = dot2_acc_split((w & 0x00F000F0u) | kMagic, xl[m][4 * j + 1], xh[m][4 * j + 1], pb);
+              pa = dot2_acc_split((h & 0x000F000Fu) | kMagic, xl[m][4 * j + 2], xh[m][4 * j + 2], pa);
+              pb = dot2_acc_split((h & 0x00F000F0u) | kMagic, xl[m][4 * j + 3], xh[m][4 * j + 3], pb);
             }
             acc[m][r] = fmaf(sc[r], (pa + sxa[m]) + fmaf(pb, 0.0625f, sxb[m]), acc[m][r]);
           }

@@ -209,7 +209,16 @@ def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool =
     Returns [B, H, Nq, D] in the input dtype. Inference only (no backward).
     """
     _check_attn(q, k, v, causal)
+    if _plain_eager(q):
+        return _attn_launch(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
     return _flash_attn_op(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
+
+
+def _plain_eager(t: torch.Tensor) -> bool:
+    """True for an ordinary tensor outside torch.compile / export tracing.  The torch.library op costs ~15 us of
+    dispatcher time per call, which is as long as a small kernel; it is only needed when the call is being
+    traced (fake tensors, dynamo), so plain eager calls -- CUDA-graph capture included -- go straight to the library."""
+    return type(t) is torch.Tensor and not torch.compiler.is_compiling()
 
 
 def flash_attn_kv_view(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
@@ -220,6 +229,8 @@ def flash_attn_kv_view(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal
     differ between k and v, or are not multiples of 8 elements, are copied first."""
     _check_attn(q, k, v, causal, strided_kv=True)
     if k.is_contiguous() and v.is_contiguous():
+        if _plain_eager(q):
+            return _attn_launch(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
         return _flash_attn_op(q, k, v, bool(causal), _resolve_scale(scale, q.shape[-1]))
     if k.stride() != v.stride() or k.stride(3) != 1 or any(s % 8 for s in k.stride()[:3]):
         return _flash_attn_op(q, k.contiguous(), v.contiguous(), bool(causal), _resolve_scale(scale, q.shape[-1]))
@@ -283,7 +294,10 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
     if not x2.is_contiguous():
         x2 = x2.contiguous()
     _check_int4(x2, packed, scales, group_size)
-    y = _int4_matmul_op(x2, packed, scales, int(group_size))
+    if _plain_eager(x2):
+        y = int4_matmul(x2, packed, scales, int(group_size))
+    else:
+        y = _int4_matmul_op(x2, packed, scales, int(group_size))
     if bias is not None:
         y = y + bias
     return y.reshape(*lead, packed.shape[0])
