@@ -19,6 +19,9 @@
 //     directly and the offsets are subtracted per chunk using sums of x shared by all rows.
 // K can be split across the warps of a CTA (fixed-order shared-memory reduce: deterministic).
 #include "common.cuh"
+#include "int4_gemv_mma.cuh"
+
+#include <cstdlib>
 
 namespace kfb {
 namespace gemv {
@@ -324,6 +327,14 @@ extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scal
   if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
   if (flags & ~1) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
   cudaStream_t s = (cudaStream_t)stream;
+  // Default: the mma.sync formulation (the CUDA-core kernel is issue-bound on B200, see int4_gemv_mma.cuh).
+  // KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel; it is also used for the programmatic-dependent-
+  // launch flag, which only that kernel implements, and when the class sums would not fit in shared memory.
+  static const bool cuda_core = [] { const char* e = getenv("KFB_GEMV_IMPL"); return e && e[0] == 'c'; }();
+  const size_t mma_smem = (size_t)((K / group) * 16 + 8 * 32 * 4) * sizeof(float);
+  if (!cuda_core && !(flags & 1) && mma_smem <= 48 * 1024)
+    return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, s)
+                        : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, s);
   return group == 128 ? gemv::pick_m<128>(x, packed, scales, y, M, N, K, flags, s)
                       : gemv::pick_m<64>(x, packed, scales, y, M, N, K, flags, s);
 }
