@@ -6,18 +6,22 @@
 // multiply-accumulate of 16 rows x 16 k x 8 batch columns is ONE instruction, which leaves the unpack (5 logic ops per
 // 8 weights) as the only per-weight work: ~0.6 issue slots per weight, the same for every M up to 8.
 //
-// With the issue limit gone the kernel is bound by how many bytes each SM keeps in flight, so the weight stream goes
-// through a shared-memory ring filled by cp.async (16 bytes per lane per row per round, L1 bypassed, 128-byte L2
-// fetch): kStages rounds per warp are outstanding at any time, ~170 KB per SM.  A lane consumes exactly the 16-byte
-// pieces it requested itself, so the ring is private to the lane (no barrier, no bank conflict) -- it is a register
-// file extension for loads in flight, not a data exchange.
+// What limits the kernel after that, in the order it was measured (ncu, N = 180224, K = 2048):
+//  1. bytes in flight per SM -> the weight stream is staged through shared memory, several rounds ahead per warp;
+//  2. the integer pipe (logic and shift instructions issue at half rate on B200): address arithmetic and predication
+//     cost more than the unpack itself -> everything inside a chunk is addressed as pointer + immediate, accumulators
+//     start from the zero register, batch columns past M read a valid row instead of being zero-filled (a column of
+//     the MMA result depends on its own column of the activations only, and those columns are never stored);
+//  3. the L1 tag stage (one 128-byte line per clock per SM): per-lane 16-byte loads of 16 different rows touch 8
+//     lines per instruction -> the weights are fetched by the TMA unit instead, one bulk copy of 256 contiguous bytes
+//     per row and chunk (cp.async.bulk, mbarrier completion, no LSU involvement), scales are loaded a chunk at a
+//     time as one vector per row, and a warp may own two MMA row tiles that share every activation fragment.
 //
-// The second limit is the integer pipe (logic and shift instructions issue at half rate on B200): the first version
-// of this kernel spent 110 such instructions per round where the unpack needs 40, the rest being address arithmetic
-// and predication.  So the round loop is unrolled by the ring depth with the K split a template parameter -- every
-// global, shared and ring address of a round is then a pointer plus an immediate -- accumulators start from the zero
-// register instead of being cleared, and batch columns past M read a valid row instead of being zero-filled (a
-// column of the MMA result depends on its own column of the activations only, and those columns are never stored).
+// Shared-memory stage of a warp: R = 16 or 32 rows x 256 bytes (4 rounds of G = 128, 8 of G = 64).  Even rows first,
+// then the odd rows 64 bytes further, so that the eight lanes of a 128-bit shared load (rows g, g + 1; four pieces of
+// 16 bytes each) cover all 32 banks.  Every lane below R issues the copy of one row and arrives on the stage's
+// mbarrier with its own byte count; a stage is re-issued by the same warp after __syncwarp(), so there is no
+// consumer -> producer barrier.
 //
 // Arithmetic.  The nibbles are NOT converted to q.  The masked forms A = 1024 + u (nibble pairs 0 and 2 of a word)
 // and B = 1024 + 16u (pairs 1 and 3) are exact fp16 values and go straight into the MMA (fp16 x fp16 products are
@@ -27,8 +31,8 @@
 // only and are computed once per CTA).  The group scale is applied in FP32, one rounding to fp16 at the end.
 //
 // Fragment use (m16n8k16, A = weights row-major 16 rows x 16 k, B = activations, 8 columns = batch rows):
-//   lane = 4 g + t.  The lane streams rows g and g + 8 of the tile; per round (one scale group of 128 k, or 64 k when
-//   G = 64) it loads G/32 packed words of each row, its k range being 32 t .. 32 t + 31 (16 t .. when G = 64) of the
+//   lane = 4 g + t.  The lane consumes rows g and g + 8 of a tile; per round (one scale group of 128 k, or 64 k when
+//   G = 64) it reads G/32 packed words of each row, its k range being 32 t .. 32 t + 31 (16 t .. when G = 64) of the
 //   group.  For word j: a0/a1 = pair 0 of rows g / g+8, a2/a3 = pair 2  -> MMA (j, A);  pairs 1 and 3 -> MMA (j, B).
 //   The k positions an MMA multiplies are whatever the four lanes t = 0..3 put in the same fragment slots, so the B
 //   fragment of lane (g, t) is simply the same pairs of x[m = g] at this lane's k range -- any consistent assignment
@@ -36,24 +40,19 @@
 #pragma once
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace kfb {
 namespace gemv_mma {
 
+using namespace kfb::sm100;
+
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr int kTileRows = 16;
-constexpr int kStages = 8;             // rounds in flight per warp = unroll factor of the round loop
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+constexpr int kChunkBytes = 256;       // bytes of one weight row per bulk copy
+constexpr int kStages = 3;             // chunks in flight per warp
+constexpr uint32_t kWaitStage = 0x501; // status code of an expired wait
 
 // d = a * b + c, m16n8k16, fp16 operands, FP32 accumulation
 __device__ __forceinline__ void mma16816_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -63,60 +62,70 @@ __device__ __forceinline__ void mma16816_f16(float (&d)[4], uint32_t a0, uint32_
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
-__host__ __device__ constexpr size_t ring_bytes() { return (size_t)kWarps * kStages * 2 * 32 * 16; }
-inline size_t smem_bytes(int rounds) { return (size_t)(rounds * 16 + kWarps * 32 * 4) * sizeof(float) + ring_bytes(); }
+template <int T>
+__host__ __device__ constexpr uint32_t stage_bytes() { return 16u * T * kChunkBytes + 128u; }
+// ring | mbarriers | abort word | class sums.  The cross-warp reduction reuses the ring.
+template <int T>
+__host__ __device__ constexpr size_t sx_offset() { return (size_t)kWarps * kStages * stage_bytes<T>() + kWarps * kStages * 8 + 16; }
+template <int T>
+inline size_t smem_bytes(int rounds) { return sx_offset<T>() + (size_t)rounds * 16 * sizeof(float); }
 
-// G: scale group size (128 or 64).  Rounds of G k.  KS = 1 << KSL warps of a CTA share a row tile and take rounds
-// kpart, kpart + KS, ...  Shared memory: class sums of x for every round, the cross-warp reduction, the ring.
-template <int G, int KSL>
-__global__ void __launch_bounds__(kThreads, 3)
-int4_gemv_mma_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ packed, const __half* __restrict__ scales,
-                     __half* __restrict__ y, int M, int N, int K) {
+// G: scale group size (128 or 64).  KS = 1 << KSL warps of a CTA share a row tile and take chunks kpart, kpart + KS,
+// ...  T: MMA row tiles (16 rows) per warp.  `vec_scales`: every chunk is full and the scale rows are aligned, so the
+// scales of a chunk are one vector load per row.
+template <int G, int KSL, int T>
+__global__ void __launch_bounds__(kThreads, T == 1 ? 2 : 1)
+int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restrict__ packed, const __half* __restrict__ scales,
+                     __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status) {
   constexpr int W = G / 32;            // packed words per lane per row per round
   constexpr int kLaneK = G / 4;        // k per lane per round (32 or 16)
   constexpr int KS = 1 << KSL;
-  constexpr int kWStep = KS * (G / 8);   // words between two rounds of this warp
-  constexpr int kXStep = KS * G;         // activations
-  constexpr int kSxStep = KS * 16;       // class-sum floats
-  constexpr uint32_t kSlot = 2 * 32 * 16;  // ring bytes per round
-  extern __shared__ __align__(16) float smem_f[];
+  constexpr int C = kChunkBytes / (G / 2);   // rounds per chunk (4 or 8)
+  constexpr int R = kTileRows * T;           // rows per warp
+  constexpr uint32_t kStage = stage_bytes<T>();
+  constexpr uint32_t kOdd = (R / 2) * kChunkBytes + 64;   // where the odd rows of a stage start
+  extern __shared__ __align__(128) unsigned char smem[];
   const int rounds = K / G;
-  float* sx = smem_f;                          // [rounds][8 columns][2 classes], pre-multiplied by -1032 / -72
-  float* red = smem_f + rounds * 16;           // [kWarps][32 lanes][4]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages * kStage);
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * kStages);
+  float* sx = reinterpret_cast<float*>(smem + sx_offset<T>());   // [rounds][8 columns][2 classes], times -1032 / -72
+  float* red = reinterpret_cast<float*>(smem);                   // [kWarps][32 lanes][T][4], after the main loop
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  // this lane's ring slots: [stage][row lo / hi] 16 bytes each; consecutive lanes are 16 bytes apart
-  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(red + kWarps * 32 * 4) + (uint32_t)(warp * kStages * 2 * 32 + lane) * 16u;
 
   const int tile = blockIdx.x * (kWarps >> KSL) + (warp >> KSL);
   const int kpart = warp & (KS - 1);
-  const int row_lo = min(tile * kTileRows + g, N - 1);      // rows past N: clamped loads, never stored
-  const int row_hi = min(tile * kTileRows + g + 8, N - 1);
-  const int words_per_row = K / 8;
-  // everything below points at round kpart and advances by kStages rounds of this warp per loop trip
-  const uint32_t* pw_lo = packed + (size_t)row_lo * words_per_row + t * W + kpart * (G / 8);
-  const uint32_t* pw_hi = packed + (size_t)row_hi * words_per_row + t * W + kpart * (G / 8);
-  const __half* ps_lo = scales + (size_t)row_lo * rounds + kpart;
-  const __half* ps_hi = scales + (size_t)row_hi * rounds + kpart;
-  const __half* px = x + (size_t)min(g, M - 1) * K + t * kLaneK + kpart * G;   // column g of the B operand
-  const float* psx = sx + kpart * 16 + t * 4;                                  // columns 2t, 2t+1: (A, B, A, B)
-  // rounds of this warp: rd(i) = kpart + i * KS, i < n_i (none for a tile past N)
-  const int n_i = tile * kTileRows < N ? (rounds - kpart + KS - 1) >> KSL : 0;
+  const int row0 = tile * R;
+  // chunks of this warp: c(i) = kpart + i * KS, i < n_c (none for a tile past N)
+  const int n_chunks = (rounds + C - 1) / C;
+  const int n_c = row0 < N ? (n_chunks - kpart + KS - 1) >> KSL : 0;
 
+  uint64_t* my_bars = bars + warp * kStages;
+  const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * kStages * kStage;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], R);
+    fence_mbar_init();
+  }
+  if (threadIdx.x == 0) *abort_word = 0;
+  __syncwarp();
+
+  // lane L < R copies row L of the warp's rows (rows past N: the last row, never stored)
+  const unsigned char* src_row = packed + (size_t)min(row0 + lane, N - 1) * (size_t)(K / 2);
+  const uint32_t dst_row = ((lane & 1) ? kOdd : 0u) + (uint32_t)(lane >> 1) * kChunkBytes;
+  auto issue = [&](int i) {
+    const int c = kpart + (i << KSL);
+    const uint32_t bytes = (uint32_t)min(C, rounds - c * C) * (G / 2);
+    const int s = i % kStages;
+    if (lane < R) {
+      mbar_arrive_expect_tx(&my_bars[s], bytes);
+      bulk_load(my_ring + s * kStage + dst_row, src_row + (size_t)c * kChunkBytes, bytes, &my_bars[s]);
+    }
+  };
   // the weight stream starts before anything else: the class sums below run under its latency
 #pragma unroll
-  for (int u = 0; u < kStages; ++u) {
-    if (u < n_i) {
-      if constexpr (W == 4) {
-        cp_async16(ring + u * kSlot, pw_lo + u * kWStep);
-        cp_async16(ring + u * kSlot + 32 * 16, pw_hi + u * kWStep);
-      } else {
-        cp_async8(ring + u * kSlot, pw_lo + u * kWStep);
-        cp_async8(ring + u * kSlot + 32 * 16, pw_hi + u * kWStep);
-      }
-    }
-    cp_async_commit();   // always: group i <-> round i
-  }
+  for (int i = 0; i < kStages; ++i)
+    if (i < n_c) issue(i);
 
   // ---- class sums of the activations, once per CTA.  Four lanes share one (round, batch row): each sums a quarter
   // of the group (whole packed words: pairs 0, 2 of a word are class A, pairs 1, 3 class B), then a quad reduction.
@@ -154,122 +163,179 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ 
   }
   __syncthreads();
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};   // rows g, g+8 x columns 2t, 2t+1
-  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int i0 = 0; i0 < n_i; i0 += kStages) {
+  const AbortCtx ctx{abort_word, status};
+  float acc[T][4];
 #pragma unroll
-    for (int u = 0; u < kStages; ++u) {
-      if (i0 + u < n_i) {   // warp-uniform
-        const float s_lo = __half2float(ps_lo[u * KS]), s_hi = __half2float(ps_hi[u * KS]);
+  for (int tt = 0; tt < T; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+  // rows g + 8 k (k < 2 T) of the warp's rows: position of this lane's words inside a stage
+  const uint32_t rd_base = ((g & 1) ? kOdd : 0u) + (uint32_t)(g >> 1) * kChunkBytes + (uint32_t)t * (W * 4);
+  const __half* xrow = x + (size_t)min(g, M - 1) * K + t * kLaneK;   // column g of the B operand
+  const __half* srow[2 * T];
+#pragma unroll
+  for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + g + 8 * k, N - 1) * rounds;
+
+  for (int i = 0; i < n_c; ++i) {
+    const int c = kpart + (i << KSL);
+    const int r0 = c * C, nr = min(C, rounds - r0);
+    // group scales of the chunk, raw fp16 bits: sc[k][u / 2] holds rounds u (low half) and u + 1
+    uint32_t sc[2 * T][C / 2];
+    if (vec_scales) {
+#pragma unroll
+      for (int k = 0; k < 2 * T; ++k) {
+        if constexpr (C == 4) {
+          const uint2 v = *reinterpret_cast<const uint2*>(srow[k] + r0);
+          sc[k][0] = v.x; sc[k][1] = v.y;
+        } else {
+          const uint4 v = *reinterpret_cast<const uint4*>(srow[k] + r0);
+          sc[k][0] = v.x; sc[k][1] = v.y; sc[k][2] = v.z; sc[k][3] = v.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 2 * T; ++k)
+#pragma unroll
+        for (int u = 0; u < C; u += 2) {
+          const uint32_t a = u < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u]) : 0u;
+          const uint32_t b = u + 1 < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u + 1]) : 0u;
+          sc[k][u / 2] = a | (b << 16);
+        }
+    }
+    if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[i % kStages], (uint32_t)(i / kStages) & 1u, ctx, kWaitStage))) break;
+    const uint32_t st = my_ring + (uint32_t)(i % kStages) * kStage + rd_base;
+    const __half* px = xrow + (size_t)r0 * G;
+    const float* psx = sx + r0 * 16 + t * 4;   // columns 2t, 2t+1: (A, B, A, B)
+#pragma unroll
+    for (int u = 0; u < C; ++u) {
+      if (u < nr) {   // warp-uniform
         uint32_t xs[W * 4];
 #pragma unroll
         for (int j = 0; j < W; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4*>(px + u * kXStep + j * 8);
+          const uint4 v = *reinterpret_cast<const uint4*>(px + u * G + j * 8);
           xs[4 * j + 0] = v.x; xs[4 * j + 1] = v.y; xs[4 * j + 2] = v.z; xs[4 * j + 3] = v.w;
         }
-        cp_async_wait<kStages - 1>();   // round i0 + u has landed (this lane's own copies)
-        uint32_t wlo[W], whi[W];
-        if constexpr (W == 4) {
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wlo[0]), "=r"(wlo[1]), "=r"(wlo[2]), "=r"(wlo[3]) : "r"(ring + u * kSlot));
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(whi[0]), "=r"(whi[1]), "=r"(whi[2]), "=r"(whi[3]) : "r"(ring + u * kSlot + 32 * 16));
-        } else {
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wlo[0]), "=r"(wlo[1]) : "r"(ring + u * kSlot));
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(whi[0]), "=r"(whi[1]) : "r"(ring + u * kSlot + 32 * 16));
+        const float4 cs = *reinterpret_cast<const float4*>(psx + u * 16);
+        uint32_t w[2 * T][W];
+#pragma unroll
+        for (int k = 0; k < 2 * T; ++k) {
+          const uint32_t a = st + k * 4 * kChunkBytes + u * (G / 2);
+          if constexpr (W == 4)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[k][0]), "=r"(w[k][1]), "=r"(w[k][2]), "=r"(w[k][3]) : "r"(a));
+          else
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[k][0]), "=r"(w[k][1]) : "r"(a));
         }
-        float ca[4], cb[4];
         constexpr uint32_t kMagic = 0x64006400u;
 #pragma unroll
-        for (int j = 0; j < W; ++j) {
-          const uint32_t lo = wlo[j], hi = whi[j], lo8 = lo >> 8, hi8 = hi >> 8;
-          // xs[4j + p] holds the activation pair multiplied by nibble pair p of word j
-          mma16816_f16(ca, (lo & 0x000F000Fu) | kMagic, (hi & 0x000F000Fu) | kMagic, (lo8 & 0x000F000Fu) | kMagic,
-                       (hi8 & 0x000F000Fu) | kMagic, xs[4 * j + 0], xs[4 * j + 2], j == 0 ? zero : ca);
-          mma16816_f16(cb, (lo & 0x00F000F0u) | kMagic, (hi & 0x00F000F0u) | kMagic, (lo8 & 0x00F000F0u) | kMagic,
-                       (hi8 & 0x00F000F0u) | kMagic, xs[4 * j + 1], xs[4 * j + 3], j == 0 ? zero : cb);
-        }
-        // the slot is free again (its words sit in the MMA operands): request the round kStages ahead
-        if (i0 + kStages + u < n_i) {
-          if constexpr (W == 4) {
-            cp_async16(ring + u * kSlot, pw_lo + (kStages + u) * kWStep);
-            cp_async16(ring + u * kSlot + 32 * 16, pw_hi + (kStages + u) * kWStep);
-          } else {
-            cp_async8(ring + u * kSlot, pw_lo + (kStages + u) * kWStep);
-            cp_async8(ring + u * kSlot + 32 * 16, pw_hi + (kStages + u) * kWStep);
+        for (int tt = 0; tt < T; ++tt) {
+          float ca[4], cb[4];
+#pragma unroll
+          for (int j = 0; j < W; ++j) {
+            const uint32_t lo = w[2 * tt][j], hi = w[2 * tt + 1][j], lo8 = lo >> 8, hi8 = hi >> 8;
+            // xs[4j + p] holds the activation pair multiplied by nibble pair p of word j
+            mma16816_f16(ca, (lo & 0x000F000Fu) | kMagic, (hi & 0x000F000Fu) | kMagic, (lo8 & 0x000F000Fu) | kMagic,
+                         (hi8 & 0x000F000Fu) | kMagic, xs[4 * j + 0], xs[4 * j + 2], j == 0 ? zero : ca);
+            mma16816_f16(cb, (lo & 0x00F000F0u) | kMagic, (hi & 0x00F000F0u) | kMagic, (lo8 & 0x00F000F0u) | kMagic,
+                         (hi8 & 0x00F000F0u) | kMagic, xs[4 * j + 1], xs[4 * j + 3], j == 0 ? zero : cb);
           }
+          // remove the offsets of the unsigned forms and apply the group scale
+          const __half2 s2lo = *reinterpret_cast<const __half2*>(&sc[2 * tt][u / 2]);
+          const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
+          const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
+          const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
+          acc[tt][0] = fmaf(s_lo, (ca[0] + cs.x) + fmaf(cb[0], 0.0625f, cs.y), acc[tt][0]);
+          acc[tt][1] = fmaf(s_lo, (ca[1] + cs.z) + fmaf(cb[1], 0.0625f, cs.w), acc[tt][1]);
+          acc[tt][2] = fmaf(s_hi, (ca[2] + cs.x) + fmaf(cb[2], 0.0625f, cs.y), acc[tt][2]);
+          acc[tt][3] = fmaf(s_hi, (ca[3] + cs.z) + fmaf(cb[3], 0.0625f, cs.w), acc[tt][3]);
         }
-        cp_async_commit();
-        // remove the offsets of the unsigned forms and apply the group scale
-        const float4 c = *reinterpret_cast<const float4*>(psx + u * kSxStep);   // column 2t: (A, B), column 2t+1: (A, B)
-        acc[0] = fmaf(s_lo, (ca[0] + c.x) + fmaf(cb[0], 0.0625f, c.y), acc[0]);
-        acc[1] = fmaf(s_lo, (ca[1] + c.z) + fmaf(cb[1], 0.0625f, c.w), acc[1]);
-        acc[2] = fmaf(s_hi, (ca[2] + c.x) + fmaf(cb[2], 0.0625f, c.y), acc[2]);
-        acc[3] = fmaf(s_hi, (ca[3] + c.z) + fmaf(cb[3], 0.0625f, c.w), acc[3]);
       }
     }
-    pw_lo += kStages * kWStep;
-    pw_hi += kStages * kWStep;
-    ps_lo += kStages * KS;
-    ps_hi += kStages * KS;
-    px += kStages * kXStep;
-    psx += kStages * kSxStep;
+    __syncwarp();   // every lane has its words of this stage in registers: the stage may be refilled
+    if (i + kStages < n_c) issue(i + kStages);
   }
-  cp_async_wait<0>();
+  if (*abort_word != 0) {   // a wait expired: give the copies still in flight time to land before the CTA retires
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
 
   if constexpr (KSL != 0) {
-    __syncthreads();
-    float4* mine = reinterpret_cast<float4*>(red + (warp * 32 + lane) * 4);
-    *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();   // all warps are past their last stage: the ring becomes the reduction buffer
+    float4* mine = reinterpret_cast<float4*>(red + (size_t)(warp * 32 + lane) * T * 4);
+#pragma unroll
+    for (int tt = 0; tt < T; ++tt) mine[tt] = make_float4(acc[tt][0], acc[tt][1], acc[tt][2], acc[tt][3]);
     __syncthreads();
     if (kpart != 0) return;
     for (int p = 1; p < KS; ++p) {  // fixed order
-      const float4 o = *reinterpret_cast<const float4*>(red + ((warp + p) * 32 + lane) * 4);
-      acc[0] += o.x; acc[1] += o.y; acc[2] += o.z; acc[3] += o.w;
+      const float4* o = reinterpret_cast<const float4*>(red + (size_t)((warp + p) * 32 + lane) * T * 4);
+#pragma unroll
+      for (int tt = 0; tt < T; ++tt) {
+        acc[tt][0] += o[tt].x; acc[tt][1] += o[tt].y; acc[tt][2] += o[tt].z; acc[tt][3] += o[tt].w;
+      }
     }
   }
-  const int r0 = tile * kTileRows + g, r1 = r0 + 8, m0 = 2 * t, m1 = 2 * t + 1;
-  if (m0 < M) {
-    if (r0 < N) y[(size_t)m0 * N + r0] = __float2half_rn(acc[0]);
-    if (r1 < N) y[(size_t)m0 * N + r1] = __float2half_rn(acc[2]);
-  }
-  if (m1 < M) {
-    if (r0 < N) y[(size_t)m1 * N + r0] = __float2half_rn(acc[1]);
-    if (r1 < N) y[(size_t)m1 * N + r1] = __float2half_rn(acc[3]);
+  const int m0 = 2 * t, m1 = 2 * t + 1;
+#pragma unroll
+  for (int tt = 0; tt < T; ++tt) {
+    const int ra = row0 + tt * kTileRows + g, rb = ra + 8;
+    if (m0 < M) {
+      if (ra < N) y[(size_t)m0 * N + ra] = __float2half_rn(acc[tt][0]);
+      if (rb < N) y[(size_t)m0 * N + rb] = __float2half_rn(acc[tt][2]);
+    }
+    if (m1 < M) {
+      if (ra < N) y[(size_t)m1 * N + ra] = __float2half_rn(acc[tt][1]);
+      if (rb < N) y[(size_t)m1 * N + rb] = __float2half_rn(acc[tt][3]);
+    }
   }
 }
 
-template <int G, int KSL>
-int launch_ks(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
-              cudaStream_t stream) {
+template <int G, int KSL, int T>
+int launch_cfg(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
+               int vec_scales, cudaStream_t stream) {
   static bool attr_done[64] = {};   // per device: opt in to more than 48 KB of dynamic shared memory
   int dev = 0;
   KFB_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !attr_done[dev]) {
-    KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_mma_kernel<G, KSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_mma_kernel<G, KSL, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_done[dev] = true;
   }
-  int4_gemv_mma_kernel<G, KSL><<<grid, kThreads, smem, stream>>>((const __half*)x, (const uint32_t*)packed, (const __half*)scales,
-                                                                 (__half*)y, M, N, K);
+  unsigned int* status = device_status_word();
+  if (!status) return KFB_ERR_CUDA;
+  int4_gemv_mma_kernel<G, KSL, T><<<grid, kThreads, smem, stream>>>((const __half*)x, (const unsigned char*)packed,
+                                                                    (const __half*)scales, (__half*)y, M, N, K, vec_scales, status);
   KFB_LAUNCH_CHECK("int4_gemv_mma_kernel");
   return KFB_OK;
 }
 
+// Two row tiles per warp once that still gives every SM two CTAs' worth of rows; below that one tile per warp and K
+// split over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks).
+inline int pick_tiles(int N) { return (long long)N >= 2LL * 32 * kWarps * sm_count() ? 2 : 1; }
+template <int G>
+inline bool fits(int N, int K) {
+  return (pick_tiles(N) == 2 ? smem_bytes<2>(K / G) : smem_bytes<1>(K / G)) <= 227u * 1024u;
+}
+
+template <int G, int T>
+int launch_t(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, cudaStream_t stream) {
+  constexpr int C = kChunkBytes / (G / 2);
+  const int rounds = K / G, n_chunks = ceil_div(rounds, C);
+  const int tiles = ceil_div(N, kTileRows * T);
+  int ksl = 0;
+  const long long want = (T == 2 ? 8LL : 16LL) * sm_count();
+  while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= n_chunks) ++ksl;
+  const int grid = ceil_div(tiles, kWarps >> ksl);
+  const size_t smem = smem_bytes<T>(rounds);
+  const int vec = (rounds % C == 0) && aligned16(scales);
+  switch (ksl) {
+    case 0: return launch_cfg<G, 0, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
+    case 1: return launch_cfg<G, 1, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
+    case 2: return launch_cfg<G, 2, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
+    default: return launch_cfg<G, 3, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
+  }
+}
+
 template <int G>
 int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, cudaStream_t stream) {
-  const int rounds = K / G;
-  const int tiles = ceil_div(N, kTileRows);
-  // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than rounds)
-  int ksl = 0;
-  const long long want = 16LL * sm_count();
-  while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= rounds) ++ksl;
-  const int grid = ceil_div(tiles, kWarps >> ksl);
-  const size_t smem = smem_bytes(rounds);
-  if (smem > 200 * 1024) return fail(KFB_ERR_UNSUPPORTED, "K=%d needs %zu bytes of shared memory for the class sums", K, smem);
-  switch (ksl) {
-    case 0: return launch_ks<G, 0>(x, packed, scales, y, M, N, K, grid, smem, stream);
-    case 1: return launch_ks<G, 1>(x, packed, scales, y, M, N, K, grid, smem, stream);
-    case 2: return launch_ks<G, 2>(x, packed, scales, y, M, N, K, grid, smem, stream);
-    default: return launch_ks<G, 3>(x, packed, scales, y, M, N, K, grid, smem, stream);
-  }
+  return pick_tiles(N) == 2 ? launch_t<G, 2>(x, packed, scales, y, M, N, K, stream)
+                            : launch_t<G, 1>(x, packed, scales, y, M, N, K, stream);
 }
 
 }  // namespace gemv_mma
