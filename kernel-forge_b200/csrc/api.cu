@@ -89,7 +89,7 @@ int resolve_encoder() {
 }  // namespace
 
 int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
-                       uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer) {
+                       uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
   if (int rc = resolve_encoder()) return rc;
   if (elem_bytes != 4) return fail(KFB_ERR_INVALID, "make_tmap_2d_plain handles 32-bit elements");
   cuuint64_t gdim[2] = {inner, outer};
@@ -97,7 +97,8 @@ int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint6
   cuuint32_t bdim[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstr, bdim, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled (2-D) failed with CUresult %d (dims %llu,%llu)", (int)r,

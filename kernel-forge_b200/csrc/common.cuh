@@ -62,7 +62,8 @@ unsigned int* device_status_word();
 // dims[0] is the innermost (dense) extent; strides_bytes[i] is the stride of dims[i+1].
 int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
                        const uint64_t strides_bytes[3], const uint32_t box[4]);
-// Tiled 2-D tensor map without swizzle over 32-bit elements (the packed INT4 words).
+// Tiled 2-D tensor map over 32-bit elements (the packed INT4 words), without swizzle or with the 128-byte swizzle
+// (box_inner <= 32 elements then).
 int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
-                       uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer);
+                       uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128 = false);
 }  // namespace kfb

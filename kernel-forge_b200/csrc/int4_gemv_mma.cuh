@@ -13,27 +13,34 @@
 //     start from the zero register, batch columns past M read a valid row instead of being zero-filled (a column of
 //     the MMA result depends on its own column of the activations only, and those columns are never stored);
 //  3. the L1 tag stage (one 128-byte line per clock per SM): per-lane 16-byte loads of 16 different rows touch 8
-//     lines per instruction -> the weights are fetched by the TMA unit instead, one bulk copy of 256 contiguous bytes
-//     per row and chunk (cp.async.bulk, mbarrier completion, no LSU involvement), scales are loaded a chunk at a
-//     time as one vector per row, and a warp may own two MMA row tiles that share every activation fragment.
+//     lines per instruction -> the weights are fetched by the TMA unit instead (no LSU involvement), scales are
+//     loaded a chunk at a time as one vector per row, and a warp may own two MMA row tiles that share every
+//     activation fragment;
+//  4. the request rate of the TMA unit: untiled bulk copies of 256 bytes (one per row) stop at ~2.5 TB/s, i.e. one
+//     request per ~29 clocks per SM -> one tiled copy (tensor map over the packed matrix, box = R rows x 128 bytes)
+//     per warp and chunk, 2 or 4 KB per request.
 //
-// Shared-memory stage of a warp: R = 16 or 32 rows x 256 bytes (4 rounds of G = 128, 8 of G = 64).  Even rows first,
-// then the odd rows 64 bytes further, so that the eight lanes of a 128-bit shared load (rows g, g + 1; four pieces of
-// 16 bytes each) cover all 32 banks.  Every lane below R issues the copy of one row and arrives on the stage's
-// mbarrier with its own byte count; a stage is re-issued by the same warp after __syncwarp(), so there is no
-// consumer -> producer barrier.
+// Shared-memory stage of a warp: R = 16 or 32 rows x 128 bytes (2 rounds of G = 128, 4 of G = 64), written by the TMA
+// with the 128-byte swizzle (16-byte piece j of row r sits at piece j ^ (r & 7)).  Fragment row slot g of a tile
+// holds matrix row p(g) = 4 (g & 1) + (g >> 1) (and p(g) + 8): the eight lanes of one 128-bit shared load then read
+// rows q and q + 4, whose swizzled pieces lie in opposite 64-byte halves, so every load covers all 32 banks.  One
+// lane issues the copy; a stage is re-issued by the same warp after __syncwarp(), so there is no consumer ->
+// producer barrier.  Rows past N and bytes past K/2 are zero-filled by the TMA.
 //
-// Arithmetic.  The nibbles are NOT converted to q.  The masked forms A = 1024 + u (nibble pairs 0 and 2 of a word)
-// and B = 1024 + 16u (pairs 1 and 3) are exact fp16 values and go straight into the MMA (fp16 x fp16 products are
-// exact, FP32 accumulation); class-A and class-B values go to different MMAs, and per scale group
-//     sum_k q x = (accA - 1032 * SxA) + (accB / 16 - 72 * SxB),
-// with SxA / SxB the sums of the activations multiplied by class-A / class-B weights in that group (they depend on x
-// only and are computed once per CTA).  The group scale is applied in FP32, one rounding to fp16 at the end.
+// Arithmetic.  The nibbles are NOT converted to q.  Masking a word in place gives exact fp16 values with the nibble in
+// the mantissa: pairs 0 and 2 of a word (k offsets 0,1 / 4,5) as (w & 0x000F000F) | 0x7400.. = 16384 + 16 u, pairs 1
+// and 3 (k offsets 2,3 / 6,7) as (w & 0x00F000F0) | 0x6400.. = 1024 + 16 u.  Both carry 16 u, so all of them go into
+// the same accumulator (fp16 x fp16 products are exact, FP32 accumulation) and per scale group
+//     sum_k q x = acc / 16 - 1032 * SxA - 72 * SxB,
+// with SxA / SxB the sums of the activations that meet pairs 0,2 / pairs 1,3 in that group (they depend on x only;
+// the combined correction is computed once per CTA).  The group scale is applied in FP32, one rounding to fp16 at the
+// end.  An MMA takes pairs (0, 1) or (2, 3) of one word, so its B operand is two consecutive registers of the
+// 16-byte activation vector.
 //
 // Fragment use (m16n8k16, A = weights row-major 16 rows x 16 k, B = activations, 8 columns = batch rows):
 //   lane = 4 g + t.  The lane consumes rows g and g + 8 of a tile; per round (one scale group of 128 k, or 64 k when
 //   G = 64) it reads G/32 packed words of each row, its k range being 32 t .. 32 t + 31 (16 t .. when G = 64) of the
-//   group.  For word j: a0/a1 = pair 0 of rows g / g+8, a2/a3 = pair 2  -> MMA (j, A);  pairs 1 and 3 -> MMA (j, B).
+//   group.  For word j: a0/a1 = pair 0 of the two rows, a2/a3 = pair 1 -> first MMA;  pairs 2 and 3 -> second MMA.
 //   The k positions an MMA multiplies are whatever the four lanes t = 0..3 put in the same fragment slots, so the B
 //   fragment of lane (g, t) is simply the same pairs of x[m = g] at this lane's k range -- any consistent assignment
 //   of k to fragment slots gives the same dot product.
@@ -50,8 +57,7 @@ using namespace kfb::sm100;
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr int kTileRows = 16;
-constexpr int kChunkBytes = 256;       // bytes of one weight row per bulk copy
-constexpr int kStages = 3;             // chunks in flight per warp
+constexpr int kChunkBytes = 128;       // bytes of one weight row per stage (the span of the 128-byte swizzle)
 constexpr uint32_t kWaitStage = 0x501; // status code of an expired wait
 
 // d = a * b + c, m16n8k16, fp16 operands, FP32 accumulation
@@ -62,33 +68,67 @@ __device__ __forceinline__ void mma16816_f16(float (&d)[4], uint32_t a0, uint32_
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
+// (a & mask) | magic as ONE logic instruction.  Written with literal constants the compiler emits two (a LOP3 takes a
+// single immediate), which doubled the integer-pipe load of the unpack; the constants therefore arrive as a kernel
+// argument and stay in registers.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));
+  return d;
+}
+
+// Bounded wait for a stage.  Unlike sm100::mbar_wait it sleeps between polls: several chunks are in flight per warp,
+// so a late wake-up costs nothing, while a polling warp would take issue slots and integer-pipe cycles from the warps
+// that have data.
+__device__ __forceinline__ bool wait_stage(uint64_t* bar, uint32_t parity, const AbortCtx& ctx) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(100);
+    if ((++spins & 255u) == 0) {
+      if (*ctx.cta_word != 0) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+        *ctx.cta_word = kWaitStage;
+        atomicCAS(ctx.device_word, 0u, kWaitStage);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 template <int T>
-__host__ __device__ constexpr uint32_t stage_bytes() { return 16u * T * kChunkBytes + 128u; }
-// ring | mbarriers | abort word | class sums.  The cross-warp reduction reuses the ring.
+__host__ __device__ constexpr uint32_t stage_bytes() { return 16u * T * kChunkBytes; }
+// chunks in flight per warp: 12 KB (T = 2, two CTAs per SM) or 8 KB (T = 1, three CTAs per SM)
 template <int T>
-__host__ __device__ constexpr size_t sx_offset() { return (size_t)kWarps * kStages * stage_bytes<T>() + kWarps * kStages * 8 + 16; }
+__host__ __device__ constexpr int stages() { return T == 2 ? 3 : 4; }
+// (ring, 1024-byte aligned) | mbarriers | abort word | class sums.  The cross-warp reduction reuses the ring.
 template <int T>
-inline size_t smem_bytes(int rounds) { return sx_offset<T>() + (size_t)rounds * 16 * sizeof(float); }
+__host__ __device__ constexpr size_t sx_offset() { return (size_t)kWarps * stages<T>() * stage_bytes<T>() + kWarps * stages<T>() * 8 + 16; }
+template <int T>
+inline size_t smem_bytes(int rounds) { return 1024 + sx_offset<T>() + (size_t)rounds * 8 * sizeof(float); }
 
 // G: scale group size (128 or 64).  KS = 1 << KSL warps of a CTA share a row tile and take chunks kpart, kpart + KS,
 // ...  T: MMA row tiles (16 rows) per warp.  `vec_scales`: every chunk is full and the scale rows are aligned, so the
 // scales of a chunk are one vector load per row.
 template <int G, int KSL, int T>
-__global__ void __launch_bounds__(kThreads, T == 1 ? 2 : 1)
-int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restrict__ packed, const __half* __restrict__ scales,
-                     __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status) {
+__global__ void __launch_bounds__(kThreads, T == 1 ? 3 : 2)
+int4_gemv_mma_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ scales,
+                     __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status, const uint4 unpack) {
   constexpr int W = G / 32;            // packed words per lane per row per round
   constexpr int kLaneK = G / 4;        // k per lane per round (32 or 16)
   constexpr int KS = 1 << KSL;
-  constexpr int C = kChunkBytes / (G / 2);   // rounds per chunk (4 or 8)
+  constexpr int C = kChunkBytes / (G / 2);   // rounds per chunk (2 or 4)
   constexpr int R = kTileRows * T;           // rows per warp
+  constexpr int kStages = stages<T>();
   constexpr uint32_t kStage = stage_bytes<T>();
-  constexpr uint32_t kOdd = (R / 2) * kChunkBytes + 64;   // where the odd rows of a stage start
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // the swizzle pattern is 1024-byte periodic
   const int rounds = K / G;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages * kStage);
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * kStages);
-  float* sx = reinterpret_cast<float*>(smem + sx_offset<T>());   // [rounds][8 columns][2 classes], times -1032 / -72
+  float* sx = reinterpret_cast<float*>(smem + sx_offset<T>());   // [rounds][8 columns]: -1032 SxA - 72 SxB
   float* red = reinterpret_cast<float*>(smem);                   // [kWarps][32 lanes][T][4], after the main loop
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -104,22 +144,17 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
   const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * kStages * kStage;
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], R);
+    for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], 1);
     fence_mbar_init();
   }
   if (threadIdx.x == 0) *abort_word = 0;
   __syncwarp();
 
-  // lane L < R copies row L of the warp's rows (rows past N: the last row, never stored)
-  const unsigned char* src_row = packed + (size_t)min(row0 + lane, N - 1) * (size_t)(K / 2);
-  const uint32_t dst_row = ((lane & 1) ? kOdd : 0u) + (uint32_t)(lane >> 1) * kChunkBytes;
-  auto issue = [&](int i) {
-    const int c = kpart + (i << KSL);
-    const uint32_t bytes = (uint32_t)min(C, rounds - c * C) * (G / 2);
-    const int s = i % kStages;
-    if (lane < R) {
-      mbar_arrive_expect_tx(&my_bars[s], bytes);
-      bulk_load(my_ring + s * kStage + dst_row, src_row + (size_t)c * kChunkBytes, bytes, &my_bars[s]);
+  auto issue = [&](int i) {   // one tiled copy: R rows x 128 bytes of chunk c(i)
+    if (lane == 0) {
+      const int c = kpart + (i << KSL), st = i % kStages;
+      mbar_arrive_expect_tx(&my_bars[st], kStage);
+      tma_load_2d(smem + (size_t)(warp * kStages + st) * kStage, &wmap, &my_bars[st], c * (kChunkBytes / 4), row0);
     }
   };
   // the weight stream starts before anything else: the class sums below run under its latency
@@ -129,8 +164,8 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
 
   // ---- class sums of the activations, once per CTA.  Four lanes share one (round, batch row): each sums a quarter
   // of the group (whole packed words: pairs 0, 2 of a word are class A, pairs 1, 3 class B), then a quad reduction.
-  for (int i = threadIdx.x; i < rounds * 16; i += kThreads)
-    if (((i >> 1) & 7) >= M) sx[i] = 0.f;
+  for (int i = threadIdx.x; i < rounds * 8; i += kThreads)
+    if ((i & 7) >= M) sx[i] = 0.f;
   {
     const int q = threadIdx.x & 3, items = rounds * M;
     for (int base = 0; base < items; base += kThreads / 4) {
@@ -156,8 +191,7 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
       sa += __shfl_xor_sync(0xffffffffu, sa, 2);
       sb += __shfl_xor_sync(0xffffffffu, sb, 2);
       if (live && q == 0) {
-        sx[(rd * 8 + m) * 2 + 0] = sa * -1032.0f;
-        sx[(rd * 8 + m) * 2 + 1] = sb * -72.0f;
+        sx[rd * 8 + m] = fmaf(sa, -1032.0f, sb * -72.0f);
       }
     }
   }
@@ -168,12 +202,19 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
 #pragma unroll
   for (int tt = 0; tt < T; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-  // rows g + 8 k (k < 2 T) of the warp's rows: position of this lane's words inside a stage
-  const uint32_t rd_base = ((g & 1) ? kOdd : 0u) + (uint32_t)(g >> 1) * kChunkBytes + (uint32_t)t * (W * 4);
+  // fragment row slot g holds matrix rows pg + 8 k (k < 2 T) of the warp's rows; off[u] = position of this lane's
+  // words of round u inside a stage (row pg, swizzled 16-byte piece)
+  const int pg = ((g & 1) << 2) | (g >> 1);
+  uint32_t off[C];
+#pragma unroll
+  for (int u = 0; u < C; ++u) {
+    const uint32_t byte = (uint32_t)u * (G / 2) + (uint32_t)t * (W * 4);
+    off[u] = (uint32_t)pg * kChunkBytes + ((((byte >> 4) ^ (uint32_t)pg) << 4) | (byte & 15u));
+  }
   const __half* xrow = x + (size_t)min(g, M - 1) * K + t * kLaneK;   // column g of the B operand
   const __half* srow[2 * T];
 #pragma unroll
-  for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + g + 8 * k, N - 1) * rounds;
+  for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + pg + 8 * k, N - 1) * rounds;
 
   for (int i = 0; i < n_c; ++i) {
     const int c = kpart + (i << KSL);
@@ -183,12 +224,11 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
     if (vec_scales) {
 #pragma unroll
       for (int k = 0; k < 2 * T; ++k) {
-        if constexpr (C == 4) {
+        if constexpr (C == 2) {
+          sc[k][0] = *reinterpret_cast<const uint32_t*>(srow[k] + r0);
+        } else {
           const uint2 v = *reinterpret_cast<const uint2*>(srow[k] + r0);
           sc[k][0] = v.x; sc[k][1] = v.y;
-        } else {
-          const uint4 v = *reinterpret_cast<const uint4*>(srow[k] + r0);
-          sc[k][0] = v.x; sc[k][1] = v.y; sc[k][2] = v.z; sc[k][3] = v.w;
         }
       }
     } else {
@@ -201,10 +241,10 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
           sc[k][u / 2] = a | (b << 16);
         }
     }
-    if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[i % kStages], (uint32_t)(i / kStages) & 1u, ctx, kWaitStage))) break;
-    const uint32_t st = my_ring + (uint32_t)(i % kStages) * kStage + rd_base;
+    if (!__all_sync(0xffffffffu, wait_stage(&my_bars[i % kStages], (uint32_t)(i / kStages) & 1u, ctx))) break;
+    const uint32_t st = my_ring + (uint32_t)(i % kStages) * kStage;
     const __half* px = xrow + (size_t)r0 * G;
-    const float* psx = sx + r0 * 16 + t * 4;   // columns 2t, 2t+1: (A, B, A, B)
+    const float* psx = sx + r0 * 8 + t * 2;   // columns 2t, 2t+1
 #pragma unroll
     for (int u = 0; u < C; ++u) {
       if (u < nr) {   // warp-uniform
@@ -214,38 +254,38 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
           const uint4 v = *reinterpret_cast<const uint4*>(px + u * G + j * 8);
           xs[4 * j + 0] = v.x; xs[4 * j + 1] = v.y; xs[4 * j + 2] = v.z; xs[4 * j + 3] = v.w;
         }
-        const float4 cs = *reinterpret_cast<const float4*>(psx + u * 16);
+        const float2 cs = *reinterpret_cast<const float2*>(psx + u * 8);
         uint32_t w[2 * T][W];
 #pragma unroll
         for (int k = 0; k < 2 * T; ++k) {
-          const uint32_t a = st + k * 4 * kChunkBytes + u * (G / 2);
+          const uint32_t a = st + off[u] + k * 8 * kChunkBytes;
           if constexpr (W == 4)
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[k][0]), "=r"(w[k][1]), "=r"(w[k][2]), "=r"(w[k][3]) : "r"(a));
           else
             asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[k][0]), "=r"(w[k][1]) : "r"(a));
         }
-        constexpr uint32_t kMagic = 0x64006400u;
+        const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
 #pragma unroll
         for (int tt = 0; tt < T; ++tt) {
-          float ca[4], cb[4];
+          float ca[4], cb[4];   // two accumulators, alternating, so that consecutive MMAs do not depend on each other
 #pragma unroll
           for (int j = 0; j < W; ++j) {
             const uint32_t lo = w[2 * tt][j], hi = w[2 * tt + 1][j], lo8 = lo >> 8, hi8 = hi >> 8;
             // xs[4j + p] holds the activation pair multiplied by nibble pair p of word j
-            mma16816_f16(ca, (lo & 0x000F000Fu) | kMagic, (hi & 0x000F000Fu) | kMagic, (lo8 & 0x000F000Fu) | kMagic,
-                         (hi8 & 0x000F000Fu) | kMagic, xs[4 * j + 0], xs[4 * j + 2], j == 0 ? zero : ca);
-            mma16816_f16(cb, (lo & 0x00F000F0u) | kMagic, (hi & 0x00F000F0u) | kMagic, (lo8 & 0x00F000F0u) | kMagic,
-                         (hi8 & 0x00F000F0u) | kMagic, xs[4 * j + 1], xs[4 * j + 3], j == 0 ? zero : cb);
+            mma16816_f16(ca, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
+                         and_or(hi, kMaskB, kMagicB), xs[4 * j + 0], xs[4 * j + 1], j == 0 ? zero : ca);
+            mma16816_f16(cb, and_or(lo8, kMaskA, kMagicA), and_or(hi8, kMaskA, kMagicA), and_or(lo8, kMaskB, kMagicB),
+                         and_or(hi8, kMaskB, kMagicB), xs[4 * j + 2], xs[4 * j + 3], j == 0 ? zero : cb);
           }
           // remove the offsets of the unsigned forms and apply the group scale
           const __half2 s2lo = *reinterpret_cast<const __half2*>(&sc[2 * tt][u / 2]);
           const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
           const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
           const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
-          acc[tt][0] = fmaf(s_lo, (ca[0] + cs.x) + fmaf(cb[0], 0.0625f, cs.y), acc[tt][0]);
-          acc[tt][1] = fmaf(s_lo, (ca[1] + cs.z) + fmaf(cb[1], 0.0625f, cs.w), acc[tt][1]);
-          acc[tt][2] = fmaf(s_hi, (ca[2] + cs.x) + fmaf(cb[2], 0.0625f, cs.y), acc[tt][2]);
-          acc[tt][3] = fmaf(s_hi, (ca[3] + cs.z) + fmaf(cb[3], 0.0625f, cs.w), acc[tt][3]);
+          acc[tt][0] = fmaf(s_lo, fmaf(ca[0] + cb[0], 0.0625f, cs.x), acc[tt][0]);
+          acc[tt][1] = fmaf(s_lo, fmaf(ca[1] + cb[1], 0.0625f, cs.y), acc[tt][1]);
+          acc[tt][2] = fmaf(s_hi, fmaf(ca[2] + cb[2], 0.0625f, cs.x), acc[tt][2]);
+          acc[tt][3] = fmaf(s_hi, fmaf(ca[3] + cb[3], 0.0625f, cs.y), acc[tt][3]);
         }
       }
     }
@@ -275,7 +315,7 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
   const int m0 = 2 * t, m1 = 2 * t + 1;
 #pragma unroll
   for (int tt = 0; tt < T; ++tt) {
-    const int ra = row0 + tt * kTileRows + g, rb = ra + 8;
+    const int ra = row0 + tt * kTileRows + pg, rb = ra + 8;
     if (m0 < M) {
       if (ra < N) y[(size_t)m0 * N + ra] = __float2half_rn(acc[tt][0]);
       if (rb < N) y[(size_t)m0 * N + rb] = __float2half_rn(acc[tt][2]);
@@ -288,7 +328,7 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const unsigned char* __restri
 }
 
 template <int G, int KSL, int T>
-int launch_cfg(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
+int launch_cfg(const void* x, const CUtensorMap& wmap, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
                int vec_scales, cudaStream_t stream) {
   static bool attr_done[64] = {};   // per device: opt in to more than 48 KB of dynamic shared memory
   int dev = 0;
@@ -299,15 +339,16 @@ int launch_cfg(const void* x, const void* packed, const void* scales, void* y, i
   }
   unsigned int* status = device_status_word();
   if (!status) return KFB_ERR_CUDA;
-  int4_gemv_mma_kernel<G, KSL, T><<<grid, kThreads, smem, stream>>>((const __half*)x, (const unsigned char*)packed,
-                                                                    (const __half*)scales, (__half*)y, M, N, K, vec_scales, status);
+  int4_gemv_mma_kernel<G, KSL, T><<<grid, kThreads, smem, stream>>>((const __half*)x, wmap, (const __half*)scales, (__half*)y,
+                                                                    M, N, K, vec_scales, status,
+                                                                    make_uint4(0x000F000Fu, 0x00F000F0u, 0x74007400u, 0x64006400u));
   KFB_LAUNCH_CHECK("int4_gemv_mma_kernel");
   return KFB_OK;
 }
 
-// Two row tiles per warp once that still gives every SM two CTAs' worth of rows; below that one tile per warp and K
+// Two row tiles per warp once that still gives every SM four CTAs' worth of rows; below that one tile per warp and K
 // split over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks).
-inline int pick_tiles(int N) { return (long long)N >= 2LL * 32 * kWarps * sm_count() ? 2 : 1; }
+inline int pick_tiles(int N) { return (long long)N >= 4LL * 32 * kWarps * sm_count() ? 2 : 1; }
 template <int G>
 inline bool fits(int N, int K) {
   return (pick_tiles(N) == 2 ? smem_bytes<2>(K / G) : smem_bytes<1>(K / G)) <= 227u * 1024u;
@@ -319,16 +360,20 @@ int launch_t(const void* x, const void* packed, const void* scales, void* y, int
   const int rounds = K / G, n_chunks = ceil_div(rounds, C);
   const int tiles = ceil_div(N, kTileRows * T);
   int ksl = 0;
-  const long long want = (T == 2 ? 8LL : 16LL) * sm_count();
+  const long long want = 16LL * sm_count();
   while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= n_chunks) ++ksl;
   const int grid = ceil_div(tiles, kWarps >> ksl);
   const size_t smem = smem_bytes<T>(rounds);
   const int vec = (rounds % C == 0) && aligned16(scales);
+  CUtensorMap wmap;   // packed matrix as [N rows][K / 8 words], box = R rows x 32 words, 128-byte swizzle
+  if (int rc = make_tmap_2d_plain(&wmap, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
+                                  kTileRows * T, /*swizzle128=*/true))
+    return rc;
   switch (ksl) {
-    case 0: return launch_cfg<G, 0, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
-    case 1: return launch_cfg<G, 1, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
-    case 2: return launch_cfg<G, 2, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
-    default: return launch_cfg<G, 3, T>(x, packed, scales, y, M, N, K, grid, smem, vec, stream);
+    case 0: return launch_cfg<G, 0, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
+    case 1: return launch_cfg<G, 1, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
+    case 2: return launch_cfg<G, 2, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
+    default: return launch_cfg<G, 3, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
   }
 }
 
