@@ -113,7 +113,7 @@ inline size_t smem_bytes(int rounds) { return 1024 + sx_offset<T>() + (size_t)ro
 // ...  T: MMA row tiles (16 rows) per warp.  `vec_scales`: every chunk is full and the scale rows are aligned, so the
 // scales of a chunk are one vector load per row.
 template <int G, int KSL, int T>
-__global__ void __launch_bounds__(kThreads, T == 1 ? 3 : 2)
+__global__ void __launch_bounds__(kThreads, 2)
 int4_gemv_mma_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ scales,
                      __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status, const uint4 unpack) {
   constexpr int W = G / 32;            // packed words per lane per row per round
@@ -243,54 +243,75 @@ int4_gemv_mma_kernel(const __half* __restrict__ x, const __grid_constant__ CUten
     }
     if (!__all_sync(0xffffffffu, wait_stage(&my_bars[i % kStages], (uint32_t)(i / kStages) & 1u, ctx))) break;
     const uint32_t st = my_ring + (uint32_t)(i % kStages) * kStage;
-    const __half* px = xrow + (size_t)r0 * G;
-    const float* psx = sx + r0 * 8 + t * 2;   // columns 2t, 2t+1
+    // Rounds are computed two at a time.  Rounds past the end of K (last chunk only; their weights are TMA zero fill
+    // and their scales zero) read the activations of the chunk's first round instead of running past x.
+    const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
 #pragma unroll
-    for (int u = 0; u < C; ++u) {
-      if (u < nr) {   // warp-uniform
-        uint32_t xs[W * 4];
+    for (int h = 0; h < C; h += 2) {
+      const __half* px[2];
+      float2 cs[2];   // corrections of columns 2t, 2t+1
+      uint32_t w[2][2 * T][W];
 #pragma unroll
-        for (int j = 0; j < W; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4*>(px + u * G + j * 8);
-          xs[4 * j + 0] = v.x; xs[4 * j + 1] = v.y; xs[4 * j + 2] = v.z; xs[4 * j + 3] = v.w;
-        }
-        const float2 cs = *reinterpret_cast<const float2*>(psx + u * 8);
-        uint32_t w[2 * T][W];
+      for (int v = 0; v < 2; ++v) {
+        const int ue = h + v < nr ? h + v : 0;
+        px[v] = xrow + (size_t)(r0 + ue) * G;
+        cs[v] = *reinterpret_cast<const float2*>(sx + (r0 + ue) * 8 + t * 2);
 #pragma unroll
         for (int k = 0; k < 2 * T; ++k) {
-          const uint32_t a = st + off[u] + k * 8 * kChunkBytes;
+          const uint32_t a = st + off[h + v] + k * 8 * kChunkBytes;
           if constexpr (W == 4)
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[k][0]), "=r"(w[k][1]), "=r"(w[k][2]), "=r"(w[k][3]) : "r"(a));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]), "=r"(w[v][k][2]), "=r"(w[v][k][3]) : "r"(a));
           else
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[k][0]), "=r"(w[k][1]) : "r"(a));
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]) : "r"(a));
         }
-        const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
+      }
+      // kAcc accumulators per (round, tile).  The MMAs are issued word by word and half word by half word across all
+      // (round, tile) pairs, so that two MMAs on the same accumulator are 2 T * kAcc MMAs apart (asm volatile keeps
+      // this order).
+      constexpr int kAcc = T == 1 ? 2 : 1;
+      float ca[2][T][kAcc][4];
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        uint4 xv[2];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
+#pragma unroll
+        for (int v = 0; v < 2; ++v) xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int v = 0; v < 2; ++v)
+#pragma unroll
+            for (int tt = 0; tt < T; ++tt) {
+              const uint32_t lo = w[v][2 * tt][j] >> (8 * half), hi = w[v][2 * tt + 1][j] >> (8 * half);
+              float(&c)[4] = ca[v][tt][half % kAcc];
+              const bool first = j == 0 && half < kAcc;
+              mma16816_f16(c, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
+                           and_or(hi, kMaskB, kMagicB), half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
+            }
+        if (j == 0 && h + 2 >= C) {
+          // every shared load of this stage has delivered (each one's first word has just been consumed): refill it
+          __syncwarp();
+          if (i + kStages < n_c) issue(i + kStages);
+        }
+      }
+      // remove the offsets of the unsigned forms and apply the group scale
+#pragma unroll
+      for (int v = 0; v < 2; ++v)
 #pragma unroll
         for (int tt = 0; tt < T; ++tt) {
-          float ca[4], cb[4];   // two accumulators, alternating, so that consecutive MMAs do not depend on each other
-#pragma unroll
-          for (int j = 0; j < W; ++j) {
-            const uint32_t lo = w[2 * tt][j], hi = w[2 * tt + 1][j], lo8 = lo >> 8, hi8 = hi >> 8;
-            // xs[4j + p] holds the activation pair multiplied by nibble pair p of word j
-            mma16816_f16(ca, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
-                         and_or(hi, kMaskB, kMagicB), xs[4 * j + 0], xs[4 * j + 1], j == 0 ? zero : ca);
-            mma16816_f16(cb, and_or(lo8, kMaskA, kMagicA), and_or(hi8, kMaskA, kMagicA), and_or(lo8, kMaskB, kMagicB),
-                         and_or(hi8, kMaskB, kMagicB), xs[4 * j + 2], xs[4 * j + 3], j == 0 ? zero : cb);
-          }
-          // remove the offsets of the unsigned forms and apply the group scale
+          const int u = h + v;
           const __half2 s2lo = *reinterpret_cast<const __half2*>(&sc[2 * tt][u / 2]);
           const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
           const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
           const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
-          acc[tt][0] = fmaf(s_lo, fmaf(ca[0] + cb[0], 0.0625f, cs.x), acc[tt][0]);
-          acc[tt][1] = fmaf(s_lo, fmaf(ca[1] + cb[1], 0.0625f, cs.y), acc[tt][1]);
-          acc[tt][2] = fmaf(s_hi, fmaf(ca[2] + cb[2], 0.0625f, cs.x), acc[tt][2]);
-          acc[tt][3] = fmaf(s_hi, fmaf(ca[3] + cb[3], 0.0625f, cs.y), acc[tt][3]);
+          float d[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d[e] = kAcc == 2 ? ca[v][tt][0][e] + ca[v][tt][kAcc - 1][e] : ca[v][tt][0][e];
+          acc[tt][0] = fmaf(s_lo, fmaf(d[0], 0.0625f, cs[v].x), acc[tt][0]);
+          acc[tt][1] = fmaf(s_lo, fmaf(d[1], 0.0625f, cs[v].y), acc[tt][1]);
+          acc[tt][2] = fmaf(s_hi, fmaf(d[2], 0.0625f, cs[v].x), acc[tt][2]);
+          acc[tt][3] = fmaf(s_hi, fmaf(d[3], 0.0625f, cs[v].y), acc[tt][3]);
         }
-      }
     }
-    __syncwarp();   // every lane has its words of this stage in registers: the stage may be refilled
-    if (i + kStages < n_c) issue(i + kStages);
   }
   if (*abort_word != 0) {   // a wait expired: give the copies still in flight time to land before the CTA retires
     const unsigned long long t0 = globaltimer_ns();
