@@ -331,7 +331,7 @@ extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scal
   // KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel; it is also used for the programmatic-dependent-
   // launch flag, which only that kernel implements, and when the class sums would not fit in shared memory.
   static const bool cuda_core = [] { const char* e = getenv("KFB_GEMV_IMPL"); return e && e[0] == 'c'; }();
-  if (!cuda_core && !(flags & 1) && (group == 128 ? gemv_mma::fits<128>(N, K) : gemv_mma::fits<64>(N, K)))
+  if (!cuda_core && !(flags & 1) && (group == 128 ? gemv_mma::fits<128>(K) : gemv_mma::fits<64>(K)))
     return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, s)
                         : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, s);
   return group == 128 ? gemv::pick_m<128>(x, packed, scales, y, M, N, K, flags, s)

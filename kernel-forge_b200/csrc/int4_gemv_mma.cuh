@@ -20,6 +20,12 @@
 //     request per ~29 clocks per SM -> one tiled copy (tensor map over the packed matrix, box = R rows x 128 bytes)
 //     per warp and chunk, 2 or 4 KB per request.
 //
+//  5. tail and prologue: with one CTA per 256 rows the last wave of CTAs is partly empty (2.4 waves at N = 180224:
+//     21 % of the time) and every CTA waits ~2 us at the barrier behind the class sums -> for large N the kernel
+//     is persistent (two CTAs per SM, class sums once), every warp owns a contiguous range of 16-row tiles whose
+//     length differs by at most one between warps, processed as pairs plus one single tile, and its ring keeps
+//     streaming across tile boundaries.
+//
 // Shared-memory stage of a warp: R = 16 or 32 rows x 128 bytes (2 rounds of G = 128, 4 of G = 64), written by the TMA
 // with the 128-byte swizzle (16-byte piece j of row r sits at piece j ^ (r & 7)).  Fragment row slot g of a tile
 // holds matrix row p(g) = 4 (g & 1) + (g >> 1) (and p(g) + 8): the eight lanes of one 128-bit shared load then read
@@ -48,6 +54,9 @@
 
 #include "common.cuh"
 #include "sm100.cuh"
+
+#include <cstdlib>
+#include <type_traits>
 
 namespace kfb {
 namespace gemv_mma {
@@ -98,310 +107,453 @@ __device__ __forceinline__ bool wait_stage(uint64_t* bar, uint32_t parity, const
   return true;
 }
 
-template <int T>
-__host__ __device__ constexpr uint32_t stage_bytes() { return 16u * T * kChunkBytes; }
-// chunks in flight per warp: 12 KB (T = 2, two CTAs per SM) or 8 KB (T = 1, three CTAs per SM)
-template <int T>
-__host__ __device__ constexpr int stages() { return T == 2 ? 3 : 4; }
-// (ring, 1024-byte aligned) | mbarriers | abort word | class sums.  The cross-warp reduction reuses the ring.
-template <int T>
-__host__ __device__ constexpr size_t sx_offset() { return (size_t)kWarps * stages<T>() * stage_bytes<T>() + kWarps * stages<T>() * 8 + 16; }
-template <int T>
-inline size_t smem_bytes(int rounds) { return 1024 + sx_offset<T>() + (size_t)rounds * 8 * sizeof(float); }
+// Shared memory of a CTA: (ring, 1024-byte aligned: kWarps x S stages of RT row tiles) | mbarriers | abort word |
+// class sums.  The split-K reduction reuses the ring.
+__host__ __device__ constexpr uint32_t stage_bytes(int RT) { return (uint32_t)(kTileRows * RT * kChunkBytes); }
+__host__ __device__ constexpr size_t sx_offset(int RT, int S) { return (size_t)kWarps * S * stage_bytes(RT) + kWarps * S * 8 + 16; }
+inline size_t smem_bytes(int RT, int S, int rounds) { return 1024 + sx_offset(RT, S) + (size_t)rounds * 8 * sizeof(float); }
 
-// G: scale group size (128 or 64).  KS = 1 << KSL warps of a CTA share a row tile and take chunks kpart, kpart + KS,
-// ...  T: MMA row tiles (16 rows) per warp.  `vec_scales`: every chunk is full and the scale rows are aligned, so the
-// scales of a chunk are one vector load per row.
-template <int G, int KSL, int T>
+// What a lane needs to find its words and its activations; the same for every tile.
+template <int G>
+struct LaneMap {
+  static constexpr int W = G / 32;                   // packed words per lane per row per round
+  static constexpr int C = kChunkBytes / (G / 2);    // rounds per chunk (2 or 4)
+  int g, t, pg;         // lane = 4 g + t; fragment row slot g holds matrix rows pg + 8 k of the warp's rows
+  uint32_t off[C];      // position of this lane's words of round u inside a stage (row pg, swizzled 16-byte piece)
+  const __half* xrow;   // column g of the B operand (a valid row when g >= M), at this lane's k offset
+  __device__ __forceinline__ LaneMap(int lane, const __half* x, int M, int K) {
+    g = lane >> 2;
+    t = lane & 3;
+    pg = ((g & 1) << 2) | (g >> 1);
+#pragma unroll
+    for (int u = 0; u < C; ++u) {
+      const uint32_t byte = (uint32_t)u * (G / 2) + (uint32_t)t * (W * 4);
+      off[u] = (uint32_t)pg * kChunkBytes + ((((byte >> 4) ^ (uint32_t)pg) << 4) | (byte & 15u));
+    }
+    xrow = x + (size_t)min(g, M - 1) * K + t * (G / 4);
+  }
+};
+
+// Class sums of the activations, once per CTA: sx[round][column] = -1032 SxA - 72 SxB.  Four lanes share one
+// (round, batch row): each sums a quarter of the group (whole packed words: pairs 0, 2 of a word meet the 16384 + 16 u
+// form, pairs 1, 3 the 1024 + 16 u form), then a quad reduction.  Ends with the CTA barrier.
+template <int G>
+__device__ __forceinline__ void class_sums(const __half* __restrict__ x, int M, int K, float* sx) {
+  const int rounds = K / G;
+  for (int i = threadIdx.x; i < rounds * 8; i += kThreads)
+    if ((i & 7) >= M) sx[i] = 0.f;
+  const int q = threadIdx.x & 3, items = rounds * M;
+  for (int base = 0; base < items; base += kThreads / 4) {
+    const int item = base + (threadIdx.x >> 2);
+    const bool live = item < items;
+    const int rd = live ? item / M : 0, m = live ? item - rd * M : 0;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)rd * G + q * (G / 4));
+    float sa = 0.f, sb = 0.f;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < G / 32; ++i) {
+        const uint4 v = xr[i];
+        const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+        const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+        sa += (p0.x + p0.y) + (p2.x + p2.y);
+        sb += (p1.x + p1.y) + (p3.x + p3.y);
+      }
+    }
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+    sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+    if (live && q == 0) sx[rd * 8 + m] = fmaf(sa, -1032.0f, sb * -72.0f);
+  }
+  __syncthreads();
+}
+
+// Group scales of one chunk for this lane's 2 T rows, raw fp16 bits: sc[k][u / 2] holds rounds u (low half), u + 1.
+// `vec`: every chunk is full and the scale rows are aligned, so a chunk's scales are one vector load per row.
+template <int G, int T>
+__device__ __forceinline__ void load_scales(const __half* const (&srow)[2 * T], int r0, int nr, int vec,
+                                            uint32_t (&sc)[2 * T][LaneMap<G>::C / 2]) {
+  constexpr int C = LaneMap<G>::C;
+  if (vec) {
+#pragma unroll
+    for (int k = 0; k < 2 * T; ++k) {
+      if constexpr (C == 2) {
+        sc[k][0] = *reinterpret_cast<const uint32_t*>(srow[k] + r0);
+      } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(srow[k] + r0);
+        sc[k][0] = v.x; sc[k][1] = v.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 2 * T; ++k)
+#pragma unroll
+      for (int u = 0; u < C; u += 2) {
+        const uint32_t a = u < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u]) : 0u;
+        const uint32_t b = u + 1 < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u + 1]) : 0u;
+        sc[k][u / 2] = a | (b << 16);
+      }
+  }
+}
+
+// One chunk (C rounds) of T row tiles out of the stage at shared address `st` (already complete).  `refill` runs once
+// every shared load of the stage has delivered, i.e. as early as the stage may be handed back to the TMA.
+template <int G, int T, int RG, class Refill>
+__device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st, const float* sx, int r0, int nr,
+                                              const uint32_t (&sc)[2 * T][LaneMap<G>::C / 2], const uint4& unpack,
+                                              float (&acc)[T][4], Refill&& refill) {
+  constexpr int W = LaneMap<G>::W, C = LaneMap<G>::C;
+  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
+  // Rounds are computed RG (1 or 2) at a time.  Rounds past the end of K (last chunk only; their weights are TMA zero fill
+  // and their scales zero) read the activations of the chunk's first round instead of running past x.
+#pragma unroll
+  for (int h = 0; h < C; h += RG) {
+    const __half* px[RG];
+    float2 cs[RG];   // corrections of columns 2t, 2t+1
+    uint32_t w[RG][2 * T][W];
+#pragma unroll
+    for (int v = 0; v < RG; ++v) {
+      const int ue = h + v < nr ? h + v : 0;
+      px[v] = lm.xrow + (size_t)(r0 + ue) * G;
+      cs[v] = *reinterpret_cast<const float2*>(sx + (r0 + ue) * 8 + lm.t * 2);
+#pragma unroll
+      for (int k = 0; k < 2 * T; ++k) {
+        const uint32_t a = st + lm.off[h + v] + k * 8 * kChunkBytes;
+        if constexpr (W == 4)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]), "=r"(w[v][k][2]), "=r"(w[v][k][3]) : "r"(a));
+        else
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]) : "r"(a));
+      }
+    }
+    // kAcc accumulators per (round, tile).  The MMAs are issued word by word and half word by half word across all
+    // (round, tile) pairs, so that two MMAs on the same accumulator are 2 T * kAcc MMAs apart (asm volatile keeps
+    // this order).
+    constexpr int kAcc = T * RG >= 4 ? 1 : 2;
+    float ca[RG][T][kAcc][4];
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      uint4 xv[RG];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
+#pragma unroll
+      for (int v = 0; v < RG; ++v) xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int v = 0; v < RG; ++v)
+#pragma unroll
+          for (int tt = 0; tt < T; ++tt) {
+            const uint32_t lo = w[v][2 * tt][j] >> (8 * half), hi = w[v][2 * tt + 1][j] >> (8 * half);
+            float(&c)[4] = ca[v][tt][half % kAcc];
+            const bool first = j == 0 && half < kAcc;
+            mma16816_f16(c, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
+                         and_or(hi, kMaskB, kMagicB), half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
+          }
+      if (j == 0 && h + RG >= C) refill();   // each shared load's first word has just been consumed
+    }
+    // remove the offsets of the unsigned forms and apply the group scale
+#pragma unroll
+    for (int v = 0; v < RG; ++v)
+#pragma unroll
+      for (int tt = 0; tt < T; ++tt) {
+        const int u = h + v;
+        const __half2 s2lo = *reinterpret_cast<const __half2*>(&sc[2 * tt][u / 2]);
+        const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
+        const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
+        const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
+        float d[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d[e] = kAcc == 2 ? ca[v][tt][0][e] + ca[v][tt][kAcc - 1][e] : ca[v][tt][0][e];
+        acc[tt][0] = fmaf(s_lo, fmaf(d[0], 0.0625f, cs[v].x), acc[tt][0]);
+        acc[tt][1] = fmaf(s_lo, fmaf(d[1], 0.0625f, cs[v].y), acc[tt][1]);
+        acc[tt][2] = fmaf(s_hi, fmaf(d[2], 0.0625f, cs[v].x), acc[tt][2]);
+        acc[tt][3] = fmaf(s_hi, fmaf(d[3], 0.0625f, cs[v].y), acc[tt][3]);
+      }
+  }
+}
+
+// Stores rows row0 + pg, row0 + pg + 8 of columns 2t, 2t+1 (acc = {row lo col 2t, row lo col 2t+1, row hi ...}).
+__device__ __forceinline__ void store_tile(__half* __restrict__ y, const float (&acc)[4], int row0, int pg, int t, int M, int N) {
+  const int ra = row0 + pg, rb = ra + 8, m0 = 2 * t, m1 = 2 * t + 1;
+  if (m0 < M) {
+    if (ra < N) y[(size_t)m0 * N + ra] = __float2half_rn(acc[0]);
+    if (rb < N) y[(size_t)m0 * N + rb] = __float2half_rn(acc[2]);
+  }
+  if (m1 < M) {
+    if (ra < N) y[(size_t)m1 * N + ra] = __float2half_rn(acc[1]);
+    if (rb < N) y[(size_t)m1 * N + rb] = __float2half_rn(acc[3]);
+  }
+}
+
+__device__ __forceinline__ void linger_after_abort(volatile uint32_t* abort_word) {
+  if (*abort_word != 0) {   // a wait expired: give the copies still in flight time to land before the CTA retires
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Kernel for small and medium N: one 16-row tile per warp, KS = 1 << KSL warps of a CTA share a tile and take chunks
+// kpart, kpart + KS, ... ; partial sums meet in shared memory in a fixed order.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kSplitStages = 4;   // 8 KB in flight per warp
+
+template <int G, int KSL>
 __global__ void __launch_bounds__(kThreads, 2)
-int4_gemv_mma_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ scales,
-                     __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status, const uint4 unpack) {
-  constexpr int W = G / 32;            // packed words per lane per row per round
-  constexpr int kLaneK = G / 4;        // k per lane per round (32 or 16)
-  constexpr int KS = 1 << KSL;
-  constexpr int C = kChunkBytes / (G / 2);   // rounds per chunk (2 or 4)
-  constexpr int R = kTileRows * T;           // rows per warp
-  constexpr int kStages = stages<T>();
-  constexpr uint32_t kStage = stage_bytes<T>();
+int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap16,
+                           const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K, int vec_scales,
+                           unsigned int* status, const uint4 unpack) {
+  constexpr int C = LaneMap<G>::C, KS = 1 << KSL, S = kSplitStages;
+  constexpr uint32_t kStage = stage_bytes(1);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // the swizzle pattern is 1024-byte periodic
   const int rounds = K / G;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages * kStage);
-  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * kStages);
-  float* sx = reinterpret_cast<float*>(smem + sx_offset<T>());   // [rounds][8 columns]: -1032 SxA - 72 SxB
-  float* red = reinterpret_cast<float*>(smem);                   // [kWarps][32 lanes][T][4], after the main loop
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * S * kStage);
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * S);
+  float* sx = reinterpret_cast<float*>(smem + sx_offset(1, S));
+  float* red = reinterpret_cast<float*>(smem);   // [kWarps][32 lanes][4], after the main loop
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
 
   const int tile = blockIdx.x * (kWarps >> KSL) + (warp >> KSL);
   const int kpart = warp & (KS - 1);
-  const int row0 = tile * R;
+  const int row0 = tile * kTileRows;
   // chunks of this warp: c(i) = kpart + i * KS, i < n_c (none for a tile past N)
   const int n_chunks = (rounds + C - 1) / C;
   const int n_c = row0 < N ? (n_chunks - kpart + KS - 1) >> KSL : 0;
 
-  uint64_t* my_bars = bars + warp * kStages;
-  const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * kStages * kStage;
+  uint64_t* my_bars = bars + warp * S;
+  const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * S * kStage;
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], 1);
+    for (int s = 0; s < S; ++s) mbar_init(&my_bars[s], 1);
     fence_mbar_init();
   }
   if (threadIdx.x == 0) *abort_word = 0;
   __syncwarp();
 
-  auto issue = [&](int i) {   // one tiled copy: R rows x 128 bytes of chunk c(i)
+  auto issue = [&](int i) {   // one tiled copy: 16 rows x 128 bytes of chunk c(i)
     if (lane == 0) {
-      const int c = kpart + (i << KSL), st = i % kStages;
+      const int c = kpart + (i << KSL), st = i % S;
       mbar_arrive_expect_tx(&my_bars[st], kStage);
-      tma_load_2d(smem + (size_t)(warp * kStages + st) * kStage, &wmap, &my_bars[st], c * (kChunkBytes / 4), row0);
+      tma_load_2d(smem + (size_t)(warp * S + st) * kStage, &wmap16, &my_bars[st], c * (kChunkBytes / 4), row0);
     }
   };
   // the weight stream starts before anything else: the class sums below run under its latency
 #pragma unroll
-  for (int i = 0; i < kStages; ++i)
+  for (int i = 0; i < S; ++i)
     if (i < n_c) issue(i);
 
-  // ---- class sums of the activations, once per CTA.  Four lanes share one (round, batch row): each sums a quarter
-  // of the group (whole packed words: pairs 0, 2 of a word are class A, pairs 1, 3 class B), then a quad reduction.
-  for (int i = threadIdx.x; i < rounds * 8; i += kThreads)
-    if ((i & 7) >= M) sx[i] = 0.f;
-  {
-    const int q = threadIdx.x & 3, items = rounds * M;
-    for (int base = 0; base < items; base += kThreads / 4) {
-      const int item = base + (threadIdx.x >> 2);
-      const bool live = item < items;
-      const int rd = live ? item / M : 0, m = live ? item - rd * M : 0;
-      const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)rd * G + q * (G / 4));
-      float sa = 0.f, sb = 0.f;
-      if (live) {
-#pragma unroll
-        for (int i = 0; i < G / 32; ++i) {
-          const uint4 v = xr[i];
-          const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-          const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-          const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
-          const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
-          sa += (p0.x + p0.y) + (p2.x + p2.y);
-          sb += (p1.x + p1.y) + (p3.x + p3.y);
-        }
-      }
-      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-      sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-      sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-      if (live && q == 0) {
-        sx[rd * 8 + m] = fmaf(sa, -1032.0f, sb * -72.0f);
-      }
-    }
-  }
-  __syncthreads();
+  class_sums<G>(x, M, K, sx);
 
   const AbortCtx ctx{abort_word, status};
-  float acc[T][4];
+  const LaneMap<G> lm(lane, x, M, K);
+  float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+  const __half* srow[2];
 #pragma unroll
-  for (int tt = 0; tt < T; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
-  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-  // fragment row slot g holds matrix rows pg + 8 k (k < 2 T) of the warp's rows; off[u] = position of this lane's
-  // words of round u inside a stage (row pg, swizzled 16-byte piece)
-  const int pg = ((g & 1) << 2) | (g >> 1);
-  uint32_t off[C];
-#pragma unroll
-  for (int u = 0; u < C; ++u) {
-    const uint32_t byte = (uint32_t)u * (G / 2) + (uint32_t)t * (W * 4);
-    off[u] = (uint32_t)pg * kChunkBytes + ((((byte >> 4) ^ (uint32_t)pg) << 4) | (byte & 15u));
-  }
-  const __half* xrow = x + (size_t)min(g, M - 1) * K + t * kLaneK;   // column g of the B operand
-  const __half* srow[2 * T];
-#pragma unroll
-  for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + pg + 8 * k, N - 1) * rounds;
+  for (int k = 0; k < 2; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
 
   for (int i = 0; i < n_c; ++i) {
-    const int c = kpart + (i << KSL);
-    const int r0 = c * C, nr = min(C, rounds - r0);
-    // group scales of the chunk, raw fp16 bits: sc[k][u / 2] holds rounds u (low half) and u + 1
-    uint32_t sc[2 * T][C / 2];
-    if (vec_scales) {
-#pragma unroll
-      for (int k = 0; k < 2 * T; ++k) {
-        if constexpr (C == 2) {
-          sc[k][0] = *reinterpret_cast<const uint32_t*>(srow[k] + r0);
-        } else {
-          const uint2 v = *reinterpret_cast<const uint2*>(srow[k] + r0);
-          sc[k][0] = v.x; sc[k][1] = v.y;
-        }
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 2 * T; ++k)
-#pragma unroll
-        for (int u = 0; u < C; u += 2) {
-          const uint32_t a = u < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u]) : 0u;
-          const uint32_t b = u + 1 < nr ? (uint32_t)__half_as_ushort(srow[k][r0 + u + 1]) : 0u;
-          sc[k][u / 2] = a | (b << 16);
-        }
-    }
-    if (!__all_sync(0xffffffffu, wait_stage(&my_bars[i % kStages], (uint32_t)(i / kStages) & 1u, ctx))) break;
-    const uint32_t st = my_ring + (uint32_t)(i % kStages) * kStage;
-    // Rounds are computed two at a time.  Rounds past the end of K (last chunk only; their weights are TMA zero fill
-    // and their scales zero) read the activations of the chunk's first round instead of running past x.
-    const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
-#pragma unroll
-    for (int h = 0; h < C; h += 2) {
-      const __half* px[2];
-      float2 cs[2];   // corrections of columns 2t, 2t+1
-      uint32_t w[2][2 * T][W];
-#pragma unroll
-      for (int v = 0; v < 2; ++v) {
-        const int ue = h + v < nr ? h + v : 0;
-        px[v] = xrow + (size_t)(r0 + ue) * G;
-        cs[v] = *reinterpret_cast<const float2*>(sx + (r0 + ue) * 8 + t * 2);
-#pragma unroll
-        for (int k = 0; k < 2 * T; ++k) {
-          const uint32_t a = st + off[h + v] + k * 8 * kChunkBytes;
-          if constexpr (W == 4)
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]), "=r"(w[v][k][2]), "=r"(w[v][k][3]) : "r"(a));
-          else
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]) : "r"(a));
-        }
-      }
-      // kAcc accumulators per (round, tile).  The MMAs are issued word by word and half word by half word across all
-      // (round, tile) pairs, so that two MMAs on the same accumulator are 2 T * kAcc MMAs apart (asm volatile keeps
-      // this order).
-      constexpr int kAcc = T == 1 ? 2 : 1;
-      float ca[2][T][kAcc][4];
-#pragma unroll
-      for (int j = 0; j < W; ++j) {
-        uint4 xv[2];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
-#pragma unroll
-        for (int v = 0; v < 2; ++v) xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
-#pragma unroll
-        for (int half = 0; half < 2; ++half)
-#pragma unroll
-          for (int v = 0; v < 2; ++v)
-#pragma unroll
-            for (int tt = 0; tt < T; ++tt) {
-              const uint32_t lo = w[v][2 * tt][j] >> (8 * half), hi = w[v][2 * tt + 1][j] >> (8 * half);
-              float(&c)[4] = ca[v][tt][half % kAcc];
-              const bool first = j == 0 && half < kAcc;
-              mma16816_f16(c, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
-                           and_or(hi, kMaskB, kMagicB), half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
-            }
-        if (j == 0 && h + 2 >= C) {
-          // every shared load of this stage has delivered (each one's first word has just been consumed): refill it
-          __syncwarp();
-          if (i + kStages < n_c) issue(i + kStages);
-        }
-      }
-      // remove the offsets of the unsigned forms and apply the group scale
-#pragma unroll
-      for (int v = 0; v < 2; ++v)
-#pragma unroll
-        for (int tt = 0; tt < T; ++tt) {
-          const int u = h + v;
-          const __half2 s2lo = *reinterpret_cast<const __half2*>(&sc[2 * tt][u / 2]);
-          const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
-          const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
-          const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
-          float d[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) d[e] = kAcc == 2 ? ca[v][tt][0][e] + ca[v][tt][kAcc - 1][e] : ca[v][tt][0][e];
-          acc[tt][0] = fmaf(s_lo, fmaf(d[0], 0.0625f, cs[v].x), acc[tt][0]);
-          acc[tt][1] = fmaf(s_lo, fmaf(d[1], 0.0625f, cs[v].y), acc[tt][1]);
-          acc[tt][2] = fmaf(s_hi, fmaf(d[2], 0.0625f, cs[v].x), acc[tt][2]);
-          acc[tt][3] = fmaf(s_hi, fmaf(d[3], 0.0625f, cs[v].y), acc[tt][3]);
-        }
-    }
+    const int r0 = (kpart + (i << KSL)) * C, nr = min(C, rounds - r0);
+    uint32_t sc[2][C / 2];
+    load_scales<G, 1>(srow, r0, nr, vec_scales, sc);
+    if (!__all_sync(0xffffffffu, wait_stage(&my_bars[i % S], (uint32_t)(i / S) & 1u, ctx))) break;
+    chunk_compute<G, 1, 2>(lm, my_ring + (uint32_t)(i % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+      __syncwarp();
+      if (i + S < n_c) issue(i + S);
+    });
   }
-  if (*abort_word != 0) {   // a wait expired: give the copies still in flight time to land before the CTA retires
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-  }
+  linger_after_abort(abort_word);
 
   if constexpr (KSL != 0) {
     __syncthreads();   // all warps are past their last stage: the ring becomes the reduction buffer
-    float4* mine = reinterpret_cast<float4*>(red + (size_t)(warp * 32 + lane) * T * 4);
-#pragma unroll
-    for (int tt = 0; tt < T; ++tt) mine[tt] = make_float4(acc[tt][0], acc[tt][1], acc[tt][2], acc[tt][3]);
+    *reinterpret_cast<float4*>(red + (warp * 32 + lane) * 4) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
     __syncthreads();
     if (kpart != 0) return;
     for (int p = 1; p < KS; ++p) {  // fixed order
-      const float4* o = reinterpret_cast<const float4*>(red + (size_t)((warp + p) * 32 + lane) * T * 4);
-#pragma unroll
-      for (int tt = 0; tt < T; ++tt) {
-        acc[tt][0] += o[tt].x; acc[tt][1] += o[tt].y; acc[tt][2] += o[tt].z; acc[tt][3] += o[tt].w;
-      }
+      const float4 o = *reinterpret_cast<const float4*>(red + ((warp + p) * 32 + lane) * 4);
+      acc[0][0] += o.x; acc[0][1] += o.y; acc[0][2] += o.z; acc[0][3] += o.w;
     }
   }
-  const int m0 = 2 * t, m1 = 2 * t + 1;
-#pragma unroll
-  for (int tt = 0; tt < T; ++tt) {
-    const int ra = row0 + tt * kTileRows + pg, rb = ra + 8;
-    if (m0 < M) {
-      if (ra < N) y[(size_t)m0 * N + ra] = __float2half_rn(acc[tt][0]);
-      if (rb < N) y[(size_t)m0 * N + rb] = __float2half_rn(acc[tt][2]);
-    }
-    if (m1 < M) {
-      if (ra < N) y[(size_t)m1 * N + ra] = __float2half_rn(acc[tt][1]);
-      if (rb < N) y[(size_t)m1 * N + rb] = __float2half_rn(acc[tt][3]);
-    }
-  }
+  store_tile(y, acc[0], row0, lm.pg, lm.t, M, N);
 }
 
-template <int G, int KSL, int T>
-int launch_cfg(const void* x, const CUtensorMap& wmap, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
-               int vec_scales, cudaStream_t stream) {
-  static bool attr_done[64] = {};   // per device: opt in to more than 48 KB of dynamic shared memory
+// ---------------------------------------------------------------------------------------------------------------
+// Kernel for large N: persistent, two CTAs per SM.  Warp number gw of the grid owns the 16-row tiles
+// [first, first + count), count differing by at most one between warps; it processes them as pairs (one 32-row
+// copy per chunk, activation fragments shared by both tiles) and a final single tile when count is odd.  The
+// ring runs ahead across tile boundaries: the producer and the consumer walk the same (step, chunk) sequence.
+// ---------------------------------------------------------------------------------------------------------------
+// TMAX: 2 = pairs + single as described, 1 = single tiles only (2 KB stages).  RG: rounds computed together.  MINB: CTAs
+// per SM the register allocation must allow.  S: stages.
+template <int G, int TMAX, int RG, int MINB, int S>
+__global__ void __launch_bounds__(kThreads, MINB)
+int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap32,
+                            const __grid_constant__ CUtensorMap wmap16, const __half* __restrict__ scales,
+                            __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status,
+                            const uint4 unpack) {
+  constexpr int C = LaneMap<G>::C;
+  constexpr uint32_t kStage = stage_bytes(TMAX);
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int rounds = K / G;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * S * kStage);
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * S);
+  float* sx = reinterpret_cast<float*>(smem + sx_offset(TMAX, S));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // this warp's range of 16-row tiles
+  const int tiles = (N + kTileRows - 1) / kTileRows;
+  const int gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
+  const int base = tiles / nw, extra = tiles - base * nw;
+  const int first = gw * base + min(gw, extra), count = base + (gw < extra ? 1 : 0);
+  const int n_pairs = TMAX == 2 ? count >> 1 : 0, n_steps = TMAX == 2 ? n_pairs + (count & 1) : count;
+  const int n_chunks = (rounds + C - 1) / C;
+  const int total = n_steps * n_chunks;   // chunks this warp streams
+
+  uint64_t* my_bars = bars + warp * S;
+  const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * S * kStage;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) mbar_init(&my_bars[s], 1);
+    fence_mbar_init();
+  }
+  if (threadIdx.x == 0) *abort_word = 0;
+  __syncwarp();
+
+  // producer side: next chunk to request = (p_step, p_chunk), the p_count-th of this warp
+  int p_step = 0, p_chunk = 0, p_count = 0;
+  auto issue_next = [&]() {
+    if (p_count < total) {
+      if (lane == 0) {
+        const int st = p_count % S;
+        const bool single = TMAX == 1 || p_step == n_pairs;   // a 16-row copy (a 32-row one would overrun a 2 KB stage)
+        mbar_arrive_expect_tx(&my_bars[st], single ? stage_bytes(1) : kStage);
+        tma_load_2d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st],
+                    p_chunk * (kChunkBytes / 4), (first + (TMAX == 2 ? 2 * p_step : p_step)) * kTileRows);
+      }
+      ++p_count;
+      if (++p_chunk == n_chunks) { p_chunk = 0; ++p_step; }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < S; ++i) issue_next();
+
+  class_sums<G>(x, M, K, sx);
+
+  const AbortCtx ctx{abort_word, status};
+  const LaneMap<G> lm(lane, x, M, K);
+  int q = 0;   // chunks consumed
+  bool ok = true;
+  auto run_step = [&](auto tag, int row0) {
+    constexpr int T = decltype(tag)::value;
+    float acc[T][4];
+#pragma unroll
+    for (int tt = 0; tt < T; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+    const __half* srow[2 * T];
+#pragma unroll
+    for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
+    for (int ci = 0; ci < n_chunks; ++ci, ++q) {
+      const int r0 = ci * C, nr = min(C, rounds - r0);
+      uint32_t sc[2 * T][C / 2];
+      load_scales<G, T>(srow, r0, nr, vec_scales, sc);
+      if (!__all_sync(0xffffffffu, wait_stage(&my_bars[q % S], (uint32_t)(q / S) & 1u, ctx))) { ok = false; return; }
+      chunk_compute<G, T, RG>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+        __syncwarp();
+        issue_next();
+      });
+    }
+#pragma unroll
+    for (int tt = 0; tt < T; ++tt) store_tile(y, acc[tt], row0 + tt * kTileRows, lm.pg, lm.t, M, N);
+  };
+  for (int step = 0; step < n_steps && ok; ++step) {
+    const int row0 = (first + (TMAX == 2 ? 2 * step : step)) * kTileRows;
+    if (TMAX == 2 && step < n_pairs) run_step(std::integral_constant<int, TMAX>{}, row0);
+    else run_step(std::integral_constant<int, 1>{}, row0);
+  }
+  linger_after_abort(abort_word);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------------
+template <auto kernel>
+int opt_in_shared_memory() {   // once per kernel instantiation and device: more than 48 KB of dynamic smem
+  static bool done[64] = {};
   int dev = 0;
   KFB_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_done[dev]) {
-    KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_mma_kernel<G, KSL, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_done[dev] = true;
+  if (dev < 64 && !done[dev]) {
+    KFB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    done[dev] = true;
   }
-  unsigned int* status = device_status_word();
-  if (!status) return KFB_ERR_CUDA;
-  int4_gemv_mma_kernel<G, KSL, T><<<grid, kThreads, smem, stream>>>((const __half*)x, wmap, (const __half*)scales, (__half*)y,
-                                                                    M, N, K, vec_scales, status,
-                                                                    make_uint4(0x000F000Fu, 0x00F000F0u, 0x74007400u, 0x64006400u));
-  KFB_LAUNCH_CHECK("int4_gemv_mma_kernel");
   return KFB_OK;
 }
 
-// Two row tiles per warp once that still gives every SM four CTAs' worth of rows; below that one tile per warp and K
-// split over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks).
-inline int pick_tiles(int N) { return (long long)N >= 4LL * 32 * kWarps * sm_count() ? 2 : 1; }
 template <int G>
-inline bool fits(int N, int K) {
-  return (pick_tiles(N) == 2 ? smem_bytes<2>(K / G) : smem_bytes<1>(K / G)) <= 227u * 1024u;
+inline bool fits(int K) {
+  const size_t a = smem_bytes(1, kSplitStages, K / G), b = smem_bytes(2, 3, K / G);
+  return (a > b ? a : b) <= 227u * 1024u;
 }
 
-template <int G, int T>
-int launch_t(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, cudaStream_t stream) {
-  constexpr int C = kChunkBytes / (G / 2);
-  const int rounds = K / G, n_chunks = ceil_div(rounds, C);
-  const int tiles = ceil_div(N, kTileRows * T);
-  int ksl = 0;
-  const long long want = 16LL * sm_count();
-  while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= n_chunks) ++ksl;
-  const int grid = ceil_div(tiles, kWarps >> ksl);
-  const size_t smem = smem_bytes<T>(rounds);
-  const int vec = (rounds % C == 0) && aligned16(scales);
-  CUtensorMap wmap;   // packed matrix as [N rows][K / 8 words], box = R rows x 32 words, 128-byte swizzle
-  if (int rc = make_tmap_2d_plain(&wmap, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
-                                  kTileRows * T, /*swizzle128=*/true))
-    return rc;
-  switch (ksl) {
-    case 0: return launch_cfg<G, 0, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
-    case 1: return launch_cfg<G, 1, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
-    case 2: return launch_cfg<G, 2, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
-    default: return launch_cfg<G, 3, T>(x, wmap, scales, y, M, N, K, grid, smem, vec, stream);
-  }
+template <int G, int KSL>
+int launch_split(const void* x, const CUtensorMap& wmap16, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
+                 int vec, unsigned int* status, const uint4& unpack, cudaStream_t stream) {
+  if (int rc = opt_in_shared_memory<int4_gemv_mma_split_kernel<G, KSL>>()) return rc;
+  int4_gemv_mma_split_kernel<G, KSL><<<grid, kThreads, smem, stream>>>((const __half*)x, wmap16, (const __half*)scales, (__half*)y,
+                                                                       M, N, K, vec, status, unpack);
+  KFB_LAUNCH_CHECK("int4_gemv_mma_split_kernel");
+  return KFB_OK;
 }
 
 template <int G>
 int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, cudaStream_t stream) {
-  return pick_tiles(N) == 2 ? launch_t<G, 2>(x, packed, scales, y, M, N, K, stream)
-                            : launch_t<G, 1>(x, packed, scales, y, M, N, K, stream);
+  constexpr int C = kChunkBytes / (G / 2);
+  const int rounds = K / G, n_chunks = ceil_div(rounds, C), tiles = ceil_div(N, kTileRows);
+  const int vec = (rounds % C == 0) && aligned16(scales);
+  const uint4 unpack = make_uint4(0x000F000Fu, 0x00F000F0u, 0x74007400u, 0x64006400u);
+  unsigned int* status = device_status_word();
+  if (!status) return KFB_ERR_CUDA;
+  // packed matrix as [N rows][K / 8 words]; box = 16 (or 32) rows x 32 words, 128-byte swizzle
+  CUtensorMap wmap16;
+  if (int rc = make_tmap_2d_plain(&wmap16, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
+                                  kTileRows, /*swizzle128=*/true))
+    return rc;
+  static const int cfg = [] { const char* e = getenv("KFB_GEMV_CFG"); return e ? atoi(e) : 0; }();
+  const int ctas_per_sm = cfg == 0 ? 2 : cfg == 1 ? 2 : cfg == 2 ? 3 : 4;
+  const int stream_warps = ctas_per_sm * sm_count() * kWarps;
+  if (tiles >= 2 * stream_warps) {   // every warp of a persistent grid gets at least two tiles
+    CUtensorMap wmap32;
+    if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
+                                    2 * kTileRows, true))
+      return rc;
+#define KFB_STREAM(TMAX, RG, MINB, S)                                                                                  \
+  do {                                                                                                                 \
+    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S>>()) return rc;                  \
+    int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S><<<MINB * sm_count(), kThreads, smem_bytes(TMAX, S, rounds), stream>>>( \
+        (const __half*)x, wmap32, wmap16, (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack);            \
+  } while (0)
+    switch (cfg) {
+      case 1: KFB_STREAM(1, 2, 2, 4); break;
+      case 2: KFB_STREAM(1, 1, 3, 4); break;
+      case 3: KFB_STREAM(1, 1, 4, 3); break;
+      default: KFB_STREAM(2, 2, 2, 3); break;
+    }
+#undef KFB_STREAM
+    KFB_LAUNCH_CHECK("int4_gemv_mma_stream_kernel");
+    return KFB_OK;
+  }
+  // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks)
+  int ksl = 0;
+  const long long want = 16LL * sm_count();
+  while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= n_chunks) ++ksl;
+  const int grid = ceil_div(tiles, kWarps >> ksl);
+  const size_t smem = smem_bytes(1, kSplitStages, rounds);
+  switch (ksl) {
+    case 0: return launch_split<G, 0>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
+    case 1: return launch_split<G, 1>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
+    case 2: return launch_split<G, 2>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
+    default: return launch_split<G, 3>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
+  }
 }
 
 }  // namespace gemv_mma

@@ -35,6 +35,29 @@ def test_gemv_ragged_n(n):
     run_case(ops.int4_gemv, 3, n, 256, 128, f"ragged_n{n}")
 
 
+@pytest.mark.parametrize("m,n,k,group", [
+    (1, 80005, 256, 128),    # ragged last tile, warps with 2 and with 3 tiles (pairs + a single)
+    (5, 94720, 128, 128),    # one chunk holding a single round
+    (8, 76800, 192, 64),     # last chunk partly past K, scalar scale loads
+    (2, 151552, 384, 128),   # even ranges everywhere
+])
+def test_gemv_large_n_streaming_path(m, n, k, group):
+    """N beyond ~76k rows takes the persistent kernel (contiguous tile ranges per warp, ring running across tiles)."""
+    run_case(ops.int4_gemv, m, n, k, group, f"large_n m{m} n{n} k{k} g{group}")
+
+
+@pytest.mark.parametrize("impl", ["cuda_core"])
+def test_gemv_cuda_core_kernel_still_matches(impl):
+    """The tensor-core-free kernel stays reachable through the programmatic-dependent-launch flag."""
+    from kernelforge import _capi
+    _, x, packed, scales, ref = int4_case(2, 2048, 1024, 128, seed=4)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    y = torch.empty(2, 2048, dtype=torch.float16, device="cuda")
+    _capi.check(_capi.lib().kfb_int4_gemv(xs.data_ptr(), ps.data_ptr(), ss.data_ptr(), y.data_ptr(), 2, 2048, 1024, 128, 1,
+                                          torch.cuda.current_stream().cuda_stream))
+    assert_int4_close(y, ref, impl)
+
+
 @pytest.mark.parametrize("path", sorted(glob.glob(str(GOLDEN / "int4_linear_m[1-8]_*.npz"))), ids=lambda p: p.split("/")[-1])
 def test_gemv_golden(path):
     z = np.load(path)
