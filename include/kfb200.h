@@ -79,11 +79,15 @@ int kfb_dequantize(const void* packed, const void* scales, int N, int K, int gro
  * ------------------------------------------------------------------------------------- */
 
 /* int4_gemv (csrc/gemm/dequant_gemv.cu:21-36, kernel csrc/gemm/dequant_gemv_kernel.cuh:38-109):
- * 1 <= M <= 8, any N >= 1, K % group == 0, group in {64,128}.  CUDA-core weight stream,
- * FP32 accumulation, one rounding to fp16.  No workspace.
+ * 1 <= M <= 8, any N >= 1, K % group == 0, group in {64,128}.  FP32 accumulation, one
+ * rounding to fp16.  No workspace.  The weights are streamed by the TMA unit into shared
+ * memory and multiplied on mma.sync fragments in their masked unsigned form (exact), with
+ * a per-group correction from sums of x; a CUDA-core kernel (one FMA per weight, like the
+ * reference's) remains for comparison and for very long K.
  * flags: bit 0 = launch with programmatic dependent launch (the weight prefetch of this
  * call may overlap the tail of the previous kernel on the stream; x is read and y written
- * only after the previous kernel has completed). */
+ * only after the previous kernel has completed).
+ *        bit 1 = use the CUDA-core kernel. */
 int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y,
                   int M, int N, int K, int group, int flags, void* stream);
 

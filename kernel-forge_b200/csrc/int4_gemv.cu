@@ -325,15 +325,20 @@ extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scal
   if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
   if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
   if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
-  if (flags & ~1) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
+  if (flags & ~3) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
   cudaStream_t s = (cudaStream_t)stream;
   // Default: the mma.sync formulation (the CUDA-core kernel is issue-bound on B200, see int4_gemv_mma.cuh).
-  // KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel; it is also used for the programmatic-dependent-
-  // launch flag, which only that kernel implements, and when the class sums would not fit in shared memory.
+  // Flag bit 1 or KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel; it also serves K too long for the
+  // class sums to fit in shared memory.
   static const bool cuda_core = [] { const char* e = getenv("KFB_GEMV_IMPL"); return e && e[0] == 'c'; }();
-  if (!cuda_core && !(flags & 1) && (group == 128 ? gemv_mma::fits<128>(K) : gemv_mma::fits<64>(K)))
-    return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, s)
-                        : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, s);
+  if (!cuda_core && !(flags & 2) && (group == 128 ? gemv_mma::fits<128>(K) : gemv_mma::fits<64>(K)))
+    return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s)
+                        : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s);
   return group == 128 ? gemv::pick_m<128>(x, packed, scales, y, M, N, K, flags, s)
                       : gemv::pick_m<64>(x, packed, scales, y, M, N, K, flags, s);
+}
+
+// Tuning aid (not part of the public header): device buffer of 4 words per warp of the streaming kernel (3 timestamps in ns, SM id).
+extern "C" void kfb_debug_set_gemv_trace(void* device_buffer) {
+  kfb::gemv_mma::g_trace = static_cast<unsigned long long*>(device_buffer);
 }

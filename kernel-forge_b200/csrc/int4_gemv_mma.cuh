@@ -86,6 +86,11 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t m
   return d;
 }
 
+// Programmatic dependent launch (no-ops unless the launch carries the attribute): the weight stream of this kernel does
+// not depend on the kernel before it in the stream, only x and y do.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Bounded wait for a stage.  Unlike sm100::mbar_wait it sleeps between polls: several chunks are in flight per warp,
 // so a late wake-up costs nothing, while a polling warp would take issue slots and integer-pipe cycles from the warps
 // that have data.
@@ -343,6 +348,8 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
 #pragma unroll
   for (int i = 0; i < S; ++i)
     if (i < n_c) issue(i);
+  pdl_launch_dependents();
+  pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
 
   class_sums<G>(x, M, K, sx);
 
@@ -385,31 +392,43 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
 // ring runs ahead across tile boundaries: the producer and the consumer walk the same (step, chunk) sequence.
 // ---------------------------------------------------------------------------------------------------------------
 // TMAX: 2 = pairs + single as described, 1 = single tiles only (2 KB stages).  RG: rounds computed together.  MINB: CTAs
-// per SM the register allocation must allow.  S: stages.
-template <int G, int TMAX, int RG, int MINB, int S>
+// per SM the register allocation must allow.  S: stages.  CB: chunks per stage and per copy -- with CB > 1 the tensor
+// map is 3-D (128 bytes, rows, chunks of a row) and one copy brings CB * 128 contiguous bytes of every row, which is
+// what keeps DRAM pages open; the stage is then [chunk][row][128 bytes], each chunk laid out as before.
+template <int G, int TMAX, int RG, int MINB, int S, int CB>
 __global__ void __launch_bounds__(kThreads, MINB)
 int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap32,
                             const __grid_constant__ CUtensorMap wmap16, const __half* __restrict__ scales,
                             __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status,
-                            const uint4 unpack) {
+                            const uint4 unpack, unsigned long long* trace) {
   constexpr int C = LaneMap<G>::C;
-  constexpr uint32_t kStage = stage_bytes(TMAX);
+  constexpr uint32_t kStage = stage_bytes(TMAX) * CB;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int rounds = K / G;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * S * kStage);
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * S);
-  float* sx = reinterpret_cast<float*>(smem + sx_offset(TMAX, S));
+  float* sx = reinterpret_cast<float*>(smem + sx_offset(TMAX, S * CB));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // optional timeline for tuning: per warp (start, class sums done, end) in ns and the SM id
+  unsigned long long* tr = trace != nullptr && lane == 0 ? trace + (size_t)(blockIdx.x * kWarps + warp) * 4 : nullptr;
+  if (tr) {
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    tr[0] = globaltimer_ns();
+    tr[3] = smid;
+  }
 
   // this warp's range of 16-row tiles
   const int tiles = (N + kTileRows - 1) / kTileRows;
   const int gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
+  // tiles / nw each, the remainder spread evenly over the grid (so that every SM gets the same share of it)
   const int base = tiles / nw, extra = tiles - base * nw;
-  const int first = gw * base + min(gw, extra), count = base + (gw < extra ? 1 : 0);
+  const int ex0 = (int)(((long long)gw * extra) / nw), ex1 = (int)(((long long)(gw + 1) * extra) / nw);
+  const int first = gw * base + ex0, count = base + (ex1 - ex0);
   const int n_pairs = TMAX == 2 ? count >> 1 : 0, n_steps = TMAX == 2 ? n_pairs + (count & 1) : count;
-  const int n_chunks = (rounds + C - 1) / C;
-  const int total = n_steps * n_chunks;   // chunks this warp streams
+  const int n_chunks = (rounds + C - 1) / C, n_super = (n_chunks + CB - 1) / CB;
+  const int total = n_steps * n_super;   // copies this warp streams
 
   uint64_t* my_bars = bars + warp * S;
   const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * S * kStage;
@@ -421,29 +440,36 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   if (threadIdx.x == 0) *abort_word = 0;
   __syncwarp();
 
-  // producer side: next chunk to request = (p_step, p_chunk), the p_count-th of this warp
+  // producer side: next copy to request = chunks p_chunk * CB .. of step p_step, the p_count-th of this warp
   int p_step = 0, p_chunk = 0, p_count = 0;
   auto issue_next = [&]() {
     if (p_count < total) {
       if (lane == 0) {
         const int st = p_count % S;
         const bool single = TMAX == 1 || p_step == n_pairs;   // a 16-row copy (a 32-row one would overrun a 2 KB stage)
-        mbar_arrive_expect_tx(&my_bars[st], single ? stage_bytes(1) : kStage);
-        tma_load_2d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st],
-                    p_chunk * (kChunkBytes / 4), (first + (TMAX == 2 ? 2 * p_step : p_step)) * kTileRows);
+        const int row = (first + (TMAX == 2 ? 2 * p_step : p_step)) * kTileRows;
+        mbar_arrive_expect_tx(&my_bars[st], (single ? stage_bytes(1) : stage_bytes(TMAX)) * CB);
+        if constexpr (CB == 1)
+          tma_load_2d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st],
+                      p_chunk * (kChunkBytes / 4), row);
+        else
+          tma_load_3d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st], 0, row, p_chunk * CB);
       }
       ++p_count;
-      if (++p_chunk == n_chunks) { p_chunk = 0; ++p_step; }
+      if (++p_chunk == n_super) { p_chunk = 0; ++p_step; }
     }
   };
 #pragma unroll
   for (int i = 0; i < S; ++i) issue_next();
+  pdl_launch_dependents();
+  pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
 
   class_sums<G>(x, M, K, sx);
+  if (tr) tr[1] = globaltimer_ns();
 
   const AbortCtx ctx{abort_word, status};
   const LaneMap<G> lm(lane, x, M, K);
-  int q = 0;   // chunks consumed
+  int q = 0;   // copies consumed
   bool ok = true;
   auto run_step = [&](auto tag, int row0) {
     constexpr int T = decltype(tag)::value;
@@ -453,15 +479,24 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
     const __half* srow[2 * T];
 #pragma unroll
     for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
-    for (int ci = 0; ci < n_chunks; ++ci, ++q) {
-      const int r0 = ci * C, nr = min(C, rounds - r0);
+    for (int su = 0; su < n_super; ++su, ++q) {
       uint32_t sc[2 * T][C / 2];
-      load_scales<G, T>(srow, r0, nr, vec_scales, sc);
+      load_scales<G, T>(srow, su * CB * C, min(C, rounds - su * CB * C), vec_scales, sc);   // before the wait: overlaps it
       if (!__all_sync(0xffffffffu, wait_stage(&my_bars[q % S], (uint32_t)(q / S) & 1u, ctx))) { ok = false; return; }
-      chunk_compute<G, T, RG>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
-        __syncwarp();
-        issue_next();
-      });
+      for (int cc = 0; cc < CB; ++cc) {
+        const int ci = su * CB + cc;
+        if (ci >= n_chunks) break;
+        const int r0 = ci * C, nr = min(C, rounds - r0);
+        if (cc > 0) load_scales<G, T>(srow, r0, nr, vec_scales, sc);
+        const bool last = cc == CB - 1 || ci == n_chunks - 1;
+        chunk_compute<G, T, RG>(lm, my_ring + (uint32_t)(q % S) * kStage + (uint32_t)cc * stage_bytes(T), sx, r0, nr, sc, unpack, acc,
+                                [&] {
+                                  if (last) {
+                                    __syncwarp();
+                                    issue_next();
+                                  }
+                                });
+      }
     }
 #pragma unroll
     for (int tt = 0; tt < T; ++tt) store_tile(y, acc[tt], row0 + tt * kTileRows, lm.pg, lm.t, M, N);
@@ -471,6 +506,7 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
     if (TMAX == 2 && step < n_pairs) run_step(std::integral_constant<int, TMAX>{}, row0);
     else run_step(std::integral_constant<int, 1>{}, row0);
   }
+  if (tr) tr[2] = globaltimer_ns();
   linger_after_abort(abort_word);
 }
 
@@ -489,6 +525,24 @@ int opt_in_shared_memory() {   // once per kernel instantiation and device: more
   return KFB_OK;
 }
 
+inline unsigned long long* g_trace = nullptr;   // tuning aid, set through kfb_debug_set_gemv_trace
+
+template <class... KArgs, class... Args>
+int launch_ex(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+  return KFB_OK;
+}
+
 template <int G>
 inline bool fits(int K) {
   const size_t a = smem_bytes(1, kSplitStages, K / G), b = smem_bytes(2, 3, K / G);
@@ -497,16 +551,14 @@ inline bool fits(int K) {
 
 template <int G, int KSL>
 int launch_split(const void* x, const CUtensorMap& wmap16, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
-                 int vec, unsigned int* status, const uint4& unpack, cudaStream_t stream) {
+                 int vec, unsigned int* status, const uint4& unpack, bool pdl, cudaStream_t stream) {
   if (int rc = opt_in_shared_memory<int4_gemv_mma_split_kernel<G, KSL>>()) return rc;
-  int4_gemv_mma_split_kernel<G, KSL><<<grid, kThreads, smem, stream>>>((const __half*)x, wmap16, (const __half*)scales, (__half*)y,
-                                                                       M, N, K, vec, status, unpack);
-  KFB_LAUNCH_CHECK("int4_gemv_mma_split_kernel");
-  return KFB_OK;
+  return launch_ex(int4_gemv_mma_split_kernel<G, KSL>, grid, smem, stream, pdl, (const __half*)x, wmap16, (const __half*)scales,
+                   (__half*)y, M, N, K, vec, status, unpack);
 }
 
 template <int G>
-int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, cudaStream_t stream) {
+int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, bool pdl, cudaStream_t stream) {
   constexpr int C = kChunkBytes / (G / 2);
   const int rounds = K / G, n_chunks = ceil_div(rounds, C), tiles = ceil_div(N, kTileRows);
   const int vec = (rounds % C == 0) && aligned16(scales);
@@ -519,27 +571,39 @@ int launch(const void* x, const void* packed, const void* scales, void* y, int M
                                   kTileRows, /*swizzle128=*/true))
     return rc;
   static const int cfg = [] { const char* e = getenv("KFB_GEMV_CFG"); return e ? atoi(e) : 0; }();
-  const int ctas_per_sm = cfg == 0 ? 2 : cfg == 1 ? 2 : cfg == 2 ? 3 : 4;
+  const int ctas_per_sm = (cfg == 0 || cfg == 2) ? 2 : 1;
+  const int cb = (K % 256) ? 1 : (cfg == 3 || cfg == 5) ? 4 : (cfg == 0 ? 1 : 2);
   const int stream_warps = ctas_per_sm * sm_count() * kWarps;
   if (tiles >= 2 * stream_warps) {   // every warp of a persistent grid gets at least two tiles
     CUtensorMap wmap32;
-    if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
-                                    2 * kTileRows, true))
-      return rc;
-#define KFB_STREAM(TMAX, RG, MINB, S)                                                                                  \
+    if (cb == 1) {
+      if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
+                                      2 * kTileRows, true))
+        return rc;
+    } else {   // [N rows][K/256 chunks][32 words]: one copy = cb chunks of 16 / 32 rows
+      const uint64_t dims[3] = {kChunkBytes / 4, (uint64_t)N, (uint64_t)K / 2 / kChunkBytes};
+      const uint64_t strides[2] = {(uint64_t)K / 2, kChunkBytes};
+      const uint32_t box32[3] = {kChunkBytes / 4, 2 * kTileRows, (uint32_t)cb}, box16[3] = {kChunkBytes / 4, kTileRows, (uint32_t)cb};
+      if (int rc = make_tmap_3d_u32_sw128(&wmap32, packed, dims, strides, box32)) return rc;
+      if (int rc = make_tmap_3d_u32_sw128(&wmap16, packed, dims, strides, box16)) return rc;
+    }
+#define KFB_STREAM(TMAX, RG, MINB, S, CB)                                                                              \
   do {                                                                                                                 \
-    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S>>()) return rc;                  \
-    int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S><<<MINB * sm_count(), kThreads, smem_bytes(TMAX, S, rounds), stream>>>( \
-        (const __half*)x, wmap32, wmap16, (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack);            \
+    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S, CB>>()) return rc;              \
+    if (int rc = launch_ex(int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S, CB>, MINB * sm_count(),                    \
+                           smem_bytes(TMAX, S * CB, rounds), stream, pdl, (const __half*)x, wmap32, wmap16,             \
+                           (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack, g_trace))                   \
+      return rc;                                                                                                       \
   } while (0)
-    switch (cfg) {
-      case 1: KFB_STREAM(1, 2, 2, 4); break;
-      case 2: KFB_STREAM(1, 1, 3, 4); break;
-      case 3: KFB_STREAM(1, 1, 4, 3); break;
-      default: KFB_STREAM(2, 2, 2, 3); break;
+    if (cb == 1) KFB_STREAM(2, 2, 2, 3, 1);
+    else switch (cfg) {
+      case 1: KFB_STREAM(2, 2, 1, 2, 2); break;
+      case 2: KFB_STREAM(1, 2, 2, 3, 2); break;
+      case 3: KFB_STREAM(1, 2, 1, 2, 4); break;
+      case 4: KFB_STREAM(2, 2, 1, 3, 2); break;
+      default: KFB_STREAM(1, 2, 1, 3, 4); break;
     }
 #undef KFB_STREAM
-    KFB_LAUNCH_CHECK("int4_gemv_mma_stream_kernel");
     return KFB_OK;
   }
   // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks)
@@ -549,10 +613,10 @@ int launch(const void* x, const void* packed, const void* scales, void* y, int M
   const int grid = ceil_div(tiles, kWarps >> ksl);
   const size_t smem = smem_bytes(1, kSplitStages, rounds);
   switch (ksl) {
-    case 0: return launch_split<G, 0>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
-    case 1: return launch_split<G, 1>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
-    case 2: return launch_split<G, 2>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
-    default: return launch_split<G, 3>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, stream);
+    case 0: return launch_split<G, 0>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
+    case 1: return launch_split<G, 1>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
+    case 2: return launch_split<G, 2>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
+    default: return launch_split<G, 3>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
   }
 }
 

@@ -48,14 +48,16 @@ def test_gemv_large_n_streaming_path(m, n, k, group):
 
 @pytest.mark.parametrize("impl", ["cuda_core"])
 def test_gemv_cuda_core_kernel_still_matches(impl):
-    """The tensor-core-free kernel stays reachable through the programmatic-dependent-launch flag."""
+    """The tensor-core-free kernel stays reachable through flag bit 1; bit 0 (dependent launch) works with both."""
     from kernelforge import _capi
     _, x, packed, scales, ref = int4_case(2, 2048, 1024, 128, seed=4)
     xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
     y = torch.empty(2, 2048, dtype=torch.float16, device="cuda")
-    _capi.check(_capi.lib().kfb_int4_gemv(xs.data_ptr(), ps.data_ptr(), ss.data_ptr(), y.data_ptr(), 2, 2048, 1024, 128, 1,
-                                          torch.cuda.current_stream().cuda_stream))
-    assert_int4_close(y, ref, impl)
+    for flags in (2, 3, 1):
+        y.zero_()
+        _capi.check(_capi.lib().kfb_int4_gemv(xs.data_ptr(), ps.data_ptr(), ss.data_ptr(), y.data_ptr(), 2, 2048, 1024, 128, flags,
+                                              torch.cuda.current_stream().cuda_stream))
+        assert_int4_close(y, ref, f"{impl} flags={flags}")
 
 
 @pytest.mark.parametrize("path", sorted(glob.glob(str(GOLDEN / "int4_linear_m[1-8]_*.npz"))), ids=lambda p: p.split("/")[-1])
