@@ -145,10 +145,10 @@ struct LaneMap {
 template <int G>
 __device__ __forceinline__ void class_sums(const __half* __restrict__ x, int M, int K, float* sx) {
   const int rounds = K / G;
-  for (int i = threadIdx.x; i < rounds * 8; i += kThreads)
+  for (int i = threadIdx.x; i < rounds * 8; i += blockDim.x)
     if ((i & 7) >= M) sx[i] = 0.f;
   const int q = threadIdx.x & 3, items = rounds * M;
-  for (int base = 0; base < items; base += kThreads / 4) {
+  for (int base = 0; base < items; base += blockDim.x / 4) {
     const int item = base + (threadIdx.x >> 2);
     const bool live = item < items;
     const int rd = live ? item / M : 0, m = live ? item - rd * M : 0;
@@ -205,7 +205,7 @@ __device__ __forceinline__ void load_scales(const __half* const (&srow)[2 * T], 
 
 // One chunk (C rounds) of T row tiles out of the stage at shared address `st` (already complete).  `refill` runs once
 // every shared load of the stage has delivered, i.e. as early as the stage may be handed back to the TMA.
-template <int G, int T, int RG, class Refill>
+template <int G, int T, int RG, int DBG = 0, class Refill>
 __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st, const float* sx, int r0, int nr,
                                               const uint32_t (&sc)[2 * T][LaneMap<G>::C / 2], const uint4& unpack,
                                               float (&acc)[T][4], Refill&& refill) {
@@ -242,7 +242,10 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st,
     for (int j = 0; j < W; ++j) {
       uint4 xv[RG];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
 #pragma unroll
-      for (int v = 0; v < RG; ++v) xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
+      for (int v = 0; v < RG; ++v) {
+        if constexpr (DBG == 1) xv[v] = make_uint4(kMaskA, kMaskB, kMagicA, kMagicB);
+        else xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
+      }
 #pragma unroll
       for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -252,6 +255,14 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st,
             const uint32_t lo = w[v][2 * tt][j] >> (8 * half), hi = w[v][2 * tt + 1][j] >> (8 * half);
             float(&c)[4] = ca[v][tt][half % kAcc];
             const bool first = j == 0 && half < kAcc;
+            if constexpr (DBG == 2) {   // no MMA: fold the operands into the accumulator some other way
+              const uint32_t f = and_or(lo, kMaskA, kMagicA) ^ and_or(hi, kMaskA, kMagicA) ^ and_or(lo, kMaskB, kMagicB) ^
+                                 and_or(hi, kMaskB, kMagicB) ^ (half ? xv[v].z : xv[v].x) ^ (half ? xv[v].w : xv[v].y);
+              c[0] = first ? __uint_as_float(f) : __uint_as_float(__float_as_uint(c[0]) ^ f);
+              c[1] = c[2] = c[3] = c[0];
+            } else if constexpr (DBG == 3) {   // no unpack
+              mma16816_f16(c, lo, hi, lo, hi, half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
+            } else
             mma16816_f16(c, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
                          and_or(hi, kMaskB, kMagicB), half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
           }
@@ -386,32 +397,45 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Kernel for large N: persistent, two CTAs per SM.  Warp number gw of the grid owns the 16-row tiles
-// [first, first + count), count differing by at most one between warps; it processes them as pairs (one 32-row
-// copy per chunk, activation fragments shared by both tiles) and a final single tile when count is odd.  The
-// ring runs ahead across tile boundaries: the producer and the consumer walk the same (step, chunk) sequence.
+// Kernel for large N: persistent, NW warps per CTA.  The 16-row tiles are split evenly over the CTAs (contiguous
+// ranges); inside a CTA the warps take work units from a shared-memory counter: first pairs of tiles (one 32-row copy
+// per chunk, activation fragments shared by both tiles), at the end single tiles, so that the warps of a CTA finish
+// within one single-tile time of each other whatever service each of them got from the memory system.  A warp's ring
+// runs ahead across unit boundaries: the producer side takes the next unit as soon as it has requested the last
+// chunk of the current one and passes it to the consumer side through a small queue.
 // ---------------------------------------------------------------------------------------------------------------
-// TMAX: 2 = pairs + single as described, 1 = single tiles only (2 KB stages).  RG: rounds computed together.  MINB: CTAs
-// per SM the register allocation must allow.  S: stages.  CB: chunks per stage and per copy -- with CB > 1 the tensor
-// map is 3-D (128 bytes, rows, chunks of a row) and one copy brings CB * 128 contiguous bytes of every row, which is
-// what keeps DRAM pages open; the stage is then [chunk][row][128 bytes], each chunk laid out as before.
-template <int G, int TMAX, int RG, int MINB, int S, int CB>
-__global__ void __launch_bounds__(kThreads, MINB)
+template <int NW, int S_ = 3>
+struct StreamSmem {   // offsets from the 1024-byte aligned base
+  static constexpr int S = S_;                                  // 4 KB in flight per warp and stage
+  static constexpr uint32_t kStage = stage_bytes(2);
+  static constexpr size_t bars = (size_t)NW * S * kStage;       // uint64_t[NW * S]
+  static constexpr size_t abort_word = bars + (size_t)NW * S * 8;
+  static constexpr size_t counter = abort_word + 4;             // next unit of the CTA
+  static constexpr size_t queue = abort_word + 16;              // int[NW][4]: units taken by a warp's producer side
+  static constexpr size_t sx = queue + (size_t)NW * 16;
+  static size_t bytes(int rounds) { return 1024 + sx + (size_t)rounds * 8 * sizeof(float); }
+};
+
+template <int G, int RG, int NW, int MINB, int NS = 3, int DBG = 0>
+__global__ void __launch_bounds__(NW * 32, MINB)
 int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap32,
                             const __grid_constant__ CUtensorMap wmap16, const __half* __restrict__ scales,
                             __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status,
                             const uint4 unpack, unsigned long long* trace) {
-  constexpr int C = LaneMap<G>::C;
-  constexpr uint32_t kStage = stage_bytes(TMAX) * CB;
+  using L = StreamSmem<NW, NS>;
+  constexpr int C = LaneMap<G>::C, S = L::S;
+  constexpr uint32_t kStage = L::kStage;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int rounds = K / G;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * S * kStage);
-  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * S);
-  float* sx = reinterpret_cast<float*>(smem + sx_offset(TMAX, S * CB));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bars);
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(smem + L::abort_word);
+  int* counter = reinterpret_cast<int*>(smem + L::counter);
+  float* sx = reinterpret_cast<float*>(smem + L::sx);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* my_queue = reinterpret_cast<volatile int*>(smem + L::queue) + warp * 4;
   // optional timeline for tuning: per warp (start, class sums done, end) in ns and the SM id
-  unsigned long long* tr = trace != nullptr && lane == 0 ? trace + (size_t)(blockIdx.x * kWarps + warp) * 4 : nullptr;
+  unsigned long long* tr = trace != nullptr && lane == 0 ? trace + (size_t)(blockIdx.x * NW + warp) * 4 : nullptr;
   if (tr) {
     uint32_t smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -419,16 +443,16 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
     tr[3] = smid;
   }
 
-  // this warp's range of 16-row tiles
+  // this CTA's range of 16-row tiles: tiles / grid each, the remainder spread evenly over the grid
   const int tiles = (N + kTileRows - 1) / kTileRows;
-  const int gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
-  // tiles / nw each, the remainder spread evenly over the grid (so that every SM gets the same share of it)
-  const int base = tiles / nw, extra = tiles - base * nw;
-  const int ex0 = (int)(((long long)gw * extra) / nw), ex1 = (int)(((long long)(gw + 1) * extra) / nw);
-  const int first = gw * base + ex0, count = base + (ex1 - ex0);
-  const int n_pairs = TMAX == 2 ? count >> 1 : 0, n_steps = TMAX == 2 ? n_pairs + (count & 1) : count;
-  const int n_chunks = (rounds + C - 1) / C, n_super = (n_chunks + CB - 1) / CB;
-  const int total = n_steps * n_super;   // copies this warp streams
+  const int base = tiles / (int)gridDim.x, extra = tiles - base * (int)gridDim.x;
+  const int ex0 = (int)(((long long)blockIdx.x * extra) / gridDim.x), ex1 = (int)(((long long)(blockIdx.x + 1) * extra) / gridDim.x);
+  const int first = blockIdx.x * base + ex0, count = base + (ex1 - ex0);
+  // units: n_pairs pairs, then n_single single tiles (about one per warp, parity adjusted)
+  const int n_single = min(count, NW + ((count - NW) & 1));
+  const int n_pairs = (count - n_single) >> 1, n_units = n_pairs + n_single;
+  auto unit_tile = [&](int u) { return first + (u < n_pairs ? 2 * u : 2 * n_pairs + (u - n_pairs)); };
+  const int n_chunks = (rounds + C - 1) / C;
 
   uint64_t* my_bars = bars + warp * S;
   const uint32_t my_ring = smem_u32(smem) + (uint32_t)warp * S * kStage;
@@ -437,26 +461,34 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
     for (int s = 0; s < S; ++s) mbar_init(&my_bars[s], 1);
     fence_mbar_init();
   }
-  if (threadIdx.x == 0) *abort_word = 0;
-  __syncwarp();
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    *counter = NW;   // units 0 .. NW-1 are the warps' first units
+  }
+  __syncthreads();
 
-  // producer side: next copy to request = chunks p_chunk * CB .. of step p_step, the p_count-th of this warp
-  int p_step = 0, p_chunk = 0, p_count = 0;
+  // producer side: the unit being requested, its next chunk, copies requested so far, units taken so far
+  int p_unit = warp, p_chunk = 0, p_count = 0, p_taken = 1;
+  if (lane == 0) my_queue[0] = p_unit;
   auto issue_next = [&]() {
-    if (p_count < total) {
+    if (p_unit >= n_units) return;
+    if (lane == 0) {
+      const int st = p_count % S;
+      const bool single = p_unit >= n_pairs;
+      mbar_arrive_expect_tx(&my_bars[st], single ? stage_bytes(1) : kStage);
+      tma_load_2d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st], p_chunk * (kChunkBytes / 4),
+                  unit_tile(p_unit) * kTileRows);
+    }
+    ++p_count;
+    if (++p_chunk == n_chunks) {   // take the next unit of the CTA
+      p_chunk = 0;
+      int u = 0;
       if (lane == 0) {
-        const int st = p_count % S;
-        const bool single = TMAX == 1 || p_step == n_pairs;   // a 16-row copy (a 32-row one would overrun a 2 KB stage)
-        const int row = (first + (TMAX == 2 ? 2 * p_step : p_step)) * kTileRows;
-        mbar_arrive_expect_tx(&my_bars[st], (single ? stage_bytes(1) : stage_bytes(TMAX)) * CB);
-        if constexpr (CB == 1)
-          tma_load_2d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st],
-                      p_chunk * (kChunkBytes / 4), row);
-        else
-          tma_load_3d(smem + (size_t)(warp * S + st) * kStage, single ? &wmap16 : &wmap32, &my_bars[st], 0, row, p_chunk * CB);
+        u = atomicAdd(counter, 1);
+        my_queue[p_taken & 3] = u;
       }
-      ++p_count;
-      if (++p_chunk == n_super) { p_chunk = 0; ++p_step; }
+      p_unit = __shfl_sync(0xffffffffu, u, 0);
+      ++p_taken;
     }
   };
 #pragma unroll
@@ -471,7 +503,7 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   const LaneMap<G> lm(lane, x, M, K);
   int q = 0;   // copies consumed
   bool ok = true;
-  auto run_step = [&](auto tag, int row0) {
+  auto run_unit = [&](auto tag, int row0) {
     constexpr int T = decltype(tag)::value;
     float acc[T][4];
 #pragma unroll
@@ -479,32 +511,27 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
     const __half* srow[2 * T];
 #pragma unroll
     for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
-    for (int su = 0; su < n_super; ++su, ++q) {
+    for (int ci = 0; ci < n_chunks; ++ci, ++q) {
+      const int r0 = ci * C, nr = min(C, rounds - r0);
       uint32_t sc[2 * T][C / 2];
-      load_scales<G, T>(srow, su * CB * C, min(C, rounds - su * CB * C), vec_scales, sc);   // before the wait: overlaps it
+      load_scales<G, T>(srow, r0, nr, vec_scales, sc);   // before the wait: overlaps it
       if (!__all_sync(0xffffffffu, wait_stage(&my_bars[q % S], (uint32_t)(q / S) & 1u, ctx))) { ok = false; return; }
-      for (int cc = 0; cc < CB; ++cc) {
-        const int ci = su * CB + cc;
-        if (ci >= n_chunks) break;
-        const int r0 = ci * C, nr = min(C, rounds - r0);
-        if (cc > 0) load_scales<G, T>(srow, r0, nr, vec_scales, sc);
-        const bool last = cc == CB - 1 || ci == n_chunks - 1;
-        chunk_compute<G, T, RG>(lm, my_ring + (uint32_t)(q % S) * kStage + (uint32_t)cc * stage_bytes(T), sx, r0, nr, sc, unpack, acc,
-                                [&] {
-                                  if (last) {
-                                    __syncwarp();
-                                    issue_next();
-                                  }
-                                });
-      }
+      chunk_compute<G, T, RG, DBG>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+        __syncwarp();
+        issue_next();
+      });
     }
 #pragma unroll
     for (int tt = 0; tt < T; ++tt) store_tile(y, acc[tt], row0 + tt * kTileRows, lm.pg, lm.t, M, N);
   };
-  for (int step = 0; step < n_steps && ok; ++step) {
-    const int row0 = (first + (TMAX == 2 ? 2 * step : step)) * kTileRows;
-    if (TMAX == 2 && step < n_pairs) run_step(std::integral_constant<int, TMAX>{}, row0);
-    else run_step(std::integral_constant<int, 1>{}, row0);
+  for (int taken = 0; ok; ++taken) {
+    // the producer side is at least one chunk ahead, so the queue entry exists (same warp: __syncwarp orders it)
+    __syncwarp();
+    const int u = my_queue[taken & 3];
+    if (u >= n_units) break;
+    const int row0 = unit_tile(u) * kTileRows;
+    if (u < n_pairs) run_unit(std::integral_constant<int, 2>{}, row0);
+    else run_unit(std::integral_constant<int, 1>{}, row0);
   }
   if (tr) tr[2] = globaltimer_ns();
   linger_after_abort(abort_word);
@@ -528,10 +555,10 @@ int opt_in_shared_memory() {   // once per kernel instantiation and device: more
 inline unsigned long long* g_trace = nullptr;   // tuning aid, set through kfb_debug_set_gemv_trace
 
 template <class... KArgs, class... Args>
-int launch_ex(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+int launch_ex(void (*kernel)(KArgs...), int grid, int threads, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -545,7 +572,7 @@ int launch_ex(void (*kernel)(KArgs...), int grid, size_t smem, cudaStream_t stre
 
 template <int G>
 inline bool fits(int K) {
-  const size_t a = smem_bytes(1, kSplitStages, K / G), b = smem_bytes(2, 3, K / G);
+  const size_t a = smem_bytes(1, kSplitStages, K / G), b = StreamSmem<16>::bytes(K / G);
   return (a > b ? a : b) <= 227u * 1024u;
 }
 
@@ -553,7 +580,7 @@ template <int G, int KSL>
 int launch_split(const void* x, const CUtensorMap& wmap16, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
                  int vec, unsigned int* status, const uint4& unpack, bool pdl, cudaStream_t stream) {
   if (int rc = opt_in_shared_memory<int4_gemv_mma_split_kernel<G, KSL>>()) return rc;
-  return launch_ex(int4_gemv_mma_split_kernel<G, KSL>, grid, smem, stream, pdl, (const __half*)x, wmap16, (const __half*)scales,
+  return launch_ex(int4_gemv_mma_split_kernel<G, KSL>, grid, kThreads, smem, stream, pdl, (const __half*)x, wmap16, (const __half*)scales,
                    (__half*)y, M, N, K, vec, status, unpack);
 }
 
@@ -571,40 +598,24 @@ int launch(const void* x, const void* packed, const void* scales, void* y, int M
                                   kTileRows, /*swizzle128=*/true))
     return rc;
   static const int cfg = [] { const char* e = getenv("KFB_GEMV_CFG"); return e ? atoi(e) : 0; }();
-  const int ctas_per_sm = (cfg == 0 || cfg == 2) ? 2 : 1;
-  const int cb = (K % 256) ? 1 : (cfg == 3 || cfg == 5) ? 4 : (cfg == 0 ? 1 : 2);
-  const int stream_warps = ctas_per_sm * sm_count() * kWarps;
+  const int stream_warps = 16 * sm_count();
   if (tiles >= 2 * stream_warps) {   // every warp of a persistent grid gets at least two tiles
     CUtensorMap wmap32;
-    if (cb == 1) {
-      if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
-                                      2 * kTileRows, true))
-        return rc;
-    } else {   // [N rows][K/256 chunks][32 words]: one copy = cb chunks of 16 / 32 rows
-      const uint64_t dims[3] = {kChunkBytes / 4, (uint64_t)N, (uint64_t)K / 2 / kChunkBytes};
-      const uint64_t strides[2] = {(uint64_t)K / 2, kChunkBytes};
-      const uint32_t box32[3] = {kChunkBytes / 4, 2 * kTileRows, (uint32_t)cb}, box16[3] = {kChunkBytes / 4, kTileRows, (uint32_t)cb};
-      if (int rc = make_tmap_3d_u32_sw128(&wmap32, packed, dims, strides, box32)) return rc;
-      if (int rc = make_tmap_3d_u32_sw128(&wmap16, packed, dims, strides, box16)) return rc;
-    }
-#define KFB_STREAM(TMAX, RG, MINB, S, CB)                                                                              \
+    if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
+                                    2 * kTileRows, true))
+      return rc;
+#define KFB_STREAM(NW, MINB, NS)                                                                                       \
   do {                                                                                                                 \
-    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S, CB>>()) return rc;              \
-    if (int rc = launch_ex(int4_gemv_mma_stream_kernel<G, TMAX, RG, MINB, S, CB>, MINB * sm_count(),                    \
-                           smem_bytes(TMAX, S * CB, rounds), stream, pdl, (const __half*)x, wmap32, wmap16,             \
-                           (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack, g_trace))                   \
-      return rc;                                                                                                       \
+    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, 2, NW, MINB, NS>>()) return rc;                    \
+    return launch_ex(int4_gemv_mma_stream_kernel<G, 2, NW, MINB, NS>, MINB * sm_count(), NW * 32,                       \
+                     StreamSmem<NW, NS>::bytes(rounds), stream, pdl, (const __half*)x, wmap32, wmap16,                  \
+                     (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack, g_trace);                         \
   } while (0)
-    if (cb == 1) KFB_STREAM(2, 2, 2, 3, 1);
-    else switch (cfg) {
-      case 1: KFB_STREAM(2, 2, 1, 2, 2); break;
-      case 2: KFB_STREAM(1, 2, 2, 3, 2); break;
-      case 3: KFB_STREAM(1, 2, 1, 2, 4); break;
-      case 4: KFB_STREAM(2, 2, 1, 3, 2); break;
-      default: KFB_STREAM(1, 2, 1, 3, 4); break;
-    }
+    if (cfg == 1) KFB_STREAM(16, 1, 2);
+    else if (cfg == 2) KFB_STREAM(8, 1, 3);
+    else if (cfg == 3) KFB_STREAM(8, 1, 4);
+    else KFB_STREAM(16, 1, 3);
 #undef KFB_STREAM
-    return KFB_OK;
   }
   // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks)
   int ksl = 0;
