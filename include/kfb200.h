@@ -91,6 +91,15 @@ int kfb_dequantize(const void* packed, const void* scales, int N, int K, int gro
 int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y,
                   int M, int N, int K, int group, int flags, void* stream);
 
+/* The same weight-streaming kernel for 1 <= M <= 32: every further block of 8 batch rows is one
+ * more MMA on the weight fragment that is already unpacked, so the cost per weight byte
+ * stays that of the GEMV while the tcgen05 GEMM below still pays for a 128-row tile.
+ * No counterpart in the reference (its GEMV stops at M = 8, kernelforge/ops.py:193; from there
+ * on it uses the tensor-core GEMM).  Arguments and flags as kfb_int4_gemv; flag bit 1 is
+ * honoured for M <= 8 only. */
+int kfb_int4_small_batch(const void* x, const void* packed, const void* scales, void* y,
+                         int M, int N, int K, int group, int flags, void* stream);
+
 /* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
  * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),
  * K % group == 0.  Weights are dequantised into swizzled shared memory and multiplied on

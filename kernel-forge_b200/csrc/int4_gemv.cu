@@ -317,10 +317,12 @@ int pick_m(const void* x, const void* packed, const void* scales, void* y, int M
 
 using namespace kfb;
 
-extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
-                             int group, int flags, void* stream) {
+namespace {
+
+int gemv_entry(const char* what, int max_m, const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+               int group, int flags, void* stream) {
   if (int rc = require_sm100()) return rc;
-  if (M < 1 || M > 8) return fail(KFB_ERR_INVALID, "int4_gemv handles M in [1, 8], got M=%d", M);
+  if (M < 1 || M > max_m) return fail(KFB_ERR_INVALID, "%s handles M in [1, %d], got M=%d", what, max_m, M);
   if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
   if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
   if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
@@ -328,14 +330,28 @@ extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scal
   if (flags & ~3) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
   cudaStream_t s = (cudaStream_t)stream;
   // Default: the mma.sync formulation (the CUDA-core kernel is issue-bound on B200, see int4_gemv_mma.cuh).
-  // Flag bit 1 or KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel; it also serves K too long for the
-  // class sums to fit in shared memory.
+  // Flag bit 1 or KFB_GEMV_IMPL=cuda_core selects the tensor-core-free kernel (M <= 8); it also serves K too long
+  // for the class sums to fit in shared memory.
   static const bool cuda_core = [] { const char* e = getenv("KFB_GEMV_IMPL"); return e && e[0] == 'c'; }();
-  if (!cuda_core && !(flags & 2) && (group == 128 ? gemv_mma::fits<128>(K) : gemv_mma::fits<64>(K)))
+  const bool fits = group == 128 ? gemv_mma::fits<128>(M, K) : gemv_mma::fits<64>(M, K);
+  if (fits && (M > 8 || (!cuda_core && !(flags & 2))))
     return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s)
                         : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s);
+  if (M > 8) return fail(KFB_ERR_UNSUPPORTED, "%s: K=%d is too long for M=%d (class sums exceed shared memory)", what, K, M);
   return group == 128 ? gemv::pick_m<128>(x, packed, scales, y, M, N, K, flags, s)
                       : gemv::pick_m<64>(x, packed, scales, y, M, N, K, flags, s);
+}
+
+}  // namespace
+
+extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                             int group, int flags, void* stream) {
+  return gemv_entry("int4_gemv", 8, x, packed, scales, y, M, N, K, group, flags, stream);
+}
+
+extern "C" int kfb_int4_small_batch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                                    int group, int flags, void* stream) {
+  return gemv_entry("int4_small_batch", gemv_mma::kMaxM, x, packed, scales, y, M, N, K, group, flags, stream);
 }
 
 // Tuning aid (not part of the public header): device buffer of 4 words per warp of the streaming kernel (3 timestamps in ns, SM id).

@@ -116,16 +116,17 @@ __device__ __forceinline__ bool wait_stage(uint64_t* bar, uint32_t parity, const
 // class sums.  The split-K reduction reuses the ring.
 __host__ __device__ constexpr uint32_t stage_bytes(int RT) { return (uint32_t)(kTileRows * RT * kChunkBytes); }
 __host__ __device__ constexpr size_t sx_offset(int RT, int S) { return (size_t)kWarps * S * stage_bytes(RT) + kWarps * S * 8 + 16; }
-inline size_t smem_bytes(int RT, int S, int rounds) { return 1024 + sx_offset(RT, S) + (size_t)rounds * 8 * sizeof(float); }
+inline size_t smem_bytes(int RT, int S, int rounds, int NB) { return 1024 + sx_offset(RT, S) + (size_t)rounds * 8 * NB * sizeof(float); }
 
 // What a lane needs to find its words and its activations; the same for every tile.
-template <int G>
+// NB: blocks of 8 batch columns (M <= 8 NB); every block is one more MMA on the same unpacked weight fragment.
+template <int G, int NB = 1>
 struct LaneMap {
   static constexpr int W = G / 32;                   // packed words per lane per row per round
   static constexpr int C = kChunkBytes / (G / 2);    // rounds per chunk (2 or 4)
   int g, t, pg;         // lane = 4 g + t; fragment row slot g holds matrix rows pg + 8 k of the warp's rows
   uint32_t off[C];      // position of this lane's words of round u inside a stage (row pg, swizzled 16-byte piece)
-  const __half* xrow;   // column g of the B operand (a valid row when g >= M), at this lane's k offset
+  const __half* xrow[NB];   // column 8 nb + g of the B operand (a valid row when >= M), at this lane's k offset
   __device__ __forceinline__ LaneMap(int lane, const __half* x, int M, int K) {
     g = lane >> 2;
     t = lane & 3;
@@ -135,18 +136,19 @@ struct LaneMap {
       const uint32_t byte = (uint32_t)u * (G / 2) + (uint32_t)t * (W * 4);
       off[u] = (uint32_t)pg * kChunkBytes + ((((byte >> 4) ^ (uint32_t)pg) << 4) | (byte & 15u));
     }
-    xrow = x + (size_t)min(g, M - 1) * K + t * (G / 4);
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) xrow[nb] = x + (size_t)min(8 * nb + g, M - 1) * K + t * (G / 4);
   }
 };
 
-// Class sums of the activations, once per CTA: sx[round][column] = -1032 SxA - 72 SxB.  Four lanes share one
+// Class sums of the activations, once per CTA: sx[round][column < 8 NB] = -1032 SxA - 72 SxB.  Four lanes share one
 // (round, batch row): each sums a quarter of the group (whole packed words: pairs 0, 2 of a word meet the 16384 + 16 u
 // form, pairs 1, 3 the 1024 + 16 u form), then a quad reduction.  Ends with the CTA barrier.
-template <int G>
+template <int G, int NB>
 __device__ __forceinline__ void class_sums(const __half* __restrict__ x, int M, int K, float* sx) {
   const int rounds = K / G;
-  for (int i = threadIdx.x; i < rounds * 8; i += blockDim.x)
-    if ((i & 7) >= M) sx[i] = 0.f;
+  for (int i = threadIdx.x; i < rounds * 8 * NB; i += blockDim.x)
+    if ((i & (8 * NB - 1)) >= M) sx[i] = 0.f;
   const int q = threadIdx.x & 3, items = rounds * M;
   for (int base = 0; base < items; base += blockDim.x / 4) {
     const int item = base + (threadIdx.x >> 2);
@@ -170,7 +172,7 @@ __device__ __forceinline__ void class_sums(const __half* __restrict__ x, int M, 
     sb += __shfl_xor_sync(0xffffffffu, sb, 1);
     sa += __shfl_xor_sync(0xffffffffu, sa, 2);
     sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-    if (live && q == 0) sx[rd * 8 + m] = fmaf(sa, -1032.0f, sb * -72.0f);
+    if (live && q == 0) sx[rd * 8 * NB + m] = fmaf(sa, -1032.0f, sb * -72.0f);
   }
   __syncthreads();
 }
@@ -205,25 +207,28 @@ __device__ __forceinline__ void load_scales(const __half* const (&srow)[2 * T], 
 
 // One chunk (C rounds) of T row tiles out of the stage at shared address `st` (already complete).  `refill` runs once
 // every shared load of the stage has delivered, i.e. as early as the stage may be handed back to the TMA.
-template <int G, int T, int RG, int DBG = 0, class Refill>
-__device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st, const float* sx, int r0, int nr,
+template <int G, int T, int RG, int NB, class Refill>
+__device__ __forceinline__ void chunk_compute(const LaneMap<G, NB>& lm, uint32_t st, const float* sx, int r0, int nr,
                                               const uint32_t (&sc)[2 * T][LaneMap<G>::C / 2], const uint4& unpack,
-                                              float (&acc)[T][4], Refill&& refill) {
+                                              float (&acc)[T][NB][4], Refill&& refill) {
   constexpr int W = LaneMap<G>::W, C = LaneMap<G>::C;
+  static_assert(C % RG == 0, "rounds per chunk must be a multiple of the round group");
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t kMaskA = unpack.x, kMaskB = unpack.y, kMagicA = unpack.z, kMagicB = unpack.w;
-  // Rounds are computed RG (1 or 2) at a time.  Rounds past the end of K (last chunk only; their weights are TMA zero fill
-  // and their scales zero) read the activations of the chunk's first round instead of running past x.
+  // Rounds are computed RG (1 or 2) at a time.  Rounds past the end of K (last chunk only; their weights are TMA zero
+  // fill and their scales zero) read the activations of the chunk's first round instead of running past x.
 #pragma unroll
   for (int h = 0; h < C; h += RG) {
-    const __half* px[RG];
-    float2 cs[RG];   // corrections of columns 2t, 2t+1
+    int xoff[RG];      // element offset of the round in a row of x
+    float2 cs[RG][NB]; // corrections of columns 8 nb + 2t, + 1
     uint32_t w[RG][2 * T][W];
 #pragma unroll
     for (int v = 0; v < RG; ++v) {
       const int ue = h + v < nr ? h + v : 0;
-      px[v] = lm.xrow + (size_t)(r0 + ue) * G;
-      cs[v] = *reinterpret_cast<const float2*>(sx + (r0 + ue) * 8 + lm.t * 2);
+      xoff[v] = (r0 + ue) * G;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+        cs[v][nb] = *reinterpret_cast<const float2*>(sx + (r0 + ue) * (8 * NB) + 8 * nb + lm.t * 2);
 #pragma unroll
       for (int k = 0; k < 2 * T; ++k) {
         const uint32_t a = st + lm.off[h + v] + k * 8 * kChunkBytes;
@@ -233,19 +238,18 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st,
           asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[v][k][0]), "=r"(w[v][k][1]) : "r"(a));
       }
     }
-    // kAcc accumulators per (round, tile).  The MMAs are issued word by word and half word by half word across all
-    // (round, tile) pairs, so that two MMAs on the same accumulator are 2 T * kAcc MMAs apart (asm volatile keeps
-    // this order).
-    constexpr int kAcc = T * RG >= 4 ? 1 : 2;
-    float ca[RG][T][kAcc][4];
+    // kAcc accumulators per (round, tile, column block).  The MMAs are issued word by word and half word by half
+    // word across all of those, so that two MMAs on the same accumulator are RG * T * NB * kAcc MMAs apart (asm
+    // volatile keeps this order).  A weight fragment is unpacked once and multiplied with every column block.
+    constexpr int kAcc = T * RG * NB >= 4 ? 1 : 2;
+    float ca[RG][T][NB][kAcc][4];
 #pragma unroll
     for (int j = 0; j < W; ++j) {
-      uint4 xv[RG];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
+      uint4 xv[RG][NB];   // .x .y .z .w: the activation pairs multiplied by nibble pairs 0..3 of word j
 #pragma unroll
-      for (int v = 0; v < RG; ++v) {
-        if constexpr (DBG == 1) xv[v] = make_uint4(kMaskA, kMaskB, kMagicA, kMagicB);
-        else xv[v] = *reinterpret_cast<const uint4*>(px[v] + j * 8);
-      }
+      for (int v = 0; v < RG; ++v)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) xv[v][nb] = *reinterpret_cast<const uint4*>(lm.xrow[nb] + xoff[v] + j * 8);
 #pragma unroll
       for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -253,18 +257,14 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st,
 #pragma unroll
           for (int tt = 0; tt < T; ++tt) {
             const uint32_t lo = w[v][2 * tt][j] >> (8 * half), hi = w[v][2 * tt + 1][j] >> (8 * half);
-            float(&c)[4] = ca[v][tt][half % kAcc];
+            const uint32_t a0 = and_or(lo, kMaskA, kMagicA), a1 = and_or(hi, kMaskA, kMagicA);
+            const uint32_t a2 = and_or(lo, kMaskB, kMagicB), a3 = and_or(hi, kMaskB, kMagicB);
             const bool first = j == 0 && half < kAcc;
-            if constexpr (DBG == 2) {   // no MMA: fold the operands into the accumulator some other way
-              const uint32_t f = and_or(lo, kMaskA, kMagicA) ^ and_or(hi, kMaskA, kMagicA) ^ and_or(lo, kMaskB, kMagicB) ^
-                                 and_or(hi, kMaskB, kMagicB) ^ (half ? xv[v].z : xv[v].x) ^ (half ? xv[v].w : xv[v].y);
-              c[0] = first ? __uint_as_float(f) : __uint_as_float(__float_as_uint(c[0]) ^ f);
-              c[1] = c[2] = c[3] = c[0];
-            } else if constexpr (DBG == 3) {   // no unpack
-              mma16816_f16(c, lo, hi, lo, hi, half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
-            } else
-            mma16816_f16(c, and_or(lo, kMaskA, kMagicA), and_or(hi, kMaskA, kMagicA), and_or(lo, kMaskB, kMagicB),
-                         and_or(hi, kMaskB, kMagicB), half ? xv[v].z : xv[v].x, half ? xv[v].w : xv[v].y, first ? zero : c);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              float(&c)[4] = ca[v][tt][nb][half % kAcc];
+              mma16816_f16(c, a0, a1, a2, a3, half ? xv[v][nb].z : xv[v][nb].x, half ? xv[v][nb].w : xv[v][nb].y, first ? zero : c);
+            }
           }
       if (j == 0 && h + RG >= C) refill();   // each shared load's first word has just been consumed
     }
@@ -278,20 +278,24 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G>& lm, uint32_t st,
         const __half2 s2hi = *reinterpret_cast<const __half2*>(&sc[2 * tt + 1][u / 2]);
         const float s_lo = (u & 1) ? __high2float(s2lo) : __low2float(s2lo);
         const float s_hi = (u & 1) ? __high2float(s2hi) : __low2float(s2hi);
-        float d[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) d[e] = kAcc == 2 ? ca[v][tt][0][e] + ca[v][tt][kAcc - 1][e] : ca[v][tt][0][e];
-        acc[tt][0] = fmaf(s_lo, fmaf(d[0], 0.0625f, cs[v].x), acc[tt][0]);
-        acc[tt][1] = fmaf(s_lo, fmaf(d[1], 0.0625f, cs[v].y), acc[tt][1]);
-        acc[tt][2] = fmaf(s_hi, fmaf(d[2], 0.0625f, cs[v].x), acc[tt][2]);
-        acc[tt][3] = fmaf(s_hi, fmaf(d[3], 0.0625f, cs[v].y), acc[tt][3]);
+        for (int nb = 0; nb < NB; ++nb) {
+          float d[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d[e] = kAcc == 2 ? ca[v][tt][nb][0][e] + ca[v][tt][nb][kAcc - 1][e] : ca[v][tt][nb][0][e];
+          acc[tt][nb][0] = fmaf(s_lo, fmaf(d[0], 0.0625f, cs[v][nb].x), acc[tt][nb][0]);
+          acc[tt][nb][1] = fmaf(s_lo, fmaf(d[1], 0.0625f, cs[v][nb].y), acc[tt][nb][1]);
+          acc[tt][nb][2] = fmaf(s_hi, fmaf(d[2], 0.0625f, cs[v][nb].x), acc[tt][nb][2]);
+          acc[tt][nb][3] = fmaf(s_hi, fmaf(d[3], 0.0625f, cs[v][nb].y), acc[tt][nb][3]);
+        }
       }
   }
 }
 
-// Stores rows row0 + pg, row0 + pg + 8 of columns 2t, 2t+1 (acc = {row lo col 2t, row lo col 2t+1, row hi ...}).
-__device__ __forceinline__ void store_tile(__half* __restrict__ y, const float (&acc)[4], int row0, int pg, int t, int M, int N) {
-  const int ra = row0 + pg, rb = ra + 8, m0 = 2 * t, m1 = 2 * t + 1;
+// Stores rows row0 + pg, row0 + pg + 8 of columns col0 + 2t, + 1 (acc = {row lo col 2t, row lo col 2t+1, row hi ...}).
+__device__ __forceinline__ void store_tile(__half* __restrict__ y, const float (&acc)[4], int row0, int col0, int pg, int t, int M,
+                                           int N) {
+  const int ra = row0 + pg, rb = ra + 8, m0 = col0 + 2 * t, m1 = m0 + 1;
   if (m0 < M) {
     if (ra < N) y[(size_t)m0 * N + ra] = __float2half_rn(acc[0]);
     if (rb < N) y[(size_t)m0 * N + rb] = __float2half_rn(acc[2]);
@@ -315,7 +319,7 @@ __device__ __forceinline__ void linger_after_abort(volatile uint32_t* abort_word
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kSplitStages = 4;   // 8 KB in flight per warp
 
-template <int G, int KSL>
+template <int G, int KSL, int NB>
 __global__ void __launch_bounds__(kThreads, 2)
 int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap16,
                            const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K, int vec_scales,
@@ -328,7 +332,7 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * S * kStage);
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + kWarps * S);
   float* sx = reinterpret_cast<float*>(smem + sx_offset(1, S));
-  float* red = reinterpret_cast<float*>(smem);   // [kWarps][32 lanes][4], after the main loop
+  float* red = reinterpret_cast<float*>(smem);   // [kWarps][32 lanes][NB][4], after the main loop
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int tile = blockIdx.x * (kWarps >> KSL) + (warp >> KSL);
@@ -362,11 +366,13 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
   pdl_launch_dependents();
   pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
 
-  class_sums<G>(x, M, K, sx);
+  class_sums<G, NB>(x, M, K, sx);
 
   const AbortCtx ctx{abort_word, status};
-  const LaneMap<G> lm(lane, x, M, K);
-  float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+  const LaneMap<G, NB> lm(lane, x, M, K);
+  float acc[1][NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) acc[0][nb][0] = acc[0][nb][1] = acc[0][nb][2] = acc[0][nb][3] = 0.f;
   const __half* srow[2];
 #pragma unroll
   for (int k = 0; k < 2; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
@@ -376,7 +382,7 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
     uint32_t sc[2][C / 2];
     load_scales<G, 1>(srow, r0, nr, vec_scales, sc);
     if (!__all_sync(0xffffffffu, wait_stage(&my_bars[i % S], (uint32_t)(i / S) & 1u, ctx))) break;
-    chunk_compute<G, 1, 2>(lm, my_ring + (uint32_t)(i % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+    chunk_compute<G, 1, (NB <= 2 ? 2 : 1), NB>(lm, my_ring + (uint32_t)(i % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
       __syncwarp();
       if (i + S < n_c) issue(i + S);
     });
@@ -385,15 +391,21 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
 
   if constexpr (KSL != 0) {
     __syncthreads();   // all warps are past their last stage: the ring becomes the reduction buffer
-    *reinterpret_cast<float4*>(red + (warp * 32 + lane) * 4) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+    float4* mine = reinterpret_cast<float4*>(red + (size_t)(warp * 32 + lane) * NB * 4);
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) mine[nb] = make_float4(acc[0][nb][0], acc[0][nb][1], acc[0][nb][2], acc[0][nb][3]);
     __syncthreads();
     if (kpart != 0) return;
     for (int p = 1; p < KS; ++p) {  // fixed order
-      const float4 o = *reinterpret_cast<const float4*>(red + ((warp + p) * 32 + lane) * 4);
-      acc[0][0] += o.x; acc[0][1] += o.y; acc[0][2] += o.z; acc[0][3] += o.w;
+      const float4* o = reinterpret_cast<const float4*>(red + (size_t)((warp + p) * 32 + lane) * NB * 4);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        acc[0][nb][0] += o[nb].x; acc[0][nb][1] += o[nb].y; acc[0][nb][2] += o[nb].z; acc[0][nb][3] += o[nb].w;
+      }
     }
   }
-  store_tile(y, acc[0], row0, lm.pg, lm.t, M, N);
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) store_tile(y, acc[0][nb], row0, 8 * nb, lm.pg, lm.t, M, N);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -413,10 +425,10 @@ struct StreamSmem {   // offsets from the 1024-byte aligned base
   static constexpr size_t counter = abort_word + 4;             // next unit of the CTA
   static constexpr size_t queue = abort_word + 16;              // int[NW][4]: units taken by a warp's producer side
   static constexpr size_t sx = queue + (size_t)NW * 16;
-  static size_t bytes(int rounds) { return 1024 + sx + (size_t)rounds * 8 * sizeof(float); }
+  static size_t bytes(int rounds, int NB) { return 1024 + sx + (size_t)rounds * 8 * NB * sizeof(float); }
 };
 
-template <int G, int RG, int NW, int MINB, int NS = 3, int DBG = 0>
+template <int G, int RG, int NW, int MINB, int NS, int NB>
 __global__ void __launch_bounds__(NW * 32, MINB)
 int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap32,
                             const __grid_constant__ CUtensorMap wmap16, const __half* __restrict__ scales,
@@ -496,18 +508,20 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   pdl_launch_dependents();
   pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
 
-  class_sums<G>(x, M, K, sx);
+  class_sums<G, NB>(x, M, K, sx);
   if (tr) tr[1] = globaltimer_ns();
 
   const AbortCtx ctx{abort_word, status};
-  const LaneMap<G> lm(lane, x, M, K);
+  const LaneMap<G, NB> lm(lane, x, M, K);
   int q = 0;   // copies consumed
   bool ok = true;
   auto run_unit = [&](auto tag, int row0) {
     constexpr int T = decltype(tag)::value;
-    float acc[T][4];
+    float acc[T][NB][4];
 #pragma unroll
-    for (int tt = 0; tt < T; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+    for (int tt = 0; tt < T; ++tt)
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) acc[tt][nb][0] = acc[tt][nb][1] = acc[tt][nb][2] = acc[tt][nb][3] = 0.f;
     const __half* srow[2 * T];
 #pragma unroll
     for (int k = 0; k < 2 * T; ++k) srow[k] = scales + (size_t)min(row0 + lm.pg + 8 * k, N - 1) * rounds;
@@ -516,13 +530,15 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
       uint32_t sc[2 * T][C / 2];
       load_scales<G, T>(srow, r0, nr, vec_scales, sc);   // before the wait: overlaps it
       if (!__all_sync(0xffffffffu, wait_stage(&my_bars[q % S], (uint32_t)(q / S) & 1u, ctx))) { ok = false; return; }
-      chunk_compute<G, T, RG, DBG>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+      chunk_compute<G, T, RG, NB>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
         __syncwarp();
         issue_next();
       });
     }
 #pragma unroll
-    for (int tt = 0; tt < T; ++tt) store_tile(y, acc[tt], row0 + tt * kTileRows, lm.pg, lm.t, M, N);
+    for (int tt = 0; tt < T; ++tt)
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) store_tile(y, acc[tt][nb], row0 + tt * kTileRows, 8 * nb, lm.pg, lm.t, M, N);
   };
   for (int taken = 0; ok; ++taken) {
     // the producer side is at least one chunk ahead, so the queue entry exists (same warp: __syncwarp orders it)
@@ -570,64 +586,98 @@ int launch_ex(void (*kernel)(KArgs...), int grid, int threads, size_t smem, cuda
   return KFB_OK;
 }
 
+constexpr int kMaxM = 32;   // 4 column blocks
+
+inline int column_blocks(int M) { return M <= 8 ? 1 : M <= 16 ? 2 : 4; }
+
 template <int G>
-inline bool fits(int K) {
-  const size_t a = smem_bytes(1, kSplitStages, K / G), b = StreamSmem<16>::bytes(K / G);
+inline bool fits(int M, int K) {
+  const int nb = column_blocks(M);
+  const size_t a = smem_bytes(1, kSplitStages, K / G, nb), b = StreamSmem<16>::bytes(K / G, nb);
   return (a > b ? a : b) <= 227u * 1024u;
 }
 
-template <int G, int KSL>
-int launch_split(const void* x, const CUtensorMap& wmap16, const void* scales, void* y, int M, int N, int K, int grid, size_t smem,
-                 int vec, unsigned int* status, const uint4& unpack, bool pdl, cudaStream_t stream) {
-  if (int rc = opt_in_shared_memory<int4_gemv_mma_split_kernel<G, KSL>>()) return rc;
-  return launch_ex(int4_gemv_mma_split_kernel<G, KSL>, grid, kThreads, smem, stream, pdl, (const __half*)x, wmap16, (const __half*)scales,
-                   (__half*)y, M, N, K, vec, status, unpack);
+struct Call {
+  const void* x; const void* scales; void* y;
+  int M, N, K, vec;
+  unsigned int* status;
+  uint4 unpack;
+  bool pdl;
+  cudaStream_t stream;
+};
+
+template <int G, int KSL, int NB>
+int launch_split(const Call& c, const CUtensorMap& wmap16, int grid) {
+  if (int rc = opt_in_shared_memory<int4_gemv_mma_split_kernel<G, KSL, NB>>()) return rc;
+  return launch_ex(int4_gemv_mma_split_kernel<G, KSL, NB>, grid, kThreads, smem_bytes(1, kSplitStages, c.K / G, NB), c.stream, c.pdl,
+                   (const __half*)c.x, wmap16, (const __half*)c.scales, (__half*)c.y, c.M, c.N, c.K, c.vec, c.status, c.unpack);
 }
 
-template <int G>
-int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, bool pdl, cudaStream_t stream) {
+template <int G, int RG, int NW, int NS, int NB>
+int launch_stream(const Call& c, const CUtensorMap& wmap32, const CUtensorMap& wmap16) {
+  if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB>>()) return rc;
+  return launch_ex(int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB>, sm_count(), NW * 32, StreamSmem<NW, NS>::bytes(c.K / G, NB),
+                   c.stream, c.pdl, (const __half*)c.x, wmap32, wmap16, (const __half*)c.scales, (__half*)c.y, c.M, c.N, c.K, c.vec,
+                   c.status, c.unpack, g_trace);
+}
+
+template <int G, int NB>
+int launch_nb(const Call& c, const void* packed) {
   constexpr int C = kChunkBytes / (G / 2);
+  const int N = c.N, K = c.K;
   const int rounds = K / G, n_chunks = ceil_div(rounds, C), tiles = ceil_div(N, kTileRows);
-  const int vec = (rounds % C == 0) && aligned16(scales);
-  const uint4 unpack = make_uint4(0x000F000Fu, 0x00F000F0u, 0x74007400u, 0x64006400u);
-  unsigned int* status = device_status_word();
-  if (!status) return KFB_ERR_CUDA;
   // packed matrix as [N rows][K / 8 words]; box = 16 (or 32) rows x 32 words, 128-byte swizzle
   CUtensorMap wmap16;
   if (int rc = make_tmap_2d_plain(&wmap16, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
                                   kTileRows, /*swizzle128=*/true))
     return rc;
   static const int cfg = [] { const char* e = getenv("KFB_GEMV_CFG"); return e ? atoi(e) : 0; }();
-  const int stream_warps = 16 * sm_count();
-  if (tiles >= 2 * stream_warps) {   // every warp of a persistent grid gets at least two tiles
+  if (tiles >= 2 * 16 * sm_count()) {   // every warp of the persistent grid gets at least two tiles
     CUtensorMap wmap32;
     if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
                                     2 * kTileRows, true))
       return rc;
-#define KFB_STREAM(NW, MINB, NS)                                                                                       \
-  do {                                                                                                                 \
-    if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, 2, NW, MINB, NS>>()) return rc;                    \
-    return launch_ex(int4_gemv_mma_stream_kernel<G, 2, NW, MINB, NS>, MINB * sm_count(), NW * 32,                       \
-                     StreamSmem<NW, NS>::bytes(rounds), stream, pdl, (const __half*)x, wmap32, wmap16,                  \
-                     (const __half*)scales, (__half*)y, M, N, K, vec, status, unpack, g_trace);                         \
-  } while (0)
-    if (cfg == 1) KFB_STREAM(16, 1, 2);
-    else if (cfg == 2) KFB_STREAM(8, 1, 3);
-    else if (cfg == 3) KFB_STREAM(8, 1, 4);
-    else KFB_STREAM(16, 1, 3);
-#undef KFB_STREAM
+    // registers: 512 threads leave 128 per thread, enough for two rounds at a time with one column block, one round
+    // with two; four column blocks run with 8 warps
+    if constexpr (NB == 1) {
+      if (cfg == 1) return launch_stream<G, 2, 16, 2, 1>(c, wmap32, wmap16);
+      if (cfg == 2) return launch_stream<G, 2, 8, 3, 1>(c, wmap32, wmap16);
+      if (cfg == 3) return launch_stream<G, 2, 8, 4, 1>(c, wmap32, wmap16);
+      return launch_stream<G, 2, 16, 3, 1>(c, wmap32, wmap16);
+    } else if constexpr (NB == 2) {
+      return launch_stream<G, 1, 16, 3, 2>(c, wmap32, wmap16);
+    } else {
+      return launch_stream<G, 1, 8, 3, 4>(c, wmap32, wmap16);
+    }
   }
   // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks)
   int ksl = 0;
   const long long want = 16LL * sm_count();
   while (ksl < 3 && (long long)tiles * (1 << ksl) < want && (2 << ksl) <= n_chunks) ++ksl;
   const int grid = ceil_div(tiles, kWarps >> ksl);
-  const size_t smem = smem_bytes(1, kSplitStages, rounds);
   switch (ksl) {
-    case 0: return launch_split<G, 0>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
-    case 1: return launch_split<G, 1>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
-    case 2: return launch_split<G, 2>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
-    default: return launch_split<G, 3>(x, wmap16, scales, y, M, N, K, grid, smem, vec, status, unpack, pdl, stream);
+    case 0: return launch_split<G, 0, NB>(c, wmap16, grid);
+    case 1: return launch_split<G, 1, NB>(c, wmap16, grid);
+    case 2: return launch_split<G, 2, NB>(c, wmap16, grid);
+    default: return launch_split<G, 3, NB>(c, wmap16, grid);
+  }
+}
+
+template <int G>
+int launch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, bool pdl, cudaStream_t stream) {
+  constexpr int C = kChunkBytes / (G / 2);
+  Call c;
+  c.x = x; c.scales = scales; c.y = y; c.M = M; c.N = N; c.K = K;
+  c.vec = ((K / G) % C == 0) && aligned16(scales);
+  c.unpack = make_uint4(0x000F000Fu, 0x00F000F0u, 0x74007400u, 0x64006400u);
+  c.status = device_status_word();
+  c.pdl = pdl;
+  c.stream = stream;
+  if (!c.status) return KFB_ERR_CUDA;
+  switch (column_blocks(M)) {
+    case 1: return launch_nb<G, 1>(c, packed);
+    case 2: return launch_nb<G, 2>(c, packed);
+    default: return launch_nb<G, 4>(c, packed);
   }
 }
 

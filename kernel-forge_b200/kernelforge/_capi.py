@@ -29,6 +29,7 @@ _SIGNATURES = {
     "kfb_pack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "kfb_dequantize": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "kfb_int4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "kfb_int4_small_batch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "kfb_int4_gemm_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "kfb_int4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                               c_void_p]),

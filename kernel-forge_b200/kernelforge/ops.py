@@ -63,15 +63,16 @@ def _check_int4_storage(x: torch.Tensor, packed: torch.Tensor, scales: torch.Ten
                          f"got {tuple(scales.shape)}")
 
 
-def _gemv_launch(x, packed, scales, group_size: int, flags: int = 0) -> torch.Tensor:
+def _gemv_launch(x, packed, scales, group_size: int, flags: int = 0, small_batch: bool = False) -> torch.Tensor:
     m, k = x.shape
     n = packed.shape[0]
     y = torch.empty(m, n, dtype=torch.float16, device=x.device)
     if n == 0:
         return y
+    entry = _capi.lib().kfb_int4_small_batch if small_batch else _capi.lib().kfb_int4_gemv
     with _capi.on_device(x.device):
-        _capi.check(_capi.lib().kfb_int4_gemv(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(),
-                                              m, n, k, group_size, flags, _capi.stream_ptr(x.device)))
+        _capi.check(entry(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(),
+                          m, n, k, group_size, flags, _capi.stream_ptr(x.device)))
     return y
 
 
@@ -98,6 +99,18 @@ def int4_gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group
     _check_int4_storage(x, packed, scales, group_size)
     return _gemv_launch(x, packed, scales, int(group_size))
 
+
+def int4_small_batch(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """The GEMV's weight-streaming kernel for M in [1, SMALL_BATCH_MAX_M]: every block of 8 batch rows is one more
+    MMA on the already unpacked weight fragment.  Not in the reference (its GEMV stops at M = 8)."""
+    _check_int4(x, packed, scales, group_size)
+    if not 1 <= x.shape[0] <= SMALL_BATCH_MAX_M:
+        raise ValueError(f"int4_small_batch handles M in [1, {SMALL_BATCH_MAX_M}], got M={x.shape[0]}")
+    _check_int4_storage(x, packed, scales, group_size)
+    return _gemv_launch(x, packed, scales, int(group_size), small_batch=True)
+
+
+SMALL_BATCH_MAX_M = 32
 
 # Largest M served by the GEMV; from M = GEMV_MAX_M + 1 on the tensor-core GEMM is used.  The
 # reference measured 7 on its GPU (kernelforge/ops.py:193, bench/sweep_int4_dispatch.py:47-57).

@@ -46,6 +46,27 @@ def test_gemv_large_n_streaming_path(m, n, k, group):
     run_case(ops.int4_gemv, m, n, k, group, f"large_n m{m} n{n} k{k} g{group}")
 
 
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("m", [9, 12, 16, 17, 24, 32])
+@pytest.mark.parametrize("layer", ["qwen_down", "tinyllama_gate_up", "ragged"])
+def test_small_batch_shapes(layer, m, group):
+    """M up to 32 on the weight-streaming kernel (2 and 4 column blocks), split-K shapes and a ragged N."""
+    n, k = {"ragged": (1000, 1280)}.get(layer) or LAYER_SHAPES[layer]
+    run_case(ops.int4_small_batch, m, n, k, group, f"small_batch {layer} m{m} g{group}")
+
+
+@pytest.mark.parametrize("m,n,k,group", [(16, 80005, 256, 128), (32, 76800, 192, 64), (11, 94720, 128, 128)])
+def test_small_batch_large_n_streaming_path(m, n, k, group):
+    run_case(ops.int4_small_batch, m, n, k, group, f"small_batch large_n m{m} n{n}")
+
+
+def test_small_batch_rejects_m33():
+    _, x, packed, scales, _ = int4_case(33, 64, 256, 128, seed=0)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    with pytest.raises(ValueError, match=r"M in \[1, 32\]"):
+        ops.int4_small_batch(xs, ps, ss, 128)
+
+
 @pytest.mark.parametrize("impl", ["cuda_core"])
 def test_gemv_cuda_core_kernel_still_matches(impl):
     """The tensor-core-free kernel stays reachable through flag bit 1; bit 0 (dependent launch) works with both."""
