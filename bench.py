@@ -232,7 +232,7 @@ def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict
     from kernelforge import _capi, ops
     from kernelforge import quantize as kq
     nbytes = n * k // 2 + 2 * n * (k // group) + 2 * m * k + 2 * m * n
-    copies = max(4, math.ceil(3 * L2_BYTES / nbytes))
+    copies = max(4 if nbytes < L2_BYTES else 2, math.ceil(3 * L2_BYTES / nbytes))
     g = torch.Generator().manual_seed(0)
     qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), group)
     packed = [qw.packed.clone() for _ in range(copies)]
@@ -466,8 +466,15 @@ def main():
         also["int4_gemv_m1_stream_180224x2048"] = dict(gs, roofline={
             "bound": "hbm", "achieved": None if sbest is None else sbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": None if sbest is None else sbest / world / peaks["hbm_gbs"],
-            "traffic": 193566720,  # ncu: 190.36 MB read + 3.20 MB written per launch (profiles/int4_gemv_M1_N180224_K2048.md)
+            "traffic": 194900000,  # ncu: 190.5 MB read + 4.4 MB written per launch (profiles/int4_gemv_M1_N180224_K2048.md)
             "note": "same kernel on 32 stacked copies of the 5632x2048 weight: the streaming regime of the GEMV"})
+        for mm in (1, 8):
+            gl = bench_int4_gemv(args, world, device, mm, 5632 * 128, 2048)
+            lbest = max((gl[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gl.get(k, {})), default=None)
+            also[f"int4_gemv_m{mm}_stream_720896x2048"] = dict(gl, roofline={
+                "bound": "hbm", "achieved": None if lbest is None else lbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": None if lbest is None else lbest / world / peaks["hbm_gbs"], "traffic": None,
+                "note": "128 stacked copies (738 MB): long enough for launch, ramp and tail (~10 us) not to dominate"})
         if world > 1:
             also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
         if world == 1:

@@ -55,7 +55,6 @@
 #include "common.cuh"
 #include "sm100.cuh"
 
-#include <cstdlib>
 #include <type_traits>
 
 namespace kfb {
@@ -588,12 +587,15 @@ int launch_ex(void (*kernel)(KArgs...), int grid, int threads, size_t smem, cuda
 
 constexpr int kMaxM = 32;   // 4 column blocks
 
+// N from which the persistent kernel is used: every warp of its grid (16 per SM) gets at least two 16-row tiles.
+inline bool uses_stream_kernel(int N) { return ceil_div(N, kTileRows) >= 2 * 16 * sm_count(); }
+
 inline int column_blocks(int M) { return M <= 8 ? 1 : M <= 16 ? 2 : 4; }
 
 template <int G>
 inline bool fits(int M, int K) {
   const int nb = column_blocks(M);
-  const size_t a = smem_bytes(1, kSplitStages, K / G, nb), b = StreamSmem<16>::bytes(K / G, nb);
+  const size_t a = smem_bytes(1, kSplitStages, K / G, nb), b = StreamSmem<16, 2>::bytes(K / G, nb);
   return (a > b ? a : b) <= 227u * 1024u;
 }
 
@@ -631,24 +633,18 @@ int launch_nb(const Call& c, const void* packed) {
   if (int rc = make_tmap_2d_plain(&wmap16, packed, /*elem_bytes=*/4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
                                   kTileRows, /*swizzle128=*/true))
     return rc;
-  static const int cfg = [] { const char* e = getenv("KFB_GEMV_CFG"); return e ? atoi(e) : 0; }();
-  if (tiles >= 2 * 16 * sm_count()) {   // every warp of the persistent grid gets at least two tiles
+  if (uses_stream_kernel(N)) {   // every warp of the persistent grid gets at least two tiles
     CUtensorMap wmap32;
     if (int rc = make_tmap_2d_plain(&wmap32, packed, 4, (uint64_t)K / 8, (uint64_t)N, (uint64_t)K / 2, kChunkBytes / 4,
                                     2 * kTileRows, true))
       return rc;
-    // registers: 512 threads leave 128 per thread, enough for two rounds at a time with one column block, one round
-    // with two; four column blocks run with 8 warps
-    if constexpr (NB == 1) {
-      if (cfg == 1) return launch_stream<G, 2, 16, 2, 1>(c, wmap32, wmap16);
-      if (cfg == 2) return launch_stream<G, 2, 8, 3, 1>(c, wmap32, wmap16);
-      if (cfg == 3) return launch_stream<G, 2, 8, 4, 1>(c, wmap32, wmap16);
-      return launch_stream<G, 2, 16, 3, 1>(c, wmap32, wmap16);
-    } else if constexpr (NB == 2) {
-      return launch_stream<G, 1, 16, 3, 2>(c, wmap32, wmap16);
-    } else {
-      return launch_stream<G, 1, 8, 3, 4>(c, wmap32, wmap16);
-    }
+    // Two stages (8 KB in flight per warp, 128 KB per SM) measured faster than three: the memory system is saturated
+    // either way and the shared memory not taken by the ring is L1 for the activations (N = 180224, K = 2048:
+    // 41.7 vs 45.5 us at M = 1, 48.6 vs 54.4 us at M = 8).  Registers: 512 threads leave 128 per thread, enough
+    // for two rounds at a time with one column block, one round with two; four column blocks run with 8 warps.
+    if constexpr (NB == 1) return launch_stream<G, 2, 16, 2, 1>(c, wmap32, wmap16);
+    else if constexpr (NB == 2) return launch_stream<G, 1, 16, 2, 2>(c, wmap32, wmap16);
+    else return launch_stream<G, 1, 8, 3, 4>(c, wmap32, wmap16);
   }
   // split K over the warps of a CTA until the grid offers about 16 warps per SM (never more warps than chunks)
   int ksl = 0;

@@ -112,12 +112,22 @@ def int4_small_batch(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor
 
 SMALL_BATCH_MAX_M = 32
 
-# Largest M served by the GEMV; from M = GEMV_MAX_M + 1 on the tensor-core GEMM is used.  The
-# reference measured 7 on its GPU (kernelforge/ops.py:193, bench/sweep_int4_dispatch.py:47-57).
-# On B200, summed over the four layer shapes (5632x2048, 2048x2048, 8960x1536, 1536x8960) under a
-# CUDA graph, the GEMV takes 17.0 / 24.3 / 38.5 / 66.1 us at M = 1 / 2 / 4 / 8 and the GEMM a flat
-# 38-40 us up to M = 16, so the crossover sits between M = 4 and M = 5.
-GEMV_MAX_M = 4
+# Largest M served by the GEMV entry point.  The reference measured 7 on its GPU (kernelforge/ops.py:193,
+# bench/sweep_int4_dispatch.py:47-57).  On B200 (CUDA graph, L2-cold weights, us, GEMV / GEMM):
+#   5632x2048  M=4 7.1/11.8  M=8 9.5/12.2    2048x2048  3.8/8.2  4.4/8.3    8960x1536  6.0/12.2  7.1/12.6
+#   1536x8960  8.7/12.2  11.8/12.3           11264x2048  10.1/18.0  11.4/18.0   32000x2048  17.8/24.4  20.8/24.3
+# so the GEMV keeps all of its range.
+GEMV_MAX_M = 8
+
+
+def _small_batch_wins(m: int, n: int, k: int) -> bool:
+    """Where int4_small_batch measured faster than the tcgen05 GEMM for 8 < M <= 16 (same method as above):
+    M = 12: 2048x2048 5.9/8.4, 8960x1536 9.1/13.1, 11264x2048 16.4/18.0, 128256x4096 122/153, but 1536x8960
+    16.1/12.3 and 32000x2048 29.4/24.5;  M = 16: 2048x2048 6.5/8.4, 8960x1536 9.6/13.4, 128256x4096 128/153, but
+    5632x2048 14.8/12.6.  From M = 24 on the GEMM wins everywhere."""
+    if n >= 75776:                       # the persistent streaming kernel
+        return m <= 16
+    return m <= 12 and k <= 2048 and n <= 16384
 
 
 def int4_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
@@ -140,11 +150,13 @@ def int4_gemm_ragged(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor
 def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
     """y = x @ W_hat^T for INT4 weights from kernelforge.quantize, choosing the kernel by M.
 
-    M <= GEMV_MAX_M: the bandwidth-bound GEMV (CUDA cores, FP32 accumulation).
-    Larger M: the tensor-core GEMM.
+    M <= GEMV_MAX_M: the bandwidth-bound GEMV (FP32 accumulation); a little above it, where measured faster, the same
+    kernel with more batch columns (int4_small_batch).  Larger M: the tcgen05 GEMM.
     """
     if x.shape[0] <= GEMV_MAX_M:
         return int4_gemv(x, packed, scales, group_size)
+    if x.shape[0] <= 16 and _small_batch_wins(x.shape[0], packed.shape[0], x.shape[1]):
+        return int4_small_batch(x, packed, scales, group_size)
     # the GEMM kernel takes any N; only the public int4_gemm wrapper keeps the reference's N % 64 rule,
     # so an nn.Linear with an odd N that worked below the reference's crossover (M <= 7) keeps working
     return int4_gemm_ragged(x, packed, scales, group_size)
