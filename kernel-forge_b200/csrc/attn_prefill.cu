@@ -8,9 +8,13 @@
 //   * 192 threads in three roles:
 //       warp 4  (1 thread)  TMA producer: Q once, K and V tiles of 128 keys through mbarrier rings,
 //                           128-byte-swizzled shared-memory tiles (a D=64 row is exactly 128 bytes)
-//       warp 5  (1 thread)  tcgen05.mma issuer: S = Q K^T (SS form, both operands K-major) into
-//                           TMEM, O += P V (TS form: P is read from TMEM, V is the MN-major
-//                           shared-memory operand, so V needs no transpose)
+//       warp 5  (1 thread)  tcgen05.mma issuer: S = Q K^T into TMEM and O += P V, both in the TS form
+//                           (A operand read from TMEM): Q is written to TMEM once by the softmax
+//                           threads, P every step; K is the K-major and V the MN-major shared-memory
+//                           operand, so V needs no transpose.  An SS-form MMA re-reads its 4 KB A tile
+//                           from shared memory every time (6 KB per M128 N64 K16 instruction at 128
+//                           bytes per clock = 48 clocks against 16 of tensor time); with Q in TMEM
+//                           only the 2 KB of K are read
 //       warps 0-3 (128 thr) softmax: thread r owns query row r = TMEM lane r, so row max / row sum
 //                           need no shuffles; the 64 scores of a step are loaded from TMEM once and
 //                           kept in registers for both the maximum and the exponentials; P is rounded
@@ -29,7 +33,8 @@
 //   * GQA: kv head = h / (H / Hk); TMA zero-fills rows past Nq / Nk, those keys are masked.
 //
 // TMEM columns of a CTA (256 allocated): S buffer b of step t = 2j + b at [64 b, 64 b + 64), with
-// P of the same step (16-bit, 32 columns) aliased on its first 32 columns; O [128, 128 + D).
+// P of the same step (16-bit, 32 columns) aliased on its first 32 columns; O [128, 128 + D);
+// Q (16-bit, D / 2 columns, row r in lane r) at [192, 192 + D / 2).
 // tcgen05.mma instructions of one thread execute in issue order, so QK(t+2), which overwrites the
 // columns of P(t), cannot pass PV(t), which reads them.
 //
@@ -55,6 +60,7 @@ constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColO = 128;   // S / P buffer b starts at column 64 b
+constexpr uint32_t kColQ = 192;   // head dim 64 only: O ends at 192
 constexpr int kHalfBytes = kBlockN * 128;  // one 64-column half of a tile: 128 rows x 128 bytes
 constexpr int kStepBytes = kStepN * 128;   // 64 rows of 128 bytes inside such a half
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -145,9 +151,10 @@ __device__ __forceinline__ float exp_and_store(const uint32_t (&v)[2][32], uint3
 // exponential unit.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 2)
-attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+attn_prefill_kernel(const void* __restrict__ q_ptr, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, void* __restrict__ o_ptr, int H, int Hk, int Nq, int Nk,
                     int causal, float scale_log2, unsigned int* status, unsigned long long* trace) {
+  static_assert(D == 64, "Q, two S buffers and O share 256 TMEM columns only for head dim 64");
   using L = Layout<D>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -177,7 +184,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int n_tiles = (n_steps + 1) / 2;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 128);   // every softmax thread has stored its row of Q to TMEM
     for (int s = 0; s < S; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -212,13 +219,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_arrive_expect_tx(q_full, L::kTile);
-#pragma unroll
-      for (int half = 0; half < D / 64; ++half)
-        tma_load_4d(smem + L::kQ + half * kHalfBytes, &tm_q, q_full, half * 64, q0, h, b);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % S;
         const uint32_t ph = (uint32_t)(j / S) & 1u;
@@ -239,7 +241,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t idesc_qk = idesc_f16(kBlockM, kStepN, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(kBlockM, D, kBf16 ? 1 : 0, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + L::kQ);
       auto issue_qk = [&](int t) -> bool {   // S buffer (t & 1) = Q K(step t)^T
         const int j = t >> 1, hh = t & 1, s = j % S;
         // the second step of a tile finds it already waited for (same thread, same phase)
@@ -249,7 +250,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (uint32_t)(kk / 4) * kHalfBytes + (uint32_t)(kk % 4) * 32u;
-          mma_ss(tmem_base + (uint32_t)hh * kStepN, smem_desc_sw128(q_addr + off, 16, 1024),
+          mma_ts(tmem_base + (uint32_t)hh * kStepN, tmem_base + kColQ + (uint32_t)kk * 8u,
                  smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
         if (hh == 1 || t == n_steps - 1) tc_commit(&k_empty[s]);
@@ -257,6 +258,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         return true;
       };
       bool ok = mbar_wait(q_full, 0, ctx, kWaitQ);
+      tc_fence_after_sync();
       ok = ok && issue_qk(0);
       if (n_steps > 1) ok = ok && issue_qk(1);
       for (int t = 0; ok && t < n_steps; ++t) {
@@ -285,6 +287,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int row = threadIdx.x;  // query row inside the tile == TMEM lane
     const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
     const uint32_t o_tmem = tmem_base + kColO + lane_bits;
+    {
+      // this thread's row of Q: global -> registers -> TMEM (rows past Nq: zeros, never stored)
+      uint32_t qr[D / 2];
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(q_ptr) +
+                                                        ((((size_t)b * H + h) * Nq + (size_t)(q0 + row)) * D) * 2);
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const uint4 u = q0 + row < Nq ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+        qr[4 * i + 0] = u.x; qr[4 * i + 1] = u.y; qr[4 * i + 2] = u.z; qr[4 * i + 3] = u.w;
+      }
+      tmem_st_x32(tmem_base + kColQ + lane_bits, qr);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(q_full);
+    }
     float m_base = -INFINITY;  // the base O and l are currently expressed in (log2 units)
     float l_run = 0.f;
     bool ok = true;
@@ -728,10 +745,15 @@ int launch(const Problem& p, const CUtensorMap& tq, const CUtensorMap& tk, const
   const dim3 grid(ceil_div(p.Nq, kBlockM), p.H, p.B);
   const float scale_log2 = p.scale * 1.4426950408889634f;
   static const bool force_serial = [] { const char* e = getenv("KFB_ATTN_SERIAL"); return e && e[0] == '1'; }();
-  if (D == 64 && !force_serial)
-    attn_prefill_kernel<D, kBf16><<<grid, kThreads, L::kAlloc, stream>>>(tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal,
-                                                                        scale_log2, status, g_trace);
-  else
+  bool launched = false;
+  if constexpr (D == 64) {
+    if (!force_serial) {
+      attn_prefill_kernel<D, kBf16><<<grid, kThreads, L::kAlloc, stream>>>(p.q, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal,
+                                                                          scale_log2, status, g_trace);
+      launched = true;
+    }
+  }
+  if (!launched)
     serial::attn_prefill_serial_kernel<D, kBf16><<<grid, kThreads, L::kAlloc, stream>>>(tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk,
                                                                                       p.causal, scale_log2, 0, status, g_trace);
   KFB_LAUNCH_CHECK("attn_prefill_kernel");
