@@ -498,7 +498,7 @@ def main():
                      "frac": fa["tflops"] / world / peaks["bf16_tflops"],
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload from the ncu
                      # capture summarised in profiles/attn_prefill_B2_H16_N2048_D64.md (q, k, v read once = 25.2 MB)
-                     "traffic": 25219840 if (not args.shape and not args.causal) else None,
+                     "traffic": 25205760 if (not args.shape and not args.causal) else None,
                      "peak_source": f"{peak_kind} dense bf16 cuBLAS burst", "kernel": "attn_prefill_kernel<64,fp16>"},
         "also": also,
     })
