@@ -225,7 +225,7 @@ def bench_decode_attn(args, world, device, batch=8, nk=4096) -> dict:
             "bytes_per_call": nbytes, "batch": batch, "nk": nk, "n_sets": n_sets}
 
 
-def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict:
+def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128, stack=1) -> dict:
     """INT4 linear at M=1.  Three figures on the same algorithmic bytes: a CUDA graph of back-to-back calls
     over distinct weight copies (what a decode step sees; every call reads L2-cold weights), the same with
     programmatic dependent launch, and single event-timed calls (latency)."""
@@ -234,9 +234,10 @@ def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128) -> dict
     nbytes = n * k // 2 + 2 * n * (k // group) + 2 * m * k + 2 * m * n
     copies = max(4 if nbytes < L2_BYTES else 2, math.ceil(3 * L2_BYTES / nbytes))
     g = torch.Generator().manual_seed(0)
-    qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), group)
-    packed = [qw.packed.clone() for _ in range(copies)]
-    scales = [qw.scales.clone() for _ in range(copies)]
+    # `stack` > 1: the weight is `stack` copies of an (n / stack) x k matrix stacked along N (cheap to build, same kernel work)
+    qw = kq.quantize_weight((torch.randn(n // stack, k, generator=g) * 0.02).to(device), group)
+    packed = [qw.packed.repeat(stack, 1) for _ in range(copies)]
+    scales = [qw.scales.repeat(stack, 1) for _ in range(copies)]
     x = torch.randn(m, k, generator=g).half().to(device)
     ys = [torch.empty(m, n, dtype=torch.float16, device=device) for _ in range(copies)]
     lib = _capi.lib()
@@ -461,7 +462,7 @@ def main():
             "bound": "hbm", "achieved": None if best is None else best / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": None if best is None else best / world / peaks["hbm_gbs"], "traffic": None,
             "note": "achieved = sustained back-to-back calls on L2-cold weight copies; single_call is latency"})
-        gs = bench_int4_gemv(args, world, device, 1, 5632 * 32, 2048)
+        gs = bench_int4_gemv(args, world, device, 1, 5632 * 32, 2048, stack=32)
         sbest = max((gs[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gs.get(k, {})), default=None)
         also["int4_gemv_m1_stream_180224x2048"] = dict(gs, roofline={
             "bound": "hbm", "achieved": None if sbest is None else sbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -469,7 +470,7 @@ def main():
             "traffic": 194900000,  # ncu: 190.5 MB read + 4.4 MB written per launch (profiles/int4_gemv_M1_N180224_K2048.md)
             "note": "same kernel on 32 stacked copies of the 5632x2048 weight: the streaming regime of the GEMV"})
         for mm in (1, 8):
-            gl = bench_int4_gemv(args, world, device, mm, 5632 * 128, 2048)
+            gl = bench_int4_gemv(args, world, device, mm, 5632 * 128, 2048, stack=128)
             lbest = max((gl[k]["gbs"] for k in ("graph", "graph_pdl") if "gbs" in gl.get(k, {})), default=None)
             also[f"int4_gemv_m{mm}_stream_720896x2048"] = dict(gl, roofline={
                 "bound": "hbm", "achieved": None if lbest is None else lbest / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -331,12 +331,12 @@ int gemv_entry(const char* what, int max_m, const void* x, const void* packed, c
   cudaStream_t s = (cudaStream_t)stream;
   // Two kernels: the mma.sync formulation (int4_gemv_mma.cuh) and the CUDA-core one of this file, which is
   // issue-bound on B200 and whose time grows with M.  Measured under a CUDA graph on L2-cold weights (us, CUDA core /
-  // mma):  5632x2048  M=1 4.2/5.9  M=2 5.9/7.0  M=4 9.2/7.1  M=8 16.1/9.5;   8960x1536  5.3/5.5  7.8/5.7  11.6/6.0
-  // 20.2/7.1;   2048x5632  6.1/5.3  8.8/6.0  14.2/6.7  32.0/9.1;   32000x2048  13.3/14.8  18.2/15.9  36.4/17.8
-  // 68.4/20.8;   128256x4096  76/68  132/73  273/84  521/90.  So: M = 1 takes the CUDA-core kernel unless N is
-  // large enough for the persistent streaming kernel, M >= 2 takes mma.  Flag bit 1 or KFB_GEMV_IMPL=cuda_core
-  // forces the CUDA-core kernel (M <= 8), KFB_GEMV_IMPL=mma the other; K too long for the class sums to fit in
-  // shared memory also goes to the CUDA-core kernel.
+  // mma):  5632x2048  M=1 4.2/5.0  M=2 5.9/5.4  M=4 9.2/6.3  M=8 16.1/7.7;   8960x1536  5.3/5.4  7.8/5.7  11.6/6.0
+  // 20.2/7.0;   11264x2048  6.3/9.0  8.9/9.7  16.2/10.5  25.7/12.3;   2048x5632  6.1/5.3  8.8/5.9  14.2/6.7  32.0/9.0;
+  // 32000x2048  13.3/12.6  18.2/13.7  36.4/15.2  68.4/18.3;   128256x4096  76/62  132/64  273/67  521/80.  So: M = 1 takes
+  // the CUDA-core kernel unless N is large enough for the persistent streaming kernel, M >= 2 takes mma.  Flag bit 1
+  // or KFB_GEMV_IMPL=cuda_core forces the CUDA-core kernel (M <= 8), KFB_GEMV_IMPL=mma the other; K too long for the
+  // class sums to fit in shared memory also goes to the CUDA-core kernel.
   static const int forced = [] { const char* e = getenv("KFB_GEMV_IMPL"); return !e ? 0 : e[0] == 'c' ? 1 : e[0] == 'm' ? 2 : 0; }();
   const bool fits = group == 128 ? gemv_mma::fits<128>(M, K) : gemv_mma::fits<64>(M, K);
   const bool prefer_mma = forced == 2 || (forced == 0 && !(flags & 2) && (M >= 2 || gemv_mma::uses_stream_kernel(N)));

@@ -114,20 +114,20 @@ SMALL_BATCH_MAX_M = 32
 
 # Largest M served by the GEMV entry point.  The reference measured 7 on its GPU (kernelforge/ops.py:193,
 # bench/sweep_int4_dispatch.py:47-57).  On B200 (CUDA graph, L2-cold weights, us, GEMV / GEMM):
-#   5632x2048  M=4 7.1/11.8  M=8 9.5/12.2    2048x2048  3.8/8.2  4.4/8.3    8960x1536  6.0/12.2  7.1/12.6
-#   1536x8960  8.7/12.2  11.8/12.3           11264x2048  10.1/18.0  11.4/18.0   32000x2048  17.8/24.4  20.8/24.3
+#   5632x2048  M=4 6.3/11.8  M=8 7.7/12.1    2048x2048  3.8/8.1  4.4/8.2    8960x1536  6.0/12.2  7.0/12.6
+#   1536x8960  8.6/12.1  11.8/12.2           11264x2048  10.5/18.0  12.3/17.9   32000x2048  15.2/24.3  18.3/24.3
 # so the GEMV keeps all of its range.
 GEMV_MAX_M = 8
 
 
 def _small_batch_wins(m: int, n: int, k: int) -> bool:
-    """Where int4_small_batch measured faster than the tcgen05 GEMM for 8 < M <= 16 (same method as above):
-    M = 12: 2048x2048 5.9/8.4, 8960x1536 9.1/13.1, 11264x2048 16.4/18.0, 128256x4096 122/153, but 1536x8960
-    16.1/12.3 and 32000x2048 29.4/24.5;  M = 16: 2048x2048 6.5/8.4, 8960x1536 9.6/13.4, 128256x4096 128/153, but
-    5632x2048 14.8/12.6.  From M = 24 on the GEMM wins everywhere."""
+    """Where int4_small_batch measured faster than the tcgen05 GEMM for 8 < M <= 16 (same method as above, us):
+    M = 12: 5632x2048 10.1/12.3, 2048x2048 5.9/8.3, 8960x1536 9.1/13.1, 11264x2048 16.6/18.0, 128256x4096 128/153, but
+    1536x8960 16.1/12.3, 2048x5632 12.1/11.4 and 32000x2048 26.8/24.4;  M = 16: 5632x2048 11.3/12.6, 2048x2048 6.5/8.3,
+    8960x1536 9.6/13.3, 11264x2048 18.3/18.0, 128256x4096 133/153.  From M = 24 on the GEMM wins everywhere."""
     if n >= 75776:                       # the persistent streaming kernel
         return m <= 16
-    return m <= 12 and k <= 2048 and n <= 16384
+    return m <= 16 and k <= 2048 and n <= 16384
 
 
 def int4_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
