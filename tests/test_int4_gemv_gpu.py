@@ -67,6 +67,30 @@ def test_small_batch_rejects_m33():
         ops.int4_small_batch(xs, ps, ss, 128)
 
 
+def test_gemv_streaming_path_dependent_launch_and_graph():
+    """The persistent kernel launched with programmatic dependent launch, back to back inside a CUDA graph, gives the
+    same bits as a plain call (its weight prefetch may start before the previous kernel has finished, x and y may not)."""
+    from kernelforge import _capi
+    _, x, packed, scales, ref = int4_case(3, 80005, 256, 128, seed=21)
+    xs, ps, ss = (torch.from_numpy(a).cuda() for a in (x, packed, scales))
+    plain = ops.int4_gemv(xs, ps, ss, 128)
+    ys = [torch.zeros(3, 80005, dtype=torch.float16, device="cuda") for _ in range(3)]
+    lib = _capi.lib()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for y in ys:
+                _capi.check(lib.kfb_int4_gemv(xs.data_ptr(), ps.data_ptr(), ss.data_ptr(), y.data_ptr(), 3, 80005, 256, 128, 1,
+                                              side.cuda_stream))
+    graph.replay()
+    torch.cuda.synchronize()
+    for y in ys:
+        assert torch.equal(y, plain)
+    assert_int4_close(plain, ref, "streaming path")
+    assert _capi.device_status(xs.device) == 0
+
+
 @pytest.mark.parametrize("impl", ["cuda_core"])
 def test_gemv_cuda_core_kernel_still_matches(impl):
     """The tensor-core-free kernel stays reachable through flag bit 1; bit 0 (dependent launch) works with both."""
