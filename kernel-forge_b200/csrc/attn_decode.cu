@@ -15,6 +15,8 @@
 //     partial (O, m, l) per split written to the caller's workspace and combined in split order by
 //     a second small kernel => deterministic.  With one split the result is written directly.
 #include "attn.cuh"
+
+#include <cstdlib>
 #include "sm100.cuh"
 
 namespace kfb {
@@ -371,6 +373,17 @@ SplitPlan plan_splits(int B, int H, int Hk, int Nk, int D) {
     const double cost = full * (per + 1.0) + (waves <= 1.0 ? (1.0 - waves) * 0.01 : 0.0);
     const double score = 1.0 / cost;
     if (score > best_score * 1.0001) { best_score = score; best = real; }
+  }
+  // A split plan needs the merge kernel, a second launch worth about 12 key tiles of a CTA; when the unsplit plan is
+  // within that, it wins (end-to-end decode of the 22-layer model at a cache of 784: 0.849 -> 0.843 ms per step at batch
+  // 1, 1.125 -> 1.099 at batch 8, 1.630 -> 1.548 at batch 32; with 24 tiles a lone 1024-key call gets slower).
+  constexpr double kMergeCostTiles = 12.0;
+  if (best > 1) {
+    const int per = ceil_div(tiles, best);
+    const double waves = (double)(groups * best) / (double)slots;
+    const double full = waves <= 1.0 ? 1.0 : (double)(long long)(waves + 0.999999);
+    const double unsplit = (double)(long long)((double)groups / (double)slots + 0.999999) * (tiles + 1.0);
+    if (full * (per + 1.0) + kMergeCostTiles >= unsplit) best = 1;
   }
   const int tiles_per_split = ceil_div(tiles, best);
   p.keys_per_split = tiles_per_split * kTileKeys;
