@@ -106,22 +106,6 @@ int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint6
   return KFB_OK;
 }
 
-int make_tmap_3d_u32_sw128(CUtensorMap* out, const void* base, const uint64_t dims[3], const uint64_t strides_bytes[2],
-                           const uint32_t box[3]) {
-  if (int rc = resolve_encoder()) return rc;
-  cuuint64_t gdim[3] = {dims[0], dims[1], dims[2]};
-  cuuint64_t gstr[2] = {strides_bytes[0], strides_bytes[1]};
-  cuuint32_t bdim[3] = {box[0], box[1], box[2]};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), gdim, gstr, bdim, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(KFB_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d (dims %llu,%llu,%llu)", (int)r,
-                (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2]);
-  return KFB_OK;
-}
-
 int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
                        const uint64_t strides_bytes[3], const uint32_t box[4]) {
   if (int rc = resolve_encoder()) return rc;

@@ -62,10 +62,6 @@ unsigned int* device_status_word();
 // dims[0] is the innermost (dense) extent; strides_bytes[i] is the stride of dims[i+1].
 int make_tmap_4d_sw128(CUtensorMap* out, const void* base, int dtype, const uint64_t dims[4],
                        const uint64_t strides_bytes[3], const uint32_t box[4]);
-// Tiled 3-D tensor map with 128-byte swizzle over 32-bit elements; dims[0] is the innermost (dense) extent and
-// strides_bytes[i] the stride of dims[i+1] (any multiple of 16 bytes, in any order of magnitude).
-int make_tmap_3d_u32_sw128(CUtensorMap* out, const void* base, const uint64_t dims[3], const uint64_t strides_bytes[2],
-                           const uint32_t box[3]);
 // Tiled 2-D tensor map over 32-bit elements (the packed INT4 words), without swizzle or with the 128-byte swizzle
 // (box_inner <= 32 elements then).
 int make_tmap_2d_plain(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,

@@ -1,4 +1,5 @@
-// INT4 GEMV (M = 1..8) with the dot products on mma.sync fragments.
+// INT4 GEMV (M = 1..8, and up to 32 batch rows through the small-batch entry) with the dot products on mma.sync
+// fragments.
 //
 // Why this exists: on B200 the CUDA-core GEMV (int4_gemv.cu) is issue-bound, not HBM-bound -- logic/shift ops
 // issue at half the FP32 rate, so unpack + one FMA per weight + operand extraction cost ~3 issue slots per weight
@@ -18,13 +19,16 @@
 //     activation fragment;
 //  4. the request rate of the TMA unit: untiled bulk copies of 256 bytes (one per row) stop at ~2.5 TB/s, i.e. one
 //     request per ~29 clocks per SM -> one tiled copy (tensor map over the packed matrix, box = R rows x 128 bytes)
-//     per warp and chunk, 2 or 4 KB per request.
-//
+//     per warp and chunk, 2 or 4 KB per request;
 //  5. tail and prologue: with one CTA per 256 rows the last wave of CTAs is partly empty (2.4 waves at N = 180224:
 //     21 % of the time) and every CTA waits ~2 us at the barrier behind the class sums -> for large N the kernel
-//     is persistent (two CTAs per SM, class sums once), every warp owns a contiguous range of 16-row tiles whose
-//     length differs by at most one between warps, processed as pairs plus one single tile, and its ring keeps
-//     streaming across tile boundaries.
+//     is persistent (one CTA of 16 warps per SM, class sums once), the tiles are split evenly over the CTAs, the warps
+//     of a CTA take pairs of tiles and finally single tiles from a shared-memory counter, and a warp's ring keeps
+//     streaming across tile boundaries;
+//  6. the memory system: with all of that the SMs wait for data (~5 us of queueing at 8-12 KB in flight per warp);
+//     two stages per warp instead of three are faster (less queueing, more L1 left for the activations).  What is
+//     left at N = 180224 is ~10 us of launch, class sums, ramp and tail per launch (72 % of the copy peak; 88 % on
+//     763 MB).
 //
 // Shared-memory stage of a warp: R = 16 or 32 rows x 128 bytes (2 rounds of G = 128, 4 of G = 64), written by the TMA
 // with the 128-byte swizzle (16-byte piece j of row r sits at piece j ^ (r & 7)).  Fragment row slot g of a tile
