@@ -115,7 +115,8 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     return world, rank, local
 
 
@@ -277,13 +278,13 @@ def bench_int4_gemv(args, world, device, m=1, n=5632, k=2048, group=128, stack=1
     return out
 
 
-def bench_decode_e2e(args, device, batch: int, prompt_len=512, new_tokens=256) -> dict:
+def bench_decode_e2e(args, device, batch: int, prompt_len=512, new_tokens=256, tp_group=None) -> dict:
     """Greedy decode of a random-init TinyLlama-1.1B-architecture model (22 layers, hidden 2048, 32 heads, 4 KV heads,
     head dim 64, SiLU MLP 5632, vocab 32000; weights ~ N(0, 0.02)), all decoder linears INT4 g128, fused attention,
     static KV cache, one CUDA graph per decode step.  Prompt = uniform random token ids (stands in for the
     reference's WikiText-2 prompt, which is not available offline).  tok/s = batch * steps / device time."""
     from kernelforge.llama_decode import TINYLLAMA_1B, LlamaInt4Decoder
-    dec = LlamaInt4Decoder.random_init(TINYLLAMA_1B, device, batch, prompt_len + new_tokens + 8, seed=0)
+    dec = LlamaInt4Decoder.random_init(TINYLLAMA_1B, device, batch, prompt_len + new_tokens + 8, seed=0, tp_group=tp_group)
     ids = torch.randint(0, TINYLLAMA_1B.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(0))
     t0 = time.perf_counter()
     dec.prefill(ids)
@@ -308,6 +309,7 @@ def bench_decode_e2e(args, device, batch: int, prompt_len=512, new_tokens=256) -
     out = {"tok_per_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "batch": batch, "prompt": prompt_len,
            "steps_timed": steps, "prefill_s": prefill_s, "bytes_per_step": weight_bytes + kv_bytes,
            "hbm_gbs": (weight_bytes + kv_bytes) / (ms / steps * 1e-3) / 1e9}
+    dec.release()   # the graph holds captured NCCL work when tensor-parallel: free it before any process-group teardown
     del dec
     torch.cuda.empty_cache()
     return out
@@ -478,6 +480,14 @@ def main():
                 "note": "128 stacked copies (738 MB): long enough for launch, ramp and tail (~10 us) not to dominate"})
         if world > 1:
             also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
+            import torch.distributed as dist
+            for batch in (1, 32):   # tensor-parallel decode: every linear sharded over output features, 4 all-gathers per layer
+                try:
+                    r = bench_decode_e2e(args, device, batch, tp_group=dist.group.WORLD)
+                    r["note"] = "ONE model sharded over the GPUs (strong scaling); tok/s is the model's, not per GPU"
+                    also[f"decode_e2e_tinyllama_arch_tp{world}_b{batch}"] = r
+                except Exception as exc:  # report, never hide
+                    also[f"decode_e2e_tinyllama_arch_tp{world}_b{batch}"] = {"error": repr(exc)[:300]}
         if world == 1:
             for batch in (1, 32):
                 try:

@@ -12,6 +12,14 @@ residual adds, lm_head), as the reference does.  The decode step is launch-bound
 element-wise steps run as three fused kernels (ops.add_rmsnorm, ops.rope_kv_write, ops.silu_mul) and q/k/v and
 gate/up are stored as one quantised matrix each: 11 kernels per layer instead of ~48 (2.39 -> 0.85 ms per step
 on the TinyLlama-1.1B architecture).  Embedding lookup, the fp16 lm_head and argmax stay torch.
+
+Tensor parallelism (one process per GPU, `group` given): every decoder linear is sharded over its OUTPUT features, so
+no reduction is ever needed.  Rank r owns a block of query heads with their KV heads (a KV head is replicated when
+there are more ranks than KV heads), the matching rows of the fused qkv matrix, 1/W of the rows of o_proj and
+down_proj, and the gate and up rows of 1/W of the intermediate features (SiLU * up stays local).  Four all-gathers
+per layer rebuild the activations: attention output, o_proj output, activation, down_proj output.  Norms, residual
+stream, embedding and lm_head are replicated, so every rank holds the same logits and picks the same token.  At batch
+1 a gather costs more than the kernels it connects; the numbers are reported as they are.
 """
 
 from __future__ import annotations
@@ -22,6 +30,32 @@ import torch
 
 from . import ops
 from . import quantize as kq
+
+
+def tp_plan(shape: "LlamaShape", rank: int, world: int) -> dict:
+    """Which query heads, KV heads, hidden rows and intermediate features rank `rank` of `world` owns.
+
+    KV heads are split over the ranks when there are enough of them; otherwise the query heads of one KV head are
+    split over world / kv_heads ranks and that KV head is replicated.  All ranges are contiguous and in rank order, so
+    concatenating the ranks' outputs restores the natural feature order."""
+    from .parallel import row_bounds
+    h, hk = shape.heads, shape.kv_heads
+    g = h // hk
+    if hk % world == 0:
+        per = hk // world
+        kv = (rank * per, (rank + 1) * per)
+        q = (rank * per * g, (rank + 1) * per * g)
+    elif world % hk == 0 and g % (world // hk) == 0:
+        split = world // hk
+        gq = g // split
+        kv = (rank // split, rank // split + 1)
+        q = (kv[0] * g + (rank % split) * gq, kv[0] * g + (rank % split + 1) * gq)
+    else:
+        raise ValueError(f"cannot split heads={h}, kv_heads={hk} over {world} ranks without breaking a KV group")
+    return {"q_heads": q, "kv_heads": kv, "hidden_rows": row_bounds(shape.hidden, world)[rank],
+            "inter": row_bounds(shape.intermediate, world)[rank],
+            "attn_bounds": [(r * (q[1] - q[0]) * shape.head_dim, (r + 1) * (q[1] - q[0]) * shape.head_dim) for r in range(world)],
+            "hidden_bounds": row_bounds(shape.hidden, world), "inter_bounds": row_bounds(shape.intermediate, world)}
 
 
 @dataclass
@@ -54,25 +88,42 @@ class _Int4:
 class LlamaInt4Decoder:
     """fp16 activations, INT4 g128 decoder linears, fused attention, static KV cache."""
 
-    def __init__(self, shape: LlamaShape, weights: dict, device, batch: int, max_len: int, group: int = 128):
+    def __init__(self, shape: LlamaShape, weights: dict, device, batch: int, max_len: int, group: int = 128, tp_group=None):
         self.s, self.dev, self.b, self.max_len = shape, torch.device(device), batch, max_len
         s = shape
+        self.tp_group = tp_group
+        self.world = 1
+        if tp_group is not None:
+            import torch.distributed as dist
+            self.world, self.rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
+        self.plan = tp_plan(s, self.rank, self.world) if self.world > 1 else None
+        # local sizes (the whole model when not tensor-parallel)
+        self.h_loc = s.heads if self.plan is None else self.plan["q_heads"][1] - self.plan["q_heads"][0]
+        self.hk_loc = s.kv_heads if self.plan is None else self.plan["kv_heads"][1] - self.plan["kv_heads"][0]
+        self.inter_loc = s.intermediate if self.plan is None else self.plan["inter"][1] - self.plan["inter"][0]
         f16 = lambda t: t.to(self.dev, torch.float16).contiguous()
         self.embed = f16(weights["embed"])
         self.lm_head = f16(weights["lm_head"])
         self.final_norm = f16(weights["final_norm"])
         self.layers = []
+        d = s.head_dim
         for lw in weights["layers"]:
+            q, k, v, o, gate, up, down = (lw[n] for n in ("q", "k", "v", "o", "gate", "up", "down"))
+            if self.plan is not None:   # rows of this rank (output features); groups run along K: no requantisation issue
+                (q0, q1), (k0, k1) = self.plan["q_heads"], self.plan["kv_heads"]
+                (r0, r1), (i0, i1) = self.plan["hidden_rows"], self.plan["inter"]
+                q, k, v = q[q0 * d:q1 * d], k[k0 * d:k1 * d], v[k0 * d:k1 * d]
+                o, down, gate, up = o[r0:r1], down[r0:r1], gate[i0:i1], up[i0:i1]
             # q/k/v and gate/up share their input, so they are stored as ONE quantised matrix each (rows
             # concatenated: groups run along K, so this is bit-identical to quantising them separately)
             self.layers.append({
                 "in_norm": f16(lw["in_norm"]), "post_norm": f16(lw["post_norm"]),
-                "qkv": _Int4(torch.cat([f16(lw["q"]), f16(lw["k"]), f16(lw["v"])], 0), group),
-                "o": _Int4(f16(lw["o"]), group),
-                "gate_up": _Int4(torch.cat([f16(lw["gate"]), f16(lw["up"])], 0), group),
-                "down": _Int4(f16(lw["down"]), group),
+                "qkv": _Int4(torch.cat([f16(q), f16(k), f16(v)], 0), group),
+                "o": _Int4(f16(o), group),
+                "gate_up": _Int4(torch.cat([f16(gate), f16(up)], 0), group),
+                "down": _Int4(f16(down), group),
             })
-        self.k_cache = torch.zeros(s.layers, batch, s.kv_heads, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
+        self.k_cache = torch.zeros(s.layers, batch, self.hk_loc, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) / s.head_dim))
         ang = torch.outer(torch.arange(max_len, dtype=torch.float32), inv)
@@ -86,8 +137,15 @@ class LlamaInt4Decoder:
         self.graph = None
 
     # ------------------------------------------------------------------ construction helpers
+    def _gather(self, y_local: torch.Tensor, bounds_key: str) -> torch.Tensor:
+        """All-gather of the ranks' column blocks ([rows, n_local] -> [rows, n]); the identity without tensor parallelism."""
+        if self.plan is None:
+            return y_local
+        from .parallel import gather_columns
+        return gather_columns(y_local, self.plan[bounds_key], self.tp_group)
+
     @classmethod
-    def random_init(cls, shape: LlamaShape, device, batch: int, max_len: int, seed: int = 0, std: float = 0.02):
+    def random_init(cls, shape: LlamaShape, device, batch: int, max_len: int, seed: int = 0, std: float = 0.02, tp_group=None):
         """Weights ~ N(0, std), norms = 1: the initialisation of a fresh Hugging Face Llama."""
         g = torch.Generator().manual_seed(seed)
         s = shape
@@ -98,10 +156,10 @@ class LlamaInt4Decoder:
                    "up": rn(s.intermediate, s.hidden), "down": rn(s.hidden, s.intermediate)} for _ in range(s.layers)]
         weights = {"embed": rn(s.vocab, s.hidden), "lm_head": rn(s.vocab, s.hidden), "final_norm": torch.ones(s.hidden),
                    "layers": layers}
-        return cls(shape, weights, device, batch, max_len)
+        return cls(shape, weights, device, batch, max_len, tp_group=tp_group)
 
     @classmethod
-    def from_hf(cls, model, device, batch: int, max_len: int):
+    def from_hf(cls, model, device, batch: int, max_len: int, tp_group=None):
         """From a transformers LlamaForCausalLM (any dtype; weights are rounded to fp16, then quantised)."""
         c = model.config
         theta = getattr(c, "rope_theta", None) or (getattr(c, "rope_parameters", None) or {}).get("rope_theta", 10000.0)
@@ -119,7 +177,7 @@ class LlamaInt4Decoder:
                            "down": sd[p + "mlp.down_proj.weight"]})
         weights = {"embed": sd["model.embed_tokens.weight"], "lm_head": sd["lm_head.weight"],
                    "final_norm": sd["model.norm.weight"], "layers": layers}
-        return cls(shape, weights, device, batch, max_len)
+        return cls(shape, weights, device, batch, max_len, tp_group=tp_group)
 
     # ------------------------------------------------------------------ building blocks (torch)
     def _rms(self, x, w):
@@ -136,8 +194,12 @@ class LlamaInt4Decoder:
     def _mlp(self, L, x):
         h = self._rms(x, L["post_norm"])
         gu = L["gate_up"](h)
-        inter = self.s.intermediate
-        return x + L["down"](torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:])
+        inter = self.inter_loc
+        act = torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:]
+        lead = act.shape[:-1]
+        act = self._gather(act.reshape(-1, inter), "inter_bounds").reshape(*lead, self.s.intermediate)
+        down = L["down"](act)
+        return x + self._gather(down.reshape(-1, down.shape[-1]), "hidden_bounds").reshape(*lead, self.s.hidden)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -151,15 +213,17 @@ class LlamaInt4Decoder:
         for li, L in enumerate(self.layers):
             h = self._rms(x, L["in_norm"])
             qkv = L["qkv"](h)
-            nq, nkv = s.heads * s.head_dim, s.kv_heads * s.head_dim
-            q = qkv[..., :nq].reshape(b, t, s.heads, s.head_dim).transpose(1, 2)
-            k = qkv[..., nq:nq + nkv].reshape(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
-            v = qkv[..., nq + nkv:].reshape(b, t, s.kv_heads, s.head_dim).transpose(1, 2)
+            nq, nkv = self.h_loc * s.head_dim, self.hk_loc * s.head_dim
+            q = qkv[..., :nq].reshape(b, t, self.h_loc, s.head_dim).transpose(1, 2)
+            k = qkv[..., nq:nq + nkv].reshape(b, t, self.hk_loc, s.head_dim).transpose(1, 2)
+            v = qkv[..., nq + nkv:].reshape(b, t, self.hk_loc, s.head_dim).transpose(1, 2)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
             self.k_cache[li, :, :, :t] = k
             self.v_cache[li, :, :, :t] = v
             a = ops.flash_attn_kv_view(q.contiguous(), self.k_cache[li, :, :, :t], self.v_cache[li, :, :, :t], causal=True)
-            x = x + L["o"](a.transpose(1, 2).reshape(b, t, s.heads * s.head_dim))
+            a = self._gather(a.transpose(1, 2).reshape(b * t, nq), "attn_bounds")
+            o = self._gather(L["o"](a), "hidden_bounds")
+            x = x + o.reshape(b, t, s.hidden)
             x = self._mlp(L, x)
         logits = self._rms(x, self.final_norm) @ self.lm_head.T
         self.tok.copy_(logits[:, -1].float().argmax(-1))
@@ -178,11 +242,13 @@ class LlamaInt4Decoder:
         for li, L in enumerate(self.layers):
             h, x = ops.add_rmsnorm(x, L["in_norm"], s.rms_eps, res)
             qkv = L["qkv"](h)
-            q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], s.heads)
+            q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
             a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len)
-            o = L["o"](a.view(b, s.heads * s.head_dim))
+            a = self._gather(a.view(b, self.h_loc * s.head_dim), "attn_bounds")
+            o = self._gather(L["o"](a), "hidden_bounds")
             h, x = ops.add_rmsnorm(x, L["post_norm"], s.rms_eps, o)
-            res = L["down"](ops.silu_mul(L["gate_up"](h)))
+            act = self._gather(ops.silu_mul(L["gate_up"](h)), "inter_bounds")
+            res = self._gather(L["down"](act), "hidden_bounds")
         h, x = ops.add_rmsnorm(x, self.final_norm, s.rms_eps, res)
         logits = h @ self.lm_head.T
         self.step_logits.copy_(logits)
@@ -204,6 +270,14 @@ class LlamaInt4Decoder:
             self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.kv_len.copy_(saved[2])
             side.synchronize()
         return self
+
+    def release(self):
+        """Drops the captured graph.  With tensor parallelism this must happen before the process group is destroyed:
+        a live CUDA graph that holds captured NCCL all-gathers makes destroy_process_group() wait forever."""
+        self.graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize(self.dev)
 
     @torch.no_grad()
     def decode(self, steps: int, keep_logits: bool = False):

@@ -73,3 +73,25 @@ def test_row_bounds_and_head_shards():
         assert all(t[0].shape[1] % t[1].shape[1] == 0 for t in heads)
     with pytest.raises(ValueError, match="KV group"):
         kp.shard_attention_heads(q, k, k, 0, 3)
+
+
+def test_tensor_parallel_plan_partitions_heads_rows_and_features():
+    """Ownership ranges of the tensor-parallel decoder: contiguous, in rank order, covering everything once; a KV head
+    is replicated only when there are more ranks than KV heads."""
+    from kernelforge.llama_decode import TINYLLAMA_1B, LlamaShape, tp_plan
+    for shape in (TINYLLAMA_1B, LlamaShape(hidden=1536, heads=12, kv_heads=2, head_dim=128, intermediate=8960)):
+        for world in (1, 2, 4, 8):
+            if shape.heads % world or (shape.kv_heads % world and world % shape.kv_heads):
+                continue
+            plans = [tp_plan(shape, r, world) for r in range(world)]
+            for key, total in (("q_heads", shape.heads), ("hidden_rows", shape.hidden), ("inter", shape.intermediate)):
+                assert plans[0][key][0] == 0 and plans[-1][key][1] == total
+                assert all(plans[r][key][1] == plans[r + 1][key][0] for r in range(world - 1))
+            g = shape.heads // shape.kv_heads
+            for p in plans:   # every query head of a rank reads one of the rank's KV heads
+                assert p["kv_heads"][0] * g <= p["q_heads"][0] and p["q_heads"][1] <= p["kv_heads"][1] * g
+            width = (plans[0]["q_heads"][1] - plans[0]["q_heads"][0]) * shape.head_dim
+            assert plans[0]["attn_bounds"] == [(r * width, (r + 1) * width) for r in range(world)]
+    import pytest
+    with pytest.raises(ValueError, match="cannot split"):
+        tp_plan(LlamaShape(heads=12, kv_heads=4), 0, 8)

@@ -53,3 +53,52 @@ def _worker(rank, world, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_sharded_linear_two_gpus():
     mp.spawn(_worker, args=(2, 29600 + os.getpid() % 1000), nprocs=2, join=True)
+
+
+def _tp_decode_worker(rank, world, port):
+    for p in (str(ROOT), str(ROOT / "kernel-forge_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))   # a failing rank must not keep the other waiting 10 minutes
+    tp = None
+    try:
+        from test_llama_decode_gpu import build
+        from kernelforge.llama_decode import LlamaInt4Decoder
+        base, ref = build()                      # same seed on every rank: identical weights
+        dev = torch.device("cuda", rank)
+        batch, prompt_len, steps = 2, 24, 10
+        ids = torch.randint(0, 320, (batch, prompt_len), generator=torch.Generator().manual_seed(3))
+        tp = LlamaInt4Decoder.from_hf(base, dev, batch, max_len=64, tp_group=dist.group.WORLD)
+        assert tp.h_loc == 2 and tp.hk_loc == 1 and tp.inter_loc == 256
+        pre = tp.prefill(ids).float().cpu()
+        toks, logs = tp.decode(steps, keep_logits=True)      # CUDA graph with the four all-gathers per layer captured
+        torch.cuda.synchronize()
+        full = torch.cat([ids, toks.cpu()], dim=1)
+        with torch.no_grad():
+            want = ref(full).logits
+        scale = want.abs().max().item()
+        assert (pre - want[:, :prompt_len]).abs().max().item() <= 2e-2 * scale
+        assert (logs.float().cpu() - want[:, prompt_len:]).abs().max().item() <= 2e-2 * scale
+        # every rank holds the same logits and therefore the same tokens
+        mine = toks.to(dev).contiguous()
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(both[0], t) for t in both)
+        # and they agree with the single-GPU decoder on the same weights (different kernel shapes: close, not bit-equal)
+        single = LlamaInt4Decoder.from_hf(base, dev, batch, max_len=64)
+        pre1 = single.prefill(ids).float().cpu()
+        assert (pre1 - pre).abs().max().item() <= 5e-3 * scale
+    finally:
+        if tp is not None:
+            tp.release()   # a live graph with captured all-gathers would make the teardown below wait forever
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_decode_two_gpus():
+    pytest.importorskip("transformers")
+    mp.spawn(_tp_decode_worker, args=(2, 29700 + os.getpid() % 1000), nprocs=2, join=True)
