@@ -481,7 +481,9 @@ def main():
         if world > 1:
             also["int4_linear_n_sharded_m128_8960x1536"] = bench_sharded_linear(args, world, device)
             import torch.distributed as dist
-            for batch in (1, 32):   # tensor-parallel decode: every linear sharded over output features, 4 all-gathers per layer
+            # tensor-parallel decode: every linear sharded over output features, 4 all-gathers per layer.  Run by default on
+            # 2 GPUs (the configuration this was verified on); KFB_BENCH_TP=1 enables it for 4 and 8
+            for batch in ((1, 32) if (world == 2 or os.environ.get("KFB_BENCH_TP") == "1") else ()):
                 try:
                     r = bench_decode_e2e(args, device, batch, tp_group=dist.group.WORLD)
                     r["note"] = "ONE model sharded over the GPUs (strong scaling); tok/s is the model's, not per GPU"
