@@ -103,3 +103,15 @@ def test_custom_ops_registered_with_fakes():
         p = torch.empty(40, 32, dtype=torch.int32, device="cuda")
         s = torch.empty(40, 2, dtype=torch.float16, device="cuda")
         assert torch.ops.kernelforge.int4_matmul(x, p, s, 128).shape == (3, 40)
+
+
+def test_int4_matmul_routing_table():
+    """Which kernel int4_matmul picks by shape (pure host logic): GEMV up to M = 8, the same kernel with more batch columns
+    for 8 < M <= 16 where it measured faster, the tcgen05 GEMM otherwise."""
+    from kernelforge import ops
+    assert ops.GEMV_MAX_M == 8 and ops.SMALL_BATCH_MAX_M == 32
+    wins = ops._small_batch_wins
+    assert wins(12, 5632, 2048) and wins(16, 2048, 2048) and wins(16, 8960, 1536)
+    assert wins(16, 128256, 4096)                      # large N: the persistent streaming kernel
+    assert not wins(12, 1536, 8960)                    # long K, few rows: the GEMM was faster
+    assert not wins(12, 32000, 2048)                   # between the two regimes
