@@ -491,7 +491,7 @@ def main():
                 except Exception as exc:  # report, never hide
                     also[f"decode_e2e_tinyllama_arch_tp{world}_b{batch}"] = {"error": repr(exc)[:300]}
         if world == 1:
-            for batch in (1, 32):
+            for batch in (1, 8, 32):
                 try:
                     r = bench_decode_e2e(args, device, batch)
                     r["frac_of_hbm"] = r["hbm_gbs"] / peaks["hbm_gbs"]
