@@ -28,7 +28,10 @@
 //  6. the memory system: with all of that the SMs wait for data (~5 us of queueing at 8-12 KB in flight per warp);
 //     two stages per warp instead of three are faster (less queueing, more L1 left for the activations).  What is
 //     left at N = 180224 is ~10 us of launch, class sums, ramp and tail per launch (72 % of the copy peak; 88 % on
-//     763 MB).
+//     763 MB);
+//  7. the activations: read through L1 every round they make the kernel slower the larger M is (the ring leaves L1
+//     little room) -> for M >= 2 the persistent kernel copies x to shared memory once, in fragment order, and M = 8
+//     then runs at the speed of M = 1 (87 % of the copy peak on 763 MB).
 //
 // Shared-memory stage of a warp: R = 16 or 32 rows x 128 bytes (2 rounds of G = 128, 4 of G = 64), written by the TMA
 // with the 128-byte swizzle (16-byte piece j of row r sits at piece j ^ (r & 7)).  Fragment row slot g of a tile
@@ -130,6 +133,10 @@ struct LaneMap {
   int g, t, pg;         // lane = 4 g + t; fragment row slot g holds matrix rows pg + 8 k of the warp's rows
   uint32_t off[C];      // position of this lane's words of round u inside a stage (row pg, swizzled 16-byte piece)
   const __half* xrow[NB];   // column 8 nb + g of the B operand (a valid row when >= M), at this lane's k offset
+  // optional copy of x in shared memory in fragment order (NB = 1): unit ((round * W + j) * Mp + m) * 4 + t holds the 16
+  // bytes lane (m, t) needs for word j of that round, so the 32 lanes of a load read consecutive units
+  const uint4* xs_lane = nullptr;
+  int xs_shift = 0;         // log2(4 * Mp): units per (round, word)
   __device__ __forceinline__ LaneMap(int lane, const __half* x, int M, int K) {
     g = lane >> 2;
     t = lane & 3;
@@ -210,7 +217,7 @@ __device__ __forceinline__ void load_scales(const __half* const (&srow)[2 * T], 
 
 // One chunk (C rounds) of T row tiles out of the stage at shared address `st` (already complete).  `refill` runs once
 // every shared load of the stage has delivered, i.e. as early as the stage may be handed back to the TMA.
-template <int G, int T, int RG, int NB, class Refill>
+template <int G, int T, int RG, int NB, bool XS = false, class Refill>
 __device__ __forceinline__ void chunk_compute(const LaneMap<G, NB>& lm, uint32_t st, const float* sx, int r0, int nr,
                                               const uint32_t (&sc)[2 * T][LaneMap<G>::C / 2], const uint4& unpack,
                                               float (&acc)[T][NB][4], Refill&& refill) {
@@ -252,7 +259,10 @@ __device__ __forceinline__ void chunk_compute(const LaneMap<G, NB>& lm, uint32_t
 #pragma unroll
       for (int v = 0; v < RG; ++v)
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) xv[v][nb] = *reinterpret_cast<const uint4*>(lm.xrow[nb] + xoff[v] + j * 8);
+        for (int nb = 0; nb < NB; ++nb) {
+          if constexpr (XS) xv[v][nb] = lm.xs_lane[(size_t)((xoff[v] / G) * W + j) << lm.xs_shift];
+          else xv[v][nb] = *reinterpret_cast<const uint4*>(lm.xrow[nb] + xoff[v] + j * 8);
+        }
 #pragma unroll
       for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -428,15 +438,18 @@ struct StreamSmem {   // offsets from the 1024-byte aligned base
   static constexpr size_t counter = abort_word + 4;             // next unit of the CTA
   static constexpr size_t queue = abort_word + 16;              // int[NW][4]: units taken by a warp's producer side
   static constexpr size_t sx = queue + (size_t)NW * 16;
-  static size_t bytes(int rounds, int NB) { return 1024 + sx + (size_t)rounds * 8 * NB * sizeof(float); }
+  static size_t bytes(int rounds, int NB, size_t xs_bytes = 0) { return 1024 + sx + (size_t)rounds * 8 * NB * sizeof(float) + xs_bytes; }
 };
 
-template <int G, int RG, int NW, int MINB, int NS, int NB>
+// XS: the activations are copied to shared memory in fragment order once per CTA (Mp = M rounded up to a power of two
+// columns); without it every round reads them through L1, which makes the kernel slower the larger M is.
+template <int G, int RG, int NW, int MINB, int NS, int NB, bool XS = false>
 __global__ void __launch_bounds__(NW * 32, MINB)
 int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant__ CUtensorMap wmap32,
                             const __grid_constant__ CUtensorMap wmap16, const __half* __restrict__ scales,
                             __half* __restrict__ y, int M, int N, int K, int vec_scales, unsigned int* status,
-                            const uint4 unpack, unsigned long long* trace) {
+                            const uint4 unpack, unsigned long long* trace, int mp_log2) {
+  static_assert(!XS || NB == 1, "the shared-memory copy of x is laid out for one column block");
   using L = StreamSmem<NW, NS>;
   constexpr int C = LaneMap<G>::C, S = L::S;
   constexpr uint32_t kStage = L::kStage;
@@ -511,11 +524,27 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   pdl_launch_dependents();
   pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
 
-  class_sums<G, NB>(x, M, K, sx);
+  uint4* xs = reinterpret_cast<uint4*>(sx + (size_t)rounds * 8 * NB);   // 16-byte aligned: rounds * 32 NB bytes after sx
+  if constexpr (XS) {
+    constexpr int W = LaneMap<G>::W;
+    const int units = (rounds * W) << (2 + mp_log2);
+    for (int u = threadIdx.x; u < units; u += blockDim.x) {
+      const int t4 = u & 3, m = (u >> 2) & ((1 << mp_log2) - 1), jj = u >> (2 + mp_log2);
+      const int rd = jj / W, j = jj - rd * W;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)rd * G + t4 * (G / 4) + j * 8);
+      xs[u] = v;
+    }
+  }
+  class_sums<G, NB>(x, M, K, sx);   // ends with the CTA barrier, which also publishes xs
   if (tr) tr[1] = globaltimer_ns();
 
   const AbortCtx ctx{abort_word, status};
-  const LaneMap<G, NB> lm(lane, x, M, K);
+  LaneMap<G, NB> lm(lane, x, M, K);
+  if constexpr (XS) {
+    lm.xs_shift = 2 + mp_log2;
+    lm.xs_lane = xs + ((lm.g & ((1 << mp_log2) - 1)) << 2) + lm.t;
+  }
   int q = 0;   // copies consumed
   bool ok = true;
   auto run_unit = [&](auto tag, int row0) {
@@ -533,7 +562,7 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
       uint32_t sc[2 * T][C / 2];
       load_scales<G, T>(srow, r0, nr, vec_scales, sc);   // before the wait: overlaps it
       if (!__all_sync(0xffffffffu, wait_stage(&my_bars[q % S], (uint32_t)(q / S) & 1u, ctx))) { ok = false; return; }
-      chunk_compute<G, T, RG, NB>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
+      chunk_compute<G, T, RG, NB, XS>(lm, my_ring + (uint32_t)(q % S) * kStage, sx, r0, nr, sc, unpack, acc, [&] {
         __syncwarp();
         issue_next();
       });
@@ -619,12 +648,13 @@ int launch_split(const Call& c, const CUtensorMap& wmap16, int grid) {
                    (const __half*)c.x, wmap16, (const __half*)c.scales, (__half*)c.y, c.M, c.N, c.K, c.vec, c.status, c.unpack);
 }
 
-template <int G, int RG, int NW, int NS, int NB>
-int launch_stream(const Call& c, const CUtensorMap& wmap32, const CUtensorMap& wmap16) {
-  if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB>>()) return rc;
-  return launch_ex(int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB>, sm_count(), NW * 32, StreamSmem<NW, NS>::bytes(c.K / G, NB),
-                   c.stream, c.pdl, (const __half*)c.x, wmap32, wmap16, (const __half*)c.scales, (__half*)c.y, c.M, c.N, c.K, c.vec,
-                   c.status, c.unpack, g_trace);
+template <int G, int RG, int NW, int NS, int NB, bool XS = false>
+int launch_stream(const Call& c, const CUtensorMap& wmap32, const CUtensorMap& wmap16, int mp_log2 = 0) {
+  if (int rc = opt_in_shared_memory<int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB, XS>>()) return rc;
+  const size_t xs_bytes = XS ? ((size_t)c.K * 2) << mp_log2 : 0;
+  return launch_ex(int4_gemv_mma_stream_kernel<G, RG, NW, 1, NS, NB, XS>, sm_count(), NW * 32,
+                   StreamSmem<NW, NS>::bytes(c.K / G, NB, xs_bytes), c.stream, c.pdl, (const __half*)c.x, wmap32, wmap16,
+                   (const __half*)c.scales, (__half*)c.y, c.M, c.N, c.K, c.vec, c.status, c.unpack, g_trace, mp_log2);
 }
 
 template <int G, int NB>
@@ -646,7 +676,15 @@ int launch_nb(const Call& c, const void* packed) {
     // either way and the shared memory not taken by the ring is L1 for the activations (N = 180224, K = 2048:
     // 41.7 vs 45.5 us at M = 1, 48.6 vs 54.4 us at M = 8).  Registers: 512 threads leave 128 per thread, enough
     // for two rounds at a time with one column block, one round with two; four column blocks run with 8 warps.
-    if constexpr (NB == 1) return launch_stream<G, 2, 16, 2, 1>(c, wmap32, wmap16);
+    if constexpr (NB == 1) {
+      // M >= 2: activations from a fragment-ordered shared-memory copy when it fits next to the ring (64 KB).  Through
+      // L1 the kernel slows down with M (N = 720896, K = 2048: 133 us at M = 1, 151 us at M = 8); with the copy M = 8
+      // takes 135 us.
+      const int mp_log2 = c.M <= 1 ? 0 : c.M <= 2 ? 1 : c.M <= 4 ? 2 : 3;
+      if (c.M >= 2 && (((size_t)K * 2) << mp_log2) <= 64 * 1024)
+        return launch_stream<G, 2, 16, 2, 1, true>(c, wmap32, wmap16, mp_log2);
+      return launch_stream<G, 2, 16, 2, 1>(c, wmap32, wmap16);
+    }
     else if constexpr (NB == 2) return launch_stream<G, 1, 16, 2, 2>(c, wmap32, wmap16);
     else return launch_stream<G, 1, 8, 3, 4>(c, wmap32, wmap16);
   }
