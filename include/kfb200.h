@@ -17,7 +17,9 @@
  *   - data pointers must be 16-byte aligned (the reference demands the same,
  *     csrc/attention/attn_v4.cu:26-31, csrc/gemm/dequant_gemv.cu:17-18);
  *   - thread-safe; the only shared state is a mutex-guarded one-time set-up of kernel
- *     attributes and a small cache of TMA tensor maps.
+ *     attributes; every host thread keeps its own small cache of encoded TMA tensor maps
+ *     (keyed by base address, extents, strides and box), so a loop over the same tensors
+ *     encodes each map once.
  */
 #ifndef KFB200_H
 #define KFB200_H
@@ -50,6 +52,18 @@ const char* kfb_last_error(void);
  * a non-zero code here and lets the kernel finish.  0 = no wait has ever expired.  (The
  * reference has no counterpart; its errors surface as CUDA errors, csrc/common/check.cuh:11-24.) */
 int kfb_device_status(unsigned int* out);
+/* Clears the status word of the current device (a 4-byte memset enqueued on `stream`).  The word is sticky: once a
+ * wait has expired, every later attention / GEMM / GEMV launch on that device returns at once WITHOUT writing its
+ * output, so a host that reads a non-zero status must discard the results enqueued since, find the cause, and call
+ * this before it launches again.  Codes: 0x1xx prefill attention, 0x2xx decode attention, 0x3xx-0x5xx the INT4
+ * kernels, 0x601 the self-test below, 0x701 kfb_rope_kv_write given a position outside the cache. */
+int kfb_device_status_reset(void* stream);
+/* Self-test of the bounded-wait path: launches one warp that waits, through the same helper every kernel of the
+ * library uses, on an mbarrier that nothing arrives on, with a limit of timeout_ns (1 us .. 100 ms).  The wait runs
+ * out, the kernel writes 2 to *outcome_dev (1 would mean the wait completed) and code 0x601 to the status word, and
+ * returns normally; nothing faults or traps.  Follow it with kfb_device_status_reset.  No counterpart in the
+ * reference (csrc/common/check.cuh:11-24 turns CUDA errors into exceptions; it has no in-kernel waits). */
+int kfb_selftest_wait_expiry(unsigned long long timeout_ns, unsigned int* outcome_dev, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * INT4 weight format (kernelforge/quantize.py).  packed: int32 [N, K/8], nibble position i
@@ -87,7 +101,8 @@ int kfb_dequantize(const void* packed, const void* scales, int N, int K, int gro
  * flags: bit 0 = launch with programmatic dependent launch (the weight prefetch of this
  * call may overlap the tail of the previous kernel on the stream; x is read and y written
  * only after the previous kernel has completed).
- *        bit 1 = use the CUDA-core kernel. */
+ *        bit 1 = use the CUDA-core kernel;  bit 2 = use the mma.sync kernel (bits 1 and 2 exclude each other;
+ *        with neither, the faster one for the shape is chosen). */
 int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y,
                   int M, int N, int K, int group, int flags, void* stream);
 
@@ -164,7 +179,9 @@ int kfb_add_rmsnorm(const void* x, const void* residual, const void* weight, voi
 /* Rotary embedding + KV-cache write of one decode position.  qkv: [B, (H + 2*Hk) * D] (q heads, then k
  * heads, then v heads, as produced by one fused q/k/v linear); cos_table, sin_table: fp32 [Lmax, D]
  * (rotate-half convention); pos_dev: device int64, the position being written.  q_out: [B, H, D];
- * k_cache, v_cache: [B, Hk, Lmax, D], row `pos` is written. */
+ * k_cache, v_cache: [B, Hk, Lmax, D], row `pos` is written.  A position outside [0, Lmax) writes nothing and
+ * records code 0x701 in the device status word (the kernel reads the position on the device, e.g. in a graph replay,
+ * so the host cannot check it at launch time). */
 int kfb_rope_kv_write(const void* qkv, const void* cos_table, const void* sin_table, const void* pos_dev,
                       void* q_out, void* k_cache, void* v_cache, int B, int H, int Hk, int D, int Lmax,
                       void* stream);

@@ -15,8 +15,6 @@
 //     partial (O, m, l) per split written to the caller's workspace and combined in split order by
 //     a second small kernel => deterministic.  With one split the result is written directly.
 #include "attn.cuh"
-
-#include <cstdlib>
 #include "sm100.cuh"
 
 namespace kfb {
@@ -312,7 +310,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       l_all = fmaf(f, scratch[w * kPerWarp + kRows * D + kRows + r], l_all);
     }
     if (direct) {
-      o[((size_t)b * H + h0 + r) * D + d] = pack1<kBf16>(acc / l_all);
+      o[((size_t)b * H + h0 + r) * D + d] = pack1<kBf16>(l_all > 0.f ? acc / l_all : 0.f);  // no valid key: zeros
     } else {
       out_partial[r * D + d] = acc;
       if (d == 0) {
@@ -344,7 +342,7 @@ attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict
     acc = fmaf(f, ps[r * D + d], acc);
     l_all = fmaf(f, ps[kRows * D + kRows + r], l_all);
   }
-  o[((size_t)b * H + h) * D + d] = pack1<kBf16>(acc / l_all);
+  o[((size_t)b * H + h) * D + d] = pack1<kBf16>(l_all > 0.f ? acc / l_all : 0.f);  // no valid key: zeros
 }
 
 struct SplitPlan {

@@ -80,13 +80,21 @@ add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ res,
   }
 }
 
+constexpr unsigned int kStatusRopePosition = 0x701;  // rope_kv_write: position outside [0, Lmax)
+
 // grid (H + 2 Hk, B), D / 2 threads.  qkv: [B, (H + 2 Hk) * D] = q heads, k heads, v heads.
 __global__ void rope_kv_write_kernel(const __half* __restrict__ qkv, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, const long long* __restrict__ pos_ptr,
                                      __half* __restrict__ q_out, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
-                                     int H, int Hk, int D, int Lmax) {
+                                     int H, int Hk, int D, int Lmax, unsigned int* status) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x, half = D / 2;
   const long long pos = pos_ptr[0];
+  // The position comes from device memory (a graph replay advances it), so it is checked here: a position outside
+  // the cache / the rotary tables writes nothing and reads nothing, and leaves a code in the device status word.
+  if (pos < 0 || pos >= Lmax) {
+    if (threadIdx.x == 0 && head == 0 && b == 0) atomicCAS(status, 0u, kStatusRopePosition);
+    return;
+  }
   const __half* src = qkv + ((size_t)b * (H + 2 * Hk) + head) * D;
   if (head < H + Hk) {
     const float lo = __half2float(src[d]), hi = __half2float(src[d + half]);
@@ -148,9 +156,11 @@ extern "C" int kfb_rope_kv_write(const void* qkv, const void* cos_table, const v
   if (B < 1 || H < 1 || Hk < 1 || Lmax < 1 || (D != 64 && D != 128) || B > 65535)
     return fail(KFB_ERR_INVALID, "rope_kv_write: bad shape B=%d H=%d Hk=%d D=%d Lmax=%d", B, H, Hk, D, Lmax);
   if (!qkv || !cos_table || !sin_table || !pos_dev || !q_out || !k_cache || !v_cache) return fail(KFB_ERR_INVALID, "null pointer");
+  unsigned int* status = device_status_word();
+  if (!status) return fail(KFB_ERR_CUDA, "cannot resolve the device status word");
   fused::rope_kv_write_kernel<<<dim3(H + 2 * Hk, B), D / 2, 0, (cudaStream_t)stream>>>(
       (const __half*)qkv, (const float*)cos_table, (const float*)sin_table, (const long long*)pos_dev, (__half*)q_out,
-      (__half*)k_cache, (__half*)v_cache, H, Hk, D, Lmax);
+      (__half*)k_cache, (__half*)v_cache, H, Hk, D, Lmax, status);
   KFB_LAUNCH_CHECK("rope_kv_write_kernel");
   return KFB_OK;
 }

@@ -126,8 +126,12 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool dead_on_arrival = *abort_word != 0;
-  // optional timeline of CTA (0,0,0) for tuning: 8 clock stamps per K block
+  // optional timeline of CTA (0,0,0) for tuning (builds with -DKFB_TRACE only): 8 clock stamps per K block
+#ifdef KFB_TRACE
   const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#else
+  constexpr bool tracing = false;
+#endif
   auto stamp = [&](int i, int k) {
     if (tracing && i < 64) trace[i * 8 + k] = clock64();
   };
@@ -306,7 +310,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
+#ifdef KFB_TRACE
 unsigned long long* g_trace = nullptr;  // tuning aid, set through kfb_debug_set_gemm_trace
+#else
+constexpr unsigned long long* g_trace = nullptr;
+#endif
 
 struct Plan {
   int mt, m_tiles, n_tiles, splits, kblocks_per_split;
@@ -436,7 +444,10 @@ extern "C" int kfb_int4_gemm_allgather(const void* x, const void* packed, const 
   return gemm_common(x, packed, scales, out, M, N_local, K, group, ws, ws_bytes, stream);
 }
 
-// Tuning aid (not part of the public header): device buffer of 64 x 8 clock stamps written by CTA (0,0,0).
+#ifdef KFB_TRACE
+// Tuning aid of -DKFB_TRACE builds (not part of the public header): device buffer of 64 x 8 clock stamps written by
+// CTA (0,0,0).
 extern "C" void kfb_debug_set_gemm_trace(void* device_buffer) {
   kfb::gemm::g_trace = static_cast<unsigned long long*>(device_buffer);
 }
+#endif

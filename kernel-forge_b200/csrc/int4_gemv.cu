@@ -327,7 +327,7 @@ int gemv_entry(const char* what, int max_m, const void* x, const void* packed, c
   if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
   if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
   if (!aligned16(x) || !aligned16(packed)) return fail(KFB_ERR_ALIGNMENT, "x and packed must be 16-byte aligned");
-  if (flags & ~3) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
+  if ((flags & ~7) || (flags & 6) == 6) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
   cudaStream_t s = (cudaStream_t)stream;
   // Two kernels: the mma.sync formulation (int4_gemv_mma.cuh) and the CUDA-core one of this file, which is
   // issue-bound on B200 and whose time grows with M.  Measured under a CUDA graph on L2-cold weights (us, CUDA core /
@@ -335,11 +335,10 @@ int gemv_entry(const char* what, int max_m, const void* x, const void* packed, c
   // 20.2/7.0;   11264x2048  6.3/9.0  8.9/9.7  16.2/10.5  25.7/12.3;   2048x5632  6.1/5.3  8.8/5.9  14.2/6.7  32.0/9.0;
   // 32000x2048  13.3/12.6  18.2/13.7  36.4/15.2  68.4/18.3;   128256x4096  76/62  132/64  273/67  521/80.  So: M = 1 takes
   // the CUDA-core kernel unless N is large enough for the persistent streaming kernel, M >= 2 takes mma.  Flag bit 1
-  // or KFB_GEMV_IMPL=cuda_core forces the CUDA-core kernel (M <= 8), KFB_GEMV_IMPL=mma the other; K too long for the
-  // class sums to fit in shared memory also goes to the CUDA-core kernel.
-  static const int forced = [] { const char* e = getenv("KFB_GEMV_IMPL"); return !e ? 0 : e[0] == 'c' ? 1 : e[0] == 'm' ? 2 : 0; }();
+  // forces the CUDA-core kernel (M <= 8), flag bit 2 the mma one; K too long for the class sums to fit in shared
+  // memory also goes to the CUDA-core kernel.
   const bool fits = group == 128 ? gemv_mma::fits<128>(M, K) : gemv_mma::fits<64>(M, K);
-  const bool prefer_mma = forced == 2 || (forced == 0 && !(flags & 2) && (M >= 2 || gemv_mma::uses_stream_kernel(N)));
+  const bool prefer_mma = (flags & 4) || (!(flags & 2) && (M >= 2 || gemv_mma::uses_stream_kernel(N)));
   if (fits && (M > 8 || prefer_mma))
     return group == 128 ? gemv_mma::launch<128>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s)
                         : gemv_mma::launch<64>(x, packed, scales, y, M, N, K, (flags & 1) != 0, s);
@@ -360,7 +359,10 @@ extern "C" int kfb_int4_small_batch(const void* x, const void* packed, const voi
   return gemv_entry("int4_small_batch", gemv_mma::kMaxM, x, packed, scales, y, M, N, K, group, flags, stream);
 }
 
-// Tuning aid (not part of the public header): device buffer of 4 words per warp of the streaming kernel (3 timestamps in ns, SM id).
+#ifdef KFB_TRACE
+// Tuning aid of -DKFB_TRACE builds (not part of the public header): device buffer of 4 words per warp of the
+// streaming kernel (3 timestamps in ns, SM id).
 extern "C" void kfb_debug_set_gemv_trace(void* device_buffer) {
   kfb::gemv_mma::g_trace = static_cast<unsigned long long*>(device_buffer);
 }
+#endif

@@ -463,7 +463,11 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* my_queue = reinterpret_cast<volatile int*>(smem + L::queue) + warp * 4;
   // optional timeline for tuning: per warp (start, class sums done, end) in ns and the SM id
+#ifdef KFB_TRACE
   unsigned long long* tr = trace != nullptr && lane == 0 ? trace + (size_t)(blockIdx.x * NW + warp) * 4 : nullptr;
+#else
+  constexpr unsigned long long* tr = nullptr;
+#endif
   if (tr) {
     uint32_t smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -600,7 +604,11 @@ int opt_in_shared_memory() {   // once per kernel instantiation and device: more
   return KFB_OK;
 }
 
+#ifdef KFB_TRACE
 inline unsigned long long* g_trace = nullptr;   // tuning aid, set through kfb_debug_set_gemv_trace
+#else
+constexpr unsigned long long* g_trace = nullptr;
+#endif
 
 template <class... KArgs, class... Args>
 int launch_ex(void (*kernel)(KArgs...), int grid, int threads, size_t smem, cudaStream_t stream, bool pdl, Args... args) {

@@ -2,7 +2,8 @@
 // mbarrier, TMA tensor copies (cp.async.bulk.tensor), tcgen05 MMA / TMEM, and the shared-memory
 // and instruction descriptors of tcgen05.mma.  Device code only, no library dependencies.
 //
-// Every wait in this file is BOUNDED: a wait that has not completed after kWaitTimeoutNs sets an
+// Every wait in this file is BOUNDED: a wait that has not completed after AbortCtx::timeout_ns (2 s unless the caller
+// says otherwise) sets an
 // abort word in shared memory, records a code in the global status word and returns false; the
 // callers then fall through to their normal teardown (TMEM is freed, no trap, no endless spin).
 #pragma once
@@ -17,12 +18,13 @@ namespace sm100 {
 // Where a kernel reports an expired wait: `cta_word` lives in shared memory and makes the other
 // threads of the CTA stop waiting too; `device_word` is the library's per-device status word in
 // global memory (0 = fine, otherwise the code of the first wait that expired).
+constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+
 struct AbortCtx {
   volatile uint32_t* cta_word;
   unsigned int* device_word;
+  unsigned long long timeout_ns = kWaitTimeoutNs;  // limit of every wait made through this context
 };
-
-constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -87,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0) {
       if (*ctx.cta_word != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (globaltimer_ns() - t0 > ctx.timeout_ns) {
         *ctx.cta_word = code;
         atomicCAS(ctx.device_word, 0u, code);
         return false;

@@ -24,6 +24,8 @@ _SIGNATURES = {
     "kfb_version": (c_int, []),
     "kfb_last_error": (c_char_p, []),
     "kfb_device_status": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
+    "kfb_device_status_reset": (c_int, [c_void_p]),
+    "kfb_selftest_wait_expiry": (c_int, [ctypes.c_ulonglong, c_void_p, c_void_p]),
     "kfb_quantize_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "kfb_unpack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "kfb_pack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -88,6 +90,27 @@ def device_status(device: torch.device) -> int:
     with on_device(device):
         check(lib().kfb_device_status(ctypes.byref(out)))
     return int(out.value)
+
+
+def device_status_reset(device: torch.device) -> None:
+    """Clears the device status word (enqueued on the current stream of `device`)."""
+    with on_device(device):
+        check(lib().kfb_device_status_reset(stream_ptr(device)))
+
+
+class DeviceStatusError(RuntimeError):
+    """A bounded wait inside a kernel expired (or a kernel refused a device-side argument): every launch since
+    then returned without writing its output."""
+
+
+def raise_on_device_status(device: torch.device) -> None:
+    """Synchronising check for host code at a natural sync point: raises DeviceStatusError when the status word of
+    `device` is non-zero.  The word is left as it is; clear it with device_status_reset once the cause is known."""
+    code = device_status(device)
+    if code:
+        raise DeviceStatusError(
+            f"kfb200 device status 0x{code:x} on {device}: a kernel gave up a bounded wait or rejected a device-side "
+            "argument; results enqueued since then are not valid (see kfb_device_status_reset in include/kfb200.h)")
 
 
 def dtype_code(dtype: torch.dtype) -> int:

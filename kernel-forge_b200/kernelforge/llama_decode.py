@@ -135,6 +135,9 @@ class LlamaInt4Decoder:
         self.kv_len = torch.zeros(batch, dtype=torch.int32, device=self.dev)
         self.step_logits = torch.zeros(batch, s.vocab, dtype=torch.float16, device=self.dev)
         self.graph = None
+        # Host mirror of `pos`: the number of cache rows in use.  The step graph reads the position on the device,
+        # so the host checks here that a replay can never be asked to write past the cache.
+        self._host_pos = 0
 
     # ------------------------------------------------------------------ construction helpers
     def _gather(self, y_local: torch.Tensor, bounds_key: str) -> torch.Tensor:
@@ -207,6 +210,8 @@ class LlamaInt4Decoder:
         """ids [B, T] -> logits [B, T, vocab] (fp16); fills the cache and arms the decode state with the
         greedy next token."""
         s, (b, t) = self.s, ids.shape
+        if t >= self.max_len:
+            raise ValueError(f"prompt of {t} tokens leaves no room in a cache of {self.max_len} rows for a decode step")
         ids = ids.to(self.dev)
         x = self.embed[ids]
         cos, sin = self.cos[:t], self.sin[:t]
@@ -229,6 +234,7 @@ class LlamaInt4Decoder:
         self.tok.copy_(logits[:, -1].float().argmax(-1))
         self.pos.fill_(t)
         self.kv_len.fill_(t + 1)
+        self._host_pos = t
         return logits
 
     # ------------------------------------------------------------------ one decode step (graph body)
@@ -257,7 +263,10 @@ class LlamaInt4Decoder:
         self.kv_len.add_(1)
 
     def capture(self):
-        """Captures one decode step.  State is saved and restored around the warm-up / capture runs."""
+        """Captures one decode step.  State is saved and restored around the warm-up / capture runs (the warm-up
+        step writes cache row `pos`, which the first real step rewrites with the same values)."""
+        if self._host_pos >= self.max_len:
+            raise ValueError(f"the KV cache ({self.max_len} rows) is full: no room for the warm-up step")
         saved = (self.tok.clone(), self.pos.clone(), self.kv_len.clone())
         side = torch.cuda.Stream(self.dev)
         with torch.cuda.stream(side):
@@ -280,9 +289,14 @@ class LlamaInt4Decoder:
         torch.cuda.synchronize(self.dev)
 
     @torch.no_grad()
-    def decode(self, steps: int, keep_logits: bool = False):
+    def decode(self, steps: int, keep_logits: bool = False, check_status: bool = True):
         """Runs `steps` greedy steps from the armed state.  Returns (tokens [B, steps] fed to the model,
-        logits [B, steps, vocab] or None)."""
+        logits [B, steps, vocab] or None).  Raises ValueError when the steps do not fit in the KV cache (every
+        step writes one cache row; nothing is launched then).  With `check_status` the device status word is read
+        after the last step (one 4-byte copy, synchronising) and a kernel that gave up raises DeviceStatusError."""
+        if steps < 0 or self._host_pos + steps > self.max_len:
+            raise ValueError(f"{steps} decode steps from position {self._host_pos} do not fit in a KV cache of "
+                             f"{self.max_len} rows")
         if self.graph is None:
             self.capture()
         toks, logs = [], []
@@ -291,4 +305,8 @@ class LlamaInt4Decoder:
             self.graph.replay()
             if keep_logits:
                 logs.append(self.step_logits.clone())
+        self._host_pos += steps
+        if check_status:
+            from . import _capi
+            _capi.raise_on_device_status(self.dev)
         return torch.stack(toks, 1), (torch.stack(logs, 1) if keep_logits else None)

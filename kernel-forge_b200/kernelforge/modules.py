@@ -1,6 +1,9 @@
 """Drop-in modules that put the B200 kernels inside Hugging Face models.
 
-Same surface as the reference (kernelforge/modules.py:19-115):
+Same surface as the reference (kernelforge/modules.py:19-115), and the body follows the reference's file
+function by function, in places line by line: this is glue between Hugging Face classes and the operator
+surface, and buffer names, the attention-interface registration, the reuse of the flash_attention_2 mask
+builder and the ATTN_STATS keys are all part of the contract.
 
 - KFLinearInt4: nn.Linear replacement holding group-wise INT4 weights, forward via ops.int4_linear.
 - quantize_linears_: swap a model's decoder linears (q, k, v, o, gate, up, down) for KFLinearInt4.

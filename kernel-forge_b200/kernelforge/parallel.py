@@ -136,12 +136,19 @@ class FusedShardedInt4Linear(torch.nn.Module):
     rank's kernel -- and with it every store into this rank's buffer -- has completed).  The two buffers
     alternate, so a rank that runs ahead never overwrites a result a slower peer is still reading (it cannot
     get two calls ahead: its next all-reduce needs the peer).  Only stores cross the link, never loads.
+
+    Lifetime of the result: by default forward() returns a private copy.  With `alias=True` it returns a view of
+    the symmetric buffer itself (no copy): that view is valid only until the next-but-one forward() of this
+    module -- the peers then store the new result into the same memory -- and every consumer of it must be
+    enqueued on the calling stream before that call.  Do not keep an aliased result in a list, across two calls,
+    or read it from another stream.
     """
 
     def __init__(self, qw_full_shape: tuple[int, int], local: kq.QuantizedWeight, max_m: int,
-                 bias: torch.Tensor | None = None, group: dist.ProcessGroup | None = None):
+                 bias: torch.Tensor | None = None, group: dist.ProcessGroup | None = None, alias: bool = False):
         super().__init__()
         import torch.distributed._symmetric_memory as symm
+        self.alias = alias
         self.out_features, self.in_features = qw_full_shape
         self.group_size = local.group_size
         self.group = group if group is not None else dist.group.WORLD
@@ -162,9 +169,9 @@ class FusedShardedInt4Linear(torch.nn.Module):
         self._turn = 0
 
     @classmethod
-    def from_full(cls, qw: kq.QuantizedWeight, max_m: int, bias=None, group=None) -> "FusedShardedInt4Linear":
+    def from_full(cls, qw: kq.QuantizedWeight, max_m: int, bias=None, group=None, alias: bool = False) -> "FusedShardedInt4Linear":
         g = group if group is not None else dist.group.WORLD
-        return cls(qw.shape, shard_quantized_weight(qw, dist.get_rank(g), dist.get_world_size(g)), max_m, bias, g)
+        return cls(qw.shape, shard_quantized_weight(qw, dist.get_rank(g), dist.get_world_size(g)), max_m, bias, g, alias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import ctypes
@@ -189,5 +196,7 @@ class FusedShardedInt4Linear(torch.nn.Module):
         dist.all_reduce(self._flag, group=self.group)  # stream-ordered rendezvous: every rank's stores have landed
         y = self._bufs[turn][:m]
         if self.bias is not None:
-            y = y + self.bias
+            y = y + self.bias          # a new tensor already
+        elif not self.alias:
+            y = y.clone()
         return y.reshape(*lead, self.out_features)

@@ -88,7 +88,9 @@ def attention_cases(ta):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path of a checkout of the reference repository>")
+    ref_root = Path(sys.argv[1])
     kq, ta = _ref_modules(ref_root)
     torch.set_num_threads(4)
     quant_cases(kq)
