@@ -41,7 +41,7 @@ constexpr int kHalfBytes = kBlockN * 128;  // one 64-column half of a tile: 128 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum WaitCode : uint32_t {
-  kWaitQ = 0x101, kWaitKEmpty, kWaitKFull, kWaitVEmpty, kWaitVFull, kWaitSFull, kWaitPReady, kWaitPvDone, kWaitIssuer
+  kWaitQ = 0x101, kWaitKEmpty, kWaitKFull, kWaitVEmpty, kWaitVFull, kWaitSFull, kWaitPReady, kWaitPvDone, kWaitIssuer, kWaitTurn
 };
 
 template <int D>
@@ -60,9 +60,13 @@ struct Layout {
 };
 
 __device__ __forceinline__ float ex2(float x) {
+#ifdef KFB_X_NOEXP
+  return fmaf(x, 0.001f, 0.5f);
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 // three-input maximum (one instruction on sm_100)
@@ -70,6 +74,23 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
+}
+
+// 2^x for two values on the FMA pipe instead of the exponential unit: x = j + f with j = round(x), f in [-0.5, 0.5];
+// 2^f by a degree-3 polynomial (relative error 7.5e-5, far below the rounding of p to fp16 / bf16); j goes straight
+// into the exponent field.  x <= -125 (masked scores are -inf) gives ~2^-125, which rounds to 0 like the exact value.
+__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f), nmagic = make_float2(-12582912.f, -12582912.f);  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, magic);          // low mantissa bits of t = round(x)
+  const float2 jf = __fadd2_rn(t, nmagic);
+  const float2 f = __fadd2_rn(x, make_float2(-jf.x, -jf.y));
+  float2 pl = __ffma2_rn(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
+  pl = __ffma2_rn(pl, f, make_float2(0.6932609677f, 0.6932609677f));
+  pl = __ffma2_rn(pl, f, make_float2(0.9999280572f, 0.9999280572f));
+  return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23)));
 }
 
 template <bool kBf16>
@@ -392,12 +413,11 @@ attn_prefill_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 
 // ------------------------------------------------------------------------------------------------
 // Pair kernel: one CTA per SM, two query tiles (A = rows [q0, q0+128), B = the next 128) of one
-// (batch, head), steps of 128 keys.  384 threads (three warpgroups):
+// (batch, head), steps of 128 keys.  384 threads (three warpgroups; warp 11 only takes part in barriers):
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B (warp w touches TMEM lanes 32 (w % 4)..);
 //   warp 8     TMA producer: both Q tiles once, then K and V tiles of 128 keys through mbarrier rings;
-//   warp 9     one thread issues every tcgen05.mma of the CTA from an event loop: whichever of
-//              QK_A, QK_B, PV_A, PV_B has its inputs ready goes next, so neither tile's chain ever
-//              blocks the other's.
+//   warps 9,10 one thread each issues the tcgen05.mma of tile A / tile B from an event loop: whichever
+//              of QK(j+1) and PV(j) of its tile has its inputs ready goes next.
 // TMEM (all 512 columns), head dim 64:  S_X [128 X, +128)   O_X [256 + 64 X, +64)   P_X [384 + 64 X, +64)
 //                          head dim 128: S_X [128 X, +128)   O_X [256 + 128 X, +128), P_X aliased on S_X [.., +64)
 // A softmax thread loads the 128 scores of its row into registers in one go and releases the S buffer
@@ -410,7 +430,19 @@ attn_prefill_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // ------------------------------------------------------------------------------------------------
 namespace pair {
 
-constexpr int kPairThreads = 384;   // three warpgroups; warps 10 and 11 only take part in the barriers
+#ifdef KFB_TRACE
+// Tuning aid of -DKFB_TRACE builds: CTA 0 writes clock stamps [role][step < 32][8] (roles: 0 softmax thread of
+// tile A, 1 of tile B, 2 issuer, 3 producer) into a buffer set through kfb_debug_set_attn_trace.
+__device__ unsigned long long* g_trace_buf = nullptr;
+#define KFB_STAMP(role, j, k)                                                                        \
+  do {                                                                                               \
+    if (trace_ptr != nullptr && (j) < 32) trace_ptr[((role) * 32 + (j)) * 8 + (k)] = clock64();   \
+  } while (0)
+#else
+#define KFB_STAMP(role, j, k) do { } while (0)
+#endif
+
+constexpr int kPairThreads = 384;   // three warpgroups
 constexpr int kPairProducerWarp = 8;
 constexpr int kPairMmaWarp = 9;
 constexpr uint32_t kPairTmemCols = 512;
@@ -424,7 +456,7 @@ struct PairLayout {
   static constexpr int kK = 2 * kTile;
   static constexpr int kV = kK + kStages * kTile;
   static constexpr int kBars = kV + kStages * kTile;
-  static constexpr int kNumBars = 1 + 4 * kStages + 8;
+  static constexpr int kNumBars = 1 + 4 * kStages + 10;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kBytes = kMisc + 16;
   static constexpr int kAlloc = kBytes + 1024;
@@ -436,13 +468,13 @@ struct PairLayout {
   static constexpr uint32_t kStrideP = kAliasP ? 128u : 64u;
 };
 
-// Maximum of the 128 scores of this thread's row (in registers); eight independent chains of
+// Maximum of the 128 scores of this thread's row (in registers); sixteen independent chains of
 // three-input maxima.  kMask: columns past `limit` count as -inf.
 template <bool kMask>
 __device__ __forceinline__ float row_max128(const uint32_t (&v)[4][32], int limit) {
-  float mx[8];
+  float mx[16];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+  for (int i = 0; i < 16; ++i) mx[i] = -INFINITY;
 #pragma unroll
   for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -450,9 +482,11 @@ __device__ __forceinline__ float row_max128(const uint32_t (&v)[4][32], int limi
       float x0 = __uint_as_float(v[c][i]), x1 = __uint_as_float(v[c][i + 1]);
       if (kMask && c * 32 + i > limit) x0 = -INFINITY;
       if (kMask && c * 32 + i + 1 > limit) x1 = -INFINITY;
-      mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], x0, x1);
+      mx[i >> 1] = max3(mx[i >> 1], x0, x1);
     }
-  return fmaxf(max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) mx[i] = fmaxf(max3(mx[i], mx[i + 4], mx[i + 8]), mx[i + 12]);
+  return fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
 }
 
 // p = 2^(x * scale - base) for the 128 scores of the row, rounded to the I/O type into `p` (two per
@@ -461,7 +495,7 @@ __device__ __forceinline__ float row_max128(const uint32_t (&v)[4][32], int limi
 // those of the scalar forms.
 template <bool kMask, bool kBf16>
 __device__ __forceinline__ float exp128(const uint32_t (&v)[4][32], uint32_t (&p)[4][16], int limit, float scale_log2,
-                                       float base) {
+                                       float base, uint64_t* pass_baton) {
   float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
   const float2 sc2 = make_float2(scale_log2, scale_log2), nb2 = make_float2(-base, -base);
 #pragma unroll
@@ -472,10 +506,23 @@ __device__ __forceinline__ float exp128(const uint32_t (&v)[4][32], uint32_t (&p
       if (kMask && c * 32 + 2 * i > limit) x.x = -INFINITY;
       if (kMask && c * 32 + 2 * i + 1 > limit) x.y = -INFINITY;
       x = __ffma2_rn(x, sc2, nb2);
-      const float2 e = make_float2(ex2(x.x), ex2(x.y));
+      float2 e;
+#ifdef KFB_X_POLY
+      if (i % KFB_X_POLY == KFB_X_POLY - 1) {
+        e = exp2_fma_pipe(x);
+      } else
+#endif
+      e = make_float2(ex2(x.x), ex2(x.y));
       sum[i & 3] = __fadd2_rn(sum[i & 3], e);
+#ifdef KFB_X_NOCVT
+      p[c][i] = __float_as_uint(e.x) ^ (__float_as_uint(e.y) >> 16);
+#else
       p[c][i] = pack2<kBf16>(e.x, e.y);
+#endif
     }
+#ifdef KFB_X_EARLY
+    if (c == KFB_X_EARLY) mbar_arrive(pass_baton);
+#endif
   }
   const float2 t = __fadd2_rn(__fadd2_rn(sum[0], sum[1]), __fadd2_rn(sum[2], sum[3]));
   return t.x + t.y;
@@ -489,6 +536,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   using L = PairLayout<D>;
   constexpr int S = L::kStages;
   constexpr bool kAliasP = L::kAliasP;
+#ifdef KFB_TRACE
+  const unsigned long long t_entry = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -501,6 +551,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   uint64_t* s_free = s_full + 2;     // [X]: all 128 threads of tile X hold their scores in registers
   uint64_t* p_ready = s_free + 2;    // [X]: P_X stored by all 128 threads
   uint64_t* pv_done = p_ready + 2;   // [X]: the PV product that read P_X has completed (O_X updated)
+  uint64_t* turn = pv_done + 2;      // [X]: the other warpgroup has finished its exponentials: X may start its own
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile uint32_t* abort_word = tmem_slot + 1;
   const AbortCtx ctx{abort_word, status};
@@ -521,26 +572,30 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (causal) kv_end = min(Nk, min(q0x + kBlockM, Nq) + causal_off);
     n_steps[X] = q0x < Nq ? (kv_end + kBlockN - 1) / kBlockN : 0;   // tile B may not exist
   }
+#ifdef KFB_X_ONETILE
+  n_steps[1] = 0;
+#endif
   const int n_max = max(n_steps[0], n_steps[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < S; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+      mbar_init(&k_empty[s], 2);   // one arrival per issuer thread
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+      mbar_init(&v_empty[s], 2);
     }
     for (int X = 0; X < 2; ++X) {
       mbar_init(&s_full[X], 1);
       mbar_init(&s_free[X], 128);
       mbar_init(&p_ready[X], 128);
       mbar_init(&pv_done[X], 1);
+      mbar_init(&turn[X], 128);
     }
     *abort_word = *reinterpret_cast<volatile unsigned int*>(status);  // a wait expired earlier on this device:
     fence_mbar_init();                                                // do no work, return at once
   }
-  if (warp == kPairMmaWarp) {
+  if (warp == kPairMmaWarp) {   // the first issuer warp also owns the TMEM allocation
     tmem_alloc(tmem_slot, kPairTmemCols);
     tmem_relinquish();
   }
@@ -549,6 +604,10 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool dead_on_arrival = *abort_word != 0;
+#ifdef KFB_TRACE
+  unsigned long long* const trace_ptr = blockIdx.x == 0 ? g_trace_buf : nullptr;
+  if (threadIdx.x == 0 && trace_ptr) { trace_ptr[31 * 8 + 0] = t_entry; trace_ptr[31 * 8 + 1] = clock64(); }
+#endif
 
   // Registers move from the warpgroup of the two single-thread roles to the softmax warpgroups, which keep
   // the 128 scores of a row in registers (2 x 128 x 208 + 128 x 88 = 64512 of 65536).  Each role branch
@@ -584,81 +643,95 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           tma_load_4d(smem + L::kV + s * L::kTile + half * kHalfBytes, &tm_v, &v_full[s], half * 64, j * kBlockN, hk, b);
       }
     }
-  } else if (warp == kPairMmaWarp) {
-    // ------------------------------------------------------------------ tcgen05.mma issuer (event loop)
+  } else if (warp == kPairMmaWarp || warp == kPairMmaWarp + 1) {
+    // ------------------------------------------------------------------ tcgen05.mma issuers (one thread per tile)
+    // Issuing an MMA occupies the issuing thread for about as long as the MMA runs, and a commit for ~130 clocks,
+    // so one thread feeding both tiles is the bottleneck of the CTA; with one issuer per tile the commits of one
+    // overlap the MMAs of the other.  The two threads never touch each other's TMEM columns.  A K / V stage goes
+    // back to the producer when BOTH have arrived on its `empty` barrier (count 2): a tile that does not need a
+    // key tile (no tile B, or one step less under a causal mask) still arrives for it once it has been loaded.
     if (lane == 0) {
+      const int X = warp - kPairMmaWarp;
       constexpr uint32_t idesc_qk = idesc_f16(kBlockM, kBlockN, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(kBlockM, D, kBf16 ? 1 : 0, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + L::kQ);
+      const uint32_t qa = smem_u32(smem + L::kQ) + (uint32_t)X * L::kTile;
       const uint32_t k_addr0 = smem_u32(smem + L::kK), v_addr0 = smem_u32(smem + L::kV);
-      int qk_next[2] = {0, 0}, pv_next[2] = {0, 0};   // products issued so far, per tile
-      int k_rel = 0, v_rel = 0;                       // next K / V tile to hand back to the producer
-      bool ok = mbar_wait(q_full, 0, ctx, kWaitQ);
+      const uint32_t s_col = tmem_base + L::kColS + 128u * X, o_col = tmem_base + L::kColO + (uint32_t)D * X;
+      const uint32_t p_col = tmem_base + L::kColP + L::kStrideP * X;
+      const int n = n_steps[X];
+      int qk_next = 0, pv_next = 0;   // steps handled so far (issued, or passed on for a tile that has no such step)
+      bool ok = n == 0 || mbar_wait(q_full, 0, ctx, kWaitQ);
       tc_fence_after_sync();
       uint32_t idle = 0;
       unsigned long long idle_since = 0;
-      while (ok && (pv_next[0] < n_steps[0] || pv_next[1] < n_steps[1])) {
+      while (ok && (qk_next < n_max || pv_next < n_max)) {
         bool progress = false;
+        // ---- S(j) = Q K(j)^T: needs the S buffer (scores of step j-1 in registers; with aliased P: PV(j-1)
+        //      issued, which executes first) and the K tile
+        if (qk_next < n_max) {
+          const int j = qk_next, s = j % S;
+          if (j >= n) {   // not a step of this tile: hand the stage on as soon as it has been filled
+            if (mbar_test_wait(&k_full[s], (uint32_t)(j / S) & 1u)) {
+              mbar_arrive(&k_empty[s]);
+              qk_next = j + 1;
+              progress = true;
+            }
+          } else {
+            const bool buffer_free = kAliasP ? (pv_next >= j) : (j == 0 || mbar_test_wait(&s_free[X], (uint32_t)(j - 1) & 1u));
+            if (buffer_free && mbar_test_wait(&k_full[s], (uint32_t)(j / S) & 1u)) {
+              KFB_STAMP(2 + X, j, 0);
+              tc_fence_after_sync();
+              const uint32_t ka = k_addr0 + (uint32_t)s * L::kTile;
 #pragma unroll
-        for (int X = 0; X < 2; ++X) {
-          // ---- S_X(j) = Q_X K(j)^T: needs the S buffer (scores of step j-1 in registers; with aliased P: PV(j-1)
-          //      issued, which executes first) and the K tile
-          {
-            const int j = qk_next[X];
-            if (j < n_steps[X]) {
-              const bool buffer_free = kAliasP ? (pv_next[X] >= j) : (j == 0 || mbar_try_wait(&s_free[X], (uint32_t)(j - 1) & 1u));
-              const int s = j % S;
-              if (buffer_free && mbar_try_wait(&k_full[s], (uint32_t)(j / S) & 1u)) {
-                tc_fence_after_sync();
-                const uint32_t qa = q_addr + (uint32_t)X * L::kTile, ka = k_addr0 + (uint32_t)s * L::kTile;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                  const uint32_t off = (uint32_t)(kk / 4) * kHalfBytes + (uint32_t)(kk % 4) * 32u;
-                  mma_ss(tmem_base + L::kColS + 128u * X, smem_desc_sw128(qa + off, 16, 1024),
-                         smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
-                }
-                tc_commit(&s_full[X]);
-                qk_next[X] = j + 1;
-                progress = true;
-                // a K tile goes back once every tile that needs it has multiplied it
-                while (k_rel < n_max && (qk_next[0] > k_rel || k_rel >= n_steps[0]) &&
-                       (qk_next[1] > k_rel || k_rel >= n_steps[1])) {
-                  tc_commit(&k_empty[k_rel % S]);
-                  ++k_rel;
-                }
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(kk / 4) * kHalfBytes + (uint32_t)(kk % 4) * 32u;
+                mma_ss(s_col, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_qk,
+                       kk > 0 ? 1u : 0u);
               }
+              KFB_STAMP(2 + X, j, 1);
+              tc_commit(&s_full[X]);
+              tc_commit(&k_empty[s]);
+              KFB_STAMP(2 + X, j, 2);
+              qk_next = j + 1;
+              progress = true;
             }
           }
-          // ---- O_X += P_X(j) V(j): needs P (stored by the 128 softmax threads of the tile) and the V tile
-          {
-            const int j = pv_next[X];
-            if (j < n_steps[X] && j < qk_next[X]) {
-              const int s = j % S;
-              if (mbar_try_wait(&p_ready[X], (uint32_t)j & 1u) && mbar_try_wait(&v_full[s], (uint32_t)(j / S) & 1u)) {
-                tc_fence_after_sync();
-                const uint32_t va = v_addr0 + (uint32_t)s * L::kTile;
-#pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                  // 16 keys per MMA: 16 rows of 128 bytes; the second 64-column block of V is kHalfBytes away
-                  mma_ts(tmem_base + L::kColO + (uint32_t)D * X, tmem_base + L::kColP + L::kStrideP * X + (uint32_t)kk * 8u,
-                         smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                }
-                tc_commit(&pv_done[X]);
-                pv_next[X] = j + 1;
-                progress = true;
-                while (v_rel < n_max && (pv_next[0] > v_rel || v_rel >= n_steps[0]) &&
-                       (pv_next[1] > v_rel || v_rel >= n_steps[1])) {
-                  tc_commit(&v_empty[v_rel % S]);
-                  ++v_rel;
-                }
-              }
+        }
+        // ---- O += P(j) V(j): needs P (stored by the 128 softmax threads of the tile) and the V tile
+        if (pv_next < n_max && pv_next < qk_next) {
+          const int j = pv_next, s = j % S;
+          if (j >= n) {
+            if (mbar_test_wait(&v_full[s], (uint32_t)(j / S) & 1u)) {
+              mbar_arrive(&v_empty[s]);
+              pv_next = j + 1;
+              progress = true;
             }
+          } else if (mbar_test_wait(&p_ready[X], (uint32_t)j & 1u) && mbar_test_wait(&v_full[s], (uint32_t)(j / S) & 1u)) {
+            KFB_STAMP(2 + X, j, 3);
+            tc_fence_after_sync();
+            const uint32_t va = v_addr0 + (uint32_t)s * L::kTile;
+#pragma unroll
+            for (int kk = 0; kk < kBlockN / 16; ++kk) {
+              // 16 keys per MMA: 16 rows of 128 bytes; the second 64-column block of V is kHalfBytes away
+              mma_ts(o_col, p_col + (uint32_t)kk * 8u, smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
+                     (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            KFB_STAMP(2 + X, j, 4);
+            tc_commit(&pv_done[X]);
+            tc_commit(&v_empty[s]);
+            KFB_STAMP(2 + X, j, 5);
+            pv_next = j + 1;
+            progress = true;
           }
         }
         if (progress) {
           idle = 0;
           idle_since = 0;
+#ifdef KFB_X_SLEEP
+        } else if (__nanosleep(KFB_X_SLEEP), (++idle & 63u) == 0) {
+#else
         } else if ((++idle & 63u) == 0) {   // bounded like every other wait of the library
+#endif
           if (*abort_word != 0) break;
           const unsigned long long now = globaltimer_ns();
           if (idle_since == 0) {
@@ -686,11 +759,21 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     float m_base = -INFINITY;  // the base O and l are currently expressed in (log2 units)
     float l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n; ++j) {
+    for (int j = 0; j < n_max; ++j) {
       const uint32_t ph = (uint32_t)j & 1u;
+      if (j >= n) {
+        // no such step for this tile (no tile B, or one step less under a causal mask): only pass the baton on
+        if (X == 1 || j > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&turn[X], (X == 1 ? ph : ph ^ 1u), ctx, kWaitTurn));
+          if (!ok) break;
+        }
+        mbar_arrive(&turn[X ^ 1]);
+        continue;
+      }
       // every lane polls: measured faster than one polling lane plus a shuffle
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[X], ph, ctx, kWaitSFull));
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 0);
       tc_fence_after_sync();
       uint32_t v[4][32];   // the 128 scores of this row, loaded once
 #pragma unroll
@@ -701,13 +784,18 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         tc_fence_before_sync();
         mbar_arrive(&s_free[X]);
       }
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 1);
       const int k0 = j * kBlockN;
       const bool need_mask = (k0 + kBlockN > Nk) || (causal && (k0 + kBlockN - 1 > q0x + causal_off));
       int limit = Nk - 1;
       if (causal) limit = min(limit, q0x + row + causal_off);
       limit -= k0;  // last visible column of this step for this row
 
+#ifdef KFB_X_NOMAX
+      const float m_step = 6.0f;
+#else
       const float m_step = (need_mask ? row_max128<true>(v, limit) : row_max128<false>(v, limit)) * scale_log2;
+#endif
       // lazy rescale: move the base only when the maximum outgrew it by more than the threshold
       const bool grow = m_step > m_base + kRescaleThreshold || m_base == -INFINITY;
       float alpha = 1.0f;
@@ -716,6 +804,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         m_base = m_step;
       }
       const float base = (m_base == -INFINITY) ? 0.f : m_base;
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 2);
       bool rescaled = false;
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         // O is rescaled between PV(j-1), which must have finished accumulating, and PV(j), which cannot have
@@ -738,10 +827,22 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           }
         }
       }
+      // The two warpgroups take turns on the exponential unit: A(0), B(0), A(1), B(1), ...  While one runs its
+      // exponentials the other loads scores, takes maxima, stores P and synchronises, so the unit is not idle
+      // while both do the same cheap thing and not oversubscribed while both want it.  A waits for B(j-1), B for A(j).
+      if (X == 1 || j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&turn[X], (X == 1 ? ph : ph ^ 1u), ctx, kWaitTurn));
+        if (!ok) break;
+      }
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 6);
       uint32_t p16[4][16];
-      const float step_sum = need_mask ? exp128<true, kBf16>(v, p16, limit, scale_log2, base)
-                                       : exp128<false, kBf16>(v, p16, limit, scale_log2, base);
+      const float step_sum = need_mask ? exp128<true, kBf16>(v, p16, limit, scale_log2, base, &turn[X ^ 1])
+                                       : exp128<false, kBf16>(v, p16, limit, scale_log2, base, &turn[X ^ 1]);
+#ifndef KFB_X_EARLY
+      mbar_arrive(&turn[X ^ 1]);
+#endif
       l_run = fmaf(l_run, alpha, step_sum);
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 3);
       if constexpr (!kAliasP) {
         // PV(j-1) must have finished reading the P columns before they are overwritten.  By now it has: the
         // exponentials above take longer than the product.  (With aliased P it finished before S(j) was
@@ -752,15 +853,18 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           tc_fence_after_sync();
         }
       }
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 4);
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_st_x16(p_tmem + c * 16, p16[c]);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_ready[X]);
+      if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 5);
     }
     // PVs complete in issue order: the last one done means all are
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[X], (uint32_t)(n - 1) & 1u, ctx, kWaitPvDone));
     if (ok && n > 0) {
+      if (threadIdx.x == 0) KFB_STAMP(0, 31, 2);
       tc_fence_after_sync();
       const float inv_l = 1.0f / l_run;
       const bool store = q0x + row < Nq;
@@ -789,12 +893,15 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);  // let copies in flight land
   }
+  if (threadIdx.x == 0) KFB_STAMP(0, 31, 3);
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) KFB_STAMP(0, 31, 4);
   if (warp == kPairMmaWarp) {
     __syncwarp();
     tmem_dealloc(tmem_base, kPairTmemCols);
   }
+  if (threadIdx.x == kPairMmaWarp * 32) KFB_STAMP(0, 31, 5);
 }
 
 }  // namespace pair
@@ -865,3 +972,9 @@ int launch_prefill(const Problem& p, cudaStream_t stream) {
 
 }  // namespace attn
 }  // namespace kfb
+
+#ifdef KFB_TRACE
+extern "C" void kfb_debug_set_attn_trace(void* device_buffer) {
+  cudaMemcpyToSymbol(kfb::attn::pair::g_trace_buf, &device_buffer, sizeof(void*));
+}
+#endif

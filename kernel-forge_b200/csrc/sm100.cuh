@@ -77,6 +77,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase.  mbarrier.try_wait may suspend the thread for a system-dependent time when the phase
+// is not complete; a loop that polls several barriers in turn (an event loop) must use this form instead, or every
+// unfinished barrier delays the look at the next one.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Warp-collective wait: lane 0 waits, the other lanes sleep at the warp barrier instead of polling.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const struct AbortCtx& ctx, uint32_t code);
 
