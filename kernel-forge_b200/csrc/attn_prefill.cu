@@ -60,13 +60,9 @@ struct Layout {
 };
 
 __device__ __forceinline__ float ex2(float x) {
-#ifdef KFB_X_NOEXP
-  return fmaf(x, 0.001f, 0.5f);
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 // three-input maximum (one instruction on sm_100)
@@ -74,23 +70,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
-}
-
-// 2^x for two values on the FMA pipe instead of the exponential unit: x = j + f with j = round(x), f in [-0.5, 0.5];
-// 2^f by a degree-3 polynomial (relative error 7.5e-5, far below the rounding of p to fp16 / bf16); j goes straight
-// into the exponent field.  x <= -125 (masked scores are -inf) gives ~2^-125, which rounds to 0 like the exact value.
-__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
-  const float2 magic = make_float2(12582912.f, 12582912.f), nmagic = make_float2(-12582912.f, -12582912.f);  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
-  const float2 t = __fadd2_rn(x, magic);          // low mantissa bits of t = round(x)
-  const float2 jf = __fadd2_rn(t, nmagic);
-  const float2 f = __fadd2_rn(x, make_float2(-jf.x, -jf.y));
-  float2 pl = __ffma2_rn(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
-  pl = __ffma2_rn(pl, f, make_float2(0.6932609677f, 0.6932609677f));
-  pl = __ffma2_rn(pl, f, make_float2(0.9999280572f, 0.9999280572f));
-  return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23)));
 }
 
 template <bool kBf16>
@@ -506,23 +485,11 @@ __device__ __forceinline__ float exp128(const uint32_t (&v)[4][32], uint32_t (&p
       if (kMask && c * 32 + 2 * i > limit) x.x = -INFINITY;
       if (kMask && c * 32 + 2 * i + 1 > limit) x.y = -INFINITY;
       x = __ffma2_rn(x, sc2, nb2);
-      float2 e;
-#ifdef KFB_X_POLY
-      if (i % KFB_X_POLY == KFB_X_POLY - 1) {
-        e = exp2_fma_pipe(x);
-      } else
-#endif
-      e = make_float2(ex2(x.x), ex2(x.y));
+      const float2 e = make_float2(ex2(x.x), ex2(x.y));
       sum[i & 3] = __fadd2_rn(sum[i & 3], e);
-#ifdef KFB_X_NOCVT
-      p[c][i] = __float_as_uint(e.x) ^ (__float_as_uint(e.y) >> 16);
-#else
       p[c][i] = pack2<kBf16>(e.x, e.y);
-#endif
     }
-#ifdef KFB_X_EARLY
-    if (c == KFB_X_EARLY) mbar_arrive(pass_baton);
-#endif
+    if (c == 1) mbar_arrive(pass_baton);   // half way: the other warp's first exponentials fill the gaps of the last ones here
   }
   const float2 t = __fadd2_rn(__fadd2_rn(sum[0], sum[1]), __fadd2_rn(sum[2], sum[3]));
   return t.x + t.y;
@@ -551,7 +518,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   uint64_t* s_free = s_full + 2;     // [X]: all 128 threads of tile X hold their scores in registers
   uint64_t* p_ready = s_free + 2;    // [X]: P_X stored by all 128 threads
   uint64_t* pv_done = p_ready + 2;   // [X]: the PV product that read P_X has completed (O_X updated)
-  uint64_t* turn = pv_done + 2;      // [X]: the other warpgroup has finished its exponentials: X may start its own
+  uint64_t* turn = pv_done + 2;      // [X]: the other tile's warpgroup is half way through its exponentials: X may start
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile uint32_t* abort_word = tmem_slot + 1;
   const AbortCtx ctx{abort_word, status};
@@ -572,9 +539,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (causal) kv_end = min(Nk, min(q0x + kBlockM, Nq) + causal_off);
     n_steps[X] = q0x < Nq ? (kv_end + kBlockN - 1) / kBlockN : 0;   // tile B may not exist
   }
-#ifdef KFB_X_ONETILE
-  n_steps[1] = 0;
-#endif
   const int n_max = max(n_steps[0], n_steps[1]);
 
   if (threadIdx.x == 0) {
@@ -727,11 +691,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         if (progress) {
           idle = 0;
           idle_since = 0;
-#ifdef KFB_X_SLEEP
-        } else if (__nanosleep(KFB_X_SLEEP), (++idle & 63u) == 0) {
-#else
         } else if ((++idle & 63u) == 0) {   // bounded like every other wait of the library
-#endif
           if (*abort_word != 0) break;
           const unsigned long long now = globaltimer_ns();
           if (idle_since == 0) {
@@ -791,11 +751,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
       if (causal) limit = min(limit, q0x + row + causal_off);
       limit -= k0;  // last visible column of this step for this row
 
-#ifdef KFB_X_NOMAX
-      const float m_step = 6.0f;
-#else
       const float m_step = (need_mask ? row_max128<true>(v, limit) : row_max128<false>(v, limit)) * scale_log2;
-#endif
       // lazy rescale: move the base only when the maximum outgrew it by more than the threshold
       const bool grow = m_step > m_base + kRescaleThreshold || m_base == -INFINITY;
       float alpha = 1.0f;
@@ -827,9 +783,12 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           }
         }
       }
-      // The two warpgroups take turns on the exponential unit: A(0), B(0), A(1), B(1), ...  While one runs its
-      // exponentials the other loads scores, takes maxima, stores P and synchronises, so the unit is not idle
-      // while both do the same cheap thing and not oversubscribed while both want it.  A waits for B(j-1), B for A(j).
+      // The two warpgroups take turns on the exponential units: A(0), B(0), A(1), B(1), ...  Left alone they drift into
+      // phase: both load scores and take maxima at the same time (units idle), then both want the units.  With the
+      // baton one runs its exponentials while the other loads, takes maxima, stores P and synchronises.  The baton is
+      // passed half way through, so the tail of one block overlaps the head of the next.  A waits for B(j-1), B for
+      // A(j).  (A baton per scheduler -- 32 threads instead of 128 -- measured 15 % slower: 74 against 64 us at
+      // B=2 H=16 N=2048; so did issuing the first TMA loads before the set-up barrier.)
       if (X == 1 || j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&turn[X], (X == 1 ? ph : ph ^ 1u), ctx, kWaitTurn));
         if (!ok) break;
@@ -838,9 +797,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
       uint32_t p16[4][16];
       const float step_sum = need_mask ? exp128<true, kBf16>(v, p16, limit, scale_log2, base, &turn[X ^ 1])
                                        : exp128<false, kBf16>(v, p16, limit, scale_log2, base, &turn[X ^ 1]);
-#ifndef KFB_X_EARLY
-      mbar_arrive(&turn[X ^ 1]);
-#endif
       l_run = fmaf(l_run, alpha, step_sum);
       if ((threadIdx.x & 127) == 0) KFB_STAMP(X, j, 3);
       if constexpr (!kAliasP) {
