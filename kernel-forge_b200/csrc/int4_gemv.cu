@@ -13,10 +13,13 @@
 //   * products are accumulated in FP32 with the sm_100 mixed-precision FMA
 //     (fma.rn.f32.f16: fp16 x fp16 + fp32, the product is exact), the per-group scale is
 //     applied in FP32 once per 32-weight chunk (32 divides G), then a warp-shuffle reduction
-//     and ONE rounding to fp16.  Result = FP32 dot product of the exact dequantised weights.
+//     and ONE rounding to fp16.  For M >= 3: an FP32 dot product of the exact dequantised weights.
 //     For M <= 2 the kernel is issue-bound on B200 (INT and half2 ops issue at half the FP32 rate),
 //     so there the half2 conversions are skipped: the masked 1024+u / 1024+16u forms feed the FMA
-//     directly and the offsets are subtracted per chunk using sums of x shared by all rows.
+//     directly and the offsets are subtracted per chunk using sums of x shared by all rows.  The
+//     accumulator then carries the offsets (up to ~1e3 |x| per weight) until the subtraction; the
+//     FMA rounds to nearest, so this costs a little precision (within the stated bounds, checked
+//     with one-signed activations too) but no bias.
 // K can be split across the warps of a CTA (fixed-order shared-memory reduce: deterministic).
 #include "common.cuh"
 #include "int4_gemv_mma.cuh"

@@ -145,6 +145,20 @@ def test_decode_with_device_side_length(b, h, hk, cap, d):
         assert np.abs(out[i:i + 1].float().cpu().numpy() - ref).max() <= ATTN_ATOL[torch.float16]
 
 
+@pytest.mark.parametrize("nk,d", [(512, 64), (4096, 64), (256, 128)])
+def test_decode_with_zero_length_row_gives_zeros(nk, d):
+    """A sequence with no valid key (kv_len = 0, e.g. a decode step captured before any prefill) yields zeros, not
+    0 / 0, in the unsplit and in the split-KV path; the other rows of the batch are unaffected."""
+    q, k, v = qkv_case(3, 8, 2, 1, nk, d, torch.float16, seed=nk + d)
+    lens = [0, nk, 5]
+    out = ops.flash_attn_decode(q.cuda(), k.cuda(), v.cuda(), torch.tensor(lens, dtype=torch.int32).cuda())
+    assert torch.isfinite(out).all()
+    assert bool((out[0] == 0).all())
+    for i in (1, 2):
+        ref = attn_oracle(q[i:i + 1], k[i:i + 1, :, :lens[i]], v[i:i + 1, :, :lens[i]], True)
+        assert np.abs(out[i:i + 1].float().cpu().numpy() - ref).max() <= ATTN_ATOL[torch.float16]
+
+
 def test_decode_length_is_read_at_replay_time():
     """One captured launch, replayed while the device-side length grows: the result follows the length."""
     q, k, v = qkv_case(1, 8, 2, 1, 256, 64, torch.float16, seed=77)

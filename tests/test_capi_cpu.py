@@ -115,3 +115,19 @@ def test_int4_matmul_routing_table():
     assert wins(16, 128256, 4096)                      # large N: the persistent streaming kernel
     assert not wins(12, 1536, 8960)                    # long K, few rows: the GEMM was faster
     assert not wins(12, 32000, 2048)                   # between the two regimes
+
+
+def test_decoder_refuses_steps_that_do_not_fit_the_cache():
+    """Host-side position check of the end-to-end decoder (the step graph reads the position on the device, so the
+    host must make sure a replay is never asked to write past the KV cache).  Nothing is launched: built on CPU."""
+    from kernelforge.llama_decode import LlamaInt4Decoder, LlamaShape
+    shape = LlamaShape(hidden=128, layers=1, heads=2, kv_heads=1, head_dim=64, intermediate=128, vocab=64)
+    dec = LlamaInt4Decoder.random_init(shape, "cpu", batch=1, max_len=8)
+    with pytest.raises(ValueError, match="no room"):
+        dec.prefill(torch.zeros(1, 8, dtype=torch.long))          # a prompt as long as the cache
+    dec._host_pos = 6                                             # as after a 6-token prompt
+    with pytest.raises(ValueError, match="do not fit"):
+        dec.decode(3)
+    dec._host_pos = 8
+    with pytest.raises(ValueError, match="full"):
+        dec.capture()

@@ -52,6 +52,43 @@ def test_rope_kv_write(b, h, hk, d):
     assert kc[:, :, untouched].abs().max().item() == 0 and vc[:, :, untouched].abs().max().item() == 0
 
 
+def test_rope_kv_write_stays_inside_the_cache():
+    """The position is read on the device.  In range: the row after the last cache row of the last (batch, kv head)
+    (a guard row of the same allocation) stays untouched.  Out of range: nothing is written at all and the device
+    status word reports 0x701; after a reset the kernel works again."""
+    from kernelforge import _capi
+    b, h, hk, d, lmax = 2, 8, 2, 64, 16
+    g = torch.Generator().manual_seed(1)
+    qkv = torch.randn(b, (h + 2 * hk) * d, generator=g).half().cuda()
+    ang = torch.outer(torch.arange(lmax, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d)))
+    ang = torch.cat([ang, ang], -1)
+    cos, sin = ang.cos().cuda(), ang.sin().cuda()
+    # caches with one guard row behind them: [b * hk * lmax + 1, d], the kernel is given the first b * hk * lmax rows
+    kbuf = torch.full((b * hk * lmax + 1, d), 3.0, dtype=torch.float16).cuda()
+    vbuf = torch.full((b * hk * lmax + 1, d), 3.0, dtype=torch.float16).cuda()
+    kc, vc = kbuf[:-1].view(b, hk, lmax, d), vbuf[:-1].view(b, hk, lmax, d)
+    dev = torch.device("cuda", 0)
+    ops.rope_kv_write(qkv, cos, sin, torch.tensor([lmax - 1]).cuda(), kc, vc, h)     # last legal position
+    torch.cuda.synchronize()
+    assert bool((kbuf[-1] == 3.0).all()) and bool((vbuf[-1] == 3.0).all())
+    assert not bool((kc[:, :, lmax - 1] == 3.0).all())
+    assert _capi.device_status(dev) == 0
+    before_k, before_v = kbuf.clone(), vbuf.clone()
+    try:
+        for bad in (lmax, lmax + 5, -1):
+            ops.rope_kv_write(qkv, cos, sin, torch.tensor([bad]).cuda(), kc, vc, h)
+            torch.cuda.synchronize()
+            assert torch.equal(kbuf, before_k) and torch.equal(vbuf, before_v), f"position {bad} wrote to the cache"
+        assert _capi.device_status(dev) == 0x701
+    finally:
+        _capi.device_status_reset(dev)
+        torch.cuda.synchronize()
+    assert _capi.device_status(dev) == 0
+    ops.rope_kv_write(qkv, cos, sin, torch.tensor([3]).cuda(), kc, vc, h)
+    torch.cuda.synchronize()
+    assert not bool((kc[:, :, 3] == 3.0).all())
+
+
 @pytest.mark.parametrize("rows,inter", [(1, 5632), (32, 5632), (4, 8960)])
 def test_silu_mul(rows, inter):
     gu = torch.randn(rows, 2 * inter, generator=torch.Generator().manual_seed(rows)).half().cuda()

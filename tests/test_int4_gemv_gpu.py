@@ -160,3 +160,29 @@ def test_int4_linear_shapes_and_bias():
     assert y.shape == (2, 3, 72) and y.dtype == torch.float16
     want = torch.from_numpy(ref).cuda().half() + bias
     assert (y.reshape(6, 72).float() - want.float()).abs().max().item() <= 4e-3 * float(np.abs(ref).max() + 1)
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("kind", ["abs", "shifted"])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (94720, 256)], ids=["split_k", "stream"])
+def test_gemv_one_signed_activations(n, k, kind, m, group):
+    """Activations with a large mean (post-ReLU / GELU inputs): the mma formulation accumulates offset forms of the
+    nibbles and subtracts class sums of x afterwards, so a one-signed x makes the cancelled magnitude largest.  Checked
+    against the oracle with the usual bound, and the mean error must show no systematic bias."""
+    rng = np.random.default_rng(n + k + m + group)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    from oracle import kf_oracle as ko
+    packed, scales = ko.quantize_weight(w, group)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    x = (np.abs(x) if kind == "abs" else x + 4.0).astype(np.float16)
+    ref = x.astype(np.float32) @ ko.dequantize(packed, scales, group, np.float32).T
+    for flags in (4, 2):   # the mma kernel, the CUDA-core kernel
+        y = torch.empty(m, n, dtype=torch.float16, device="cuda")
+        from kernelforge import _capi
+        xs, ps, ss = torch.from_numpy(x).cuda(), torch.from_numpy(packed).cuda(), torch.from_numpy(scales).cuda()
+        _capi.check(_capi.lib().kfb_int4_gemv(xs.data_ptr(), ps.data_ptr(), ss.data_ptr(), y.data_ptr(), m, n, k, group, flags,
+                                              _capi.stream_ptr(torch.device("cuda", 0))))
+        err, peak, rms, floor = assert_int4_close(y, ref, f"{kind} flags{flags}")
+        bias = float((y.float().cpu().numpy() - ref).mean())
+        assert abs(bias) <= 0.1 * floor + 1e-6, f"systematic bias {bias:.3e} (fp16 floor {floor:.3e}) with flags {flags}"

@@ -65,3 +65,53 @@ def test_graph_tokens_equal_eager_tokens():
         eager.append(b.tok.clone())
         b._step()
     assert torch.equal(graph_toks, torch.stack(eager, 1))
+
+
+def test_decode_past_the_cache_raises_and_writes_nothing():
+    base, _ = build(layers=1)
+    ids = torch.randint(0, 320, (1, 10), generator=torch.Generator().manual_seed(5))
+    dec = LlamaInt4Decoder.from_hf(base, "cuda", 1, max_len=16)
+    dec.prefill(ids)
+    dec.decode(6)                       # positions 10..15: the cache is now full
+    with pytest.raises(ValueError, match="do not fit"):
+        dec.decode(1)
+    from kernelforge import _capi
+    assert _capi.device_status(torch.device("cuda", 0)) == 0
+
+
+def test_tinyllama_architecture_logits_at_size():
+    """The end-to-end configuration at full size: 22 layers, hidden 2048, 32 heads / 4 KV heads of dim 64, SiLU MLP
+    5632, vocab 32000, random init (std 0.02), INT4 g128 decoder linears, prompt 512 + 256 generated tokens under a
+    CUDA graph.  Logits of the prefill and of every decode step are compared with an FP32 model holding the
+    dequantised weights, teacher-forced on the same 768 tokens (the reference's FP32 model run; here the FP32 model
+    runs on the GPU in true FP32 -- TF32 is off -- to keep the test short)."""
+    cfg = LlamaConfig(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4,
+                      intermediate_size=5632, vocab_size=32000, head_dim=64, max_position_embeddings=2048,
+                      rms_norm_eps=1e-5)
+    torch.manual_seed(0)
+    base = LlamaForCausalLM(cfg).eval()
+    prompt_len, steps = 512, 256
+    ids = torch.randint(0, 32000, (1, prompt_len), generator=torch.Generator().manual_seed(0))
+    dec = LlamaInt4Decoder.from_hf(base, "cuda", 1, max_len=prompt_len + steps + 8)
+    pre = dec.prefill(ids).float().cpu()
+    toks, logs = dec.decode(steps, keep_logits=True)
+    torch.cuda.synchronize()
+    got = torch.cat([pre, logs.float().cpu()], dim=1)            # [1, 768, vocab]
+    full = torch.cat([ids, toks.cpu()], dim=1)[:, :prompt_len + steps]
+    del dec
+    torch.cuda.empty_cache()
+    ref = base.float().cuda()
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.half().float())
+        for name, mod in ref.named_modules():
+            if name.split(".")[-1] in km.DECODER_LINEARS and isinstance(mod, torch.nn.Linear):
+                mod.weight.copy_(kq.dequantize(kq.quantize_weight(mod.weight.detach().half(), 128), torch.float32))
+        want = ref(full.cuda()).logits.float().cpu()
+    scale = want.abs().max().item()
+    err_pre = (got[:, :prompt_len] - want[:, :prompt_len]).abs().max().item()
+    err_dec = (got[:, prompt_len:] - want[:, prompt_len:]).abs().max().item()
+    agree = (got.argmax(-1) == want.argmax(-1)).float().mean().item()
+    print(f"PARITY tinyllama-arch 22 layers, 768 tokens: logit scale {scale:.3f}  max_abs_err prefill {err_pre:.3e} "
+          f"decode {err_dec:.3e}  bound {2e-2 * scale:.3e}  greedy-token agreement {agree:.4f}")
+    assert err_pre <= 2e-2 * scale and err_dec <= 2e-2 * scale

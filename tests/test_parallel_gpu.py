@@ -45,6 +45,14 @@ def _worker(rank, world, port):
                     assert np.abs(y_p - ref).max() <= tol, f"nccl n{n} m{m} rep{rep}"
                     if m > 4:  # both paths then run the same GEMM kernel on the same shard
                         assert np.array_equal(y_f, y_p)
+        # lifetime of the result: by default forward() returns a private copy, so a result kept across later calls (which
+        # overwrite both symmetric buffers) does not change; with alias=True it is a view that the next-but-one call replaces
+        keep = fused(torch.randn(16, 512, generator=g).half().to(dev))
+        saved = keep.clone()
+        for _ in range(3):
+            fused(torch.randn(16, 512, generator=g).half().to(dev))
+        torch.cuda.synchronize()
+        assert torch.equal(keep, saved)
         torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()
