@@ -189,6 +189,22 @@ int kfb_rope_kv_write(const void* qkv, const void* cos_table, const void* sin_ta
 /* out[r, c] = fp16(fp16(silu(gate_up[r, c])) * gate_up[r, inter + c]); gate_up: [rows, 2 * inter]. */
 int kfb_silu_mul(const void* gate_up, void* out, int rows, int inter, void* stream);
 
+/* The fp16 lm_head of a decode step with the greedy argmax fused: y[M, N] = x[M, K] w[N, K]^T, 1 <= M <= 32,
+ * K % 32 == 0, fp16 in, FP32 accumulation, fp16 out; w is streamed once (it is the largest read of a step:
+ * docs/phase5-notes.md:39 of the reference, which runs `h @ lm_head.T` on cuBLAS and a separate argmax,
+ * bench/e2e_model.py:97-141).  best: NULL, or M 64-bit keys that must be 0 before the call; afterwards key m holds
+ * (order-preserving bits of the largest logit of row m) << 32 | (0xFFFFFFFF - its index), lowest index on ties. */
+int kfb_fp16_gemv_argmax(const void* x, const void* w, void* y, void* best, int M, int N, int K, void* stream);
+
+/* End of a decode step: tok[m] (int64) = index held in best[m]; best[m] = 0; kv_len[m] (int32) += 1; pos[0] (int64)
+ * += 1.  One launch in place of argmax + copy + two adds in the reference's step (bench/e2e_model.py:122-131). */
+int kfb_decode_finalize(void* best, void* tok, void* pos, void* kv_len, int M, void* stream);
+
+/* Start of a decode step: x_out[r] = embed[tok[r]] (tok int64, ids clamped to [0, vocab)), y[r] = RMSNorm(x_out[r]) *
+ * weight with the rounding of kfb_add_rmsnorm.  embed: fp16 [vocab, hidden]. */
+int kfb_embed_rmsnorm(const void* tok, const void* embed, const void* weight, void* y, void* x_out, int rows,
+                      int hidden, int vocab, float eps, void* stream);
+
 /* Decode attention (Nq == 1, one query per head at the last cache position) for callers that
  * cannot allocate device memory: a server whose memory pool already owns the whole GPU, code
  * between cudaStreamBeginCapture and EndCapture (cudaMalloc is not allowed there), a host runtime

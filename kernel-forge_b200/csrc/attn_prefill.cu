@@ -25,6 +25,8 @@
 #include "attn.cuh"
 #include "sm100.cuh"
 
+#include <algorithm>
+
 namespace kfb {
 namespace attn {
 namespace {
@@ -81,6 +83,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
+}
+
+// Launch order of the 1-D grid.  (batch, head) pairs are taken in groups of `heads_per_group` whose K/V fit in L2
+// together; inside a group the query tile (or tile pair) index is the slower one and runs from the last tile to the
+// first, so that under a causal mask every long tile of the group starts before any short one, while the CTAs
+// resident at one time still share the K/V of few heads.  (Heaviest-first over ALL heads at once made the resident
+// CTAs stream the K/V of every head at the same time: at N = 8192, D = 128 that is 134 MB, more than L2.)
+struct TileOrder {
+  int q_index, bh;
+};
+__device__ __forceinline__ TileOrder decode_tile_order(unsigned int block, int n_q, int bh_total, int heads_per_group) {
+  const unsigned int per_group = (unsigned int)n_q * (unsigned int)heads_per_group;
+  const int group = (int)(block / per_group);
+  const int base = group * heads_per_group;
+  const int size = min(heads_per_group, bh_total - base);
+  const int r = (int)(block - (unsigned int)group * per_group);
+  return TileOrder{n_q - 1 - r / size, base + r % size};
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -166,7 +185,7 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_prefill_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, void* __restrict__ o_ptr, int H, int Hk, int Nq, int Nk,
-                    int causal, float scale_log2, int B, int n_q_tiles, unsigned int* status) {
+                    int causal, float scale_log2, int B, int n_q_tiles, int heads_per_group, unsigned int* status) {
   using L = Layout<D>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -185,10 +204,9 @@ attn_prefill_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   const AbortCtx ctx{abort_word, status};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, query tile slowest and reversed: under a causal mask every long tile starts before any short one
-  const int q_tile = n_q_tiles - 1 - (int)(blockIdx.x / (unsigned)(H * B));
-  const int bh = (int)(blockIdx.x % (unsigned)(H * B));
-  const int h = bh % H, b = bh / H;
+  const TileOrder ord = decode_tile_order(blockIdx.x, n_q_tiles, H * B, heads_per_group);
+  const int q_tile = ord.q_index;
+  const int h = ord.bh % H, b = ord.bh / H;
   const int hk = h / (H / Hk);
   const int q0 = q_tile * kBlockM;
   const int causal_off = Nk - Nq;
@@ -499,7 +517,7 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, void* __restrict__ o_ptr, int B, int H, int Hk, int Nq,
-                         int Nk, int causal, float scale_log2, int n_pairs, unsigned int* status) {
+                         int Nk, int causal, float scale_log2, int n_pairs, int heads_per_group, unsigned int* status) {
   using L = PairLayout<D>;
   constexpr int S = L::kStages;
   constexpr bool kAliasP = L::kAliasP;
@@ -524,10 +542,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   const AbortCtx ctx{abort_word, status};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, pair index slowest and reversed: under a causal mask every long pair starts before any short one
-  const int pair_idx = n_pairs - 1 - (int)(blockIdx.x / (unsigned)(H * B));
-  const int bh = (int)(blockIdx.x % (unsigned)(H * B));
-  const int h = bh % H, b = bh / H;
+  const TileOrder ord = decode_tile_order(blockIdx.x, n_pairs, H * B, heads_per_group);
+  const int pair_idx = ord.q_index;
+  const int h = ord.bh % H, b = ord.bh / H;
   const int hk = h / (H / Hk);
   const int q0 = pair_idx * 2 * kBlockM;
   const int causal_off = Nk - Nq;
@@ -891,17 +908,20 @@ int launch(const Problem& p, const CUtensorMap& tq, const CUtensorMap& tk, const
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const int q_tiles = ceil_div(p.Nq, kBlockM);
   const long long bh = (long long)p.B * p.H;
+  // heads whose K and V (one KV head each at worst) fit in ~48 MB of L2 together
+  const long long kv_bytes_per_head = 4LL * p.Nk * p.D;
+  const int heads_per_group = (int)std::min<long long>(bh, std::max<long long>(1, (48LL << 20) / kv_bytes_per_head));
   if (pair_kernel_for(D) && q_tiles >= 2) {
     const int n_pairs = ceil_div(q_tiles, 2);
     if (bh * n_pairs > 0x7fffffffLL) return fail(KFB_ERR_INVALID, "too many query tiles for one launch");
     pair::attn_prefill_pair_kernel<D, kBf16><<<(unsigned)(bh * n_pairs), pair::kPairThreads, PL::kAlloc, stream>>>(
-        tq, tk, tv, p.o, p.B, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, n_pairs, status);
+        tq, tk, tv, p.o, p.B, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, n_pairs, heads_per_group, status);
     KFB_LAUNCH_CHECK("attn_prefill_pair_kernel");
     return KFB_OK;
   }
   if (bh * q_tiles > 0x7fffffffLL) return fail(KFB_ERR_INVALID, "too many query tiles for one launch");
   serial::attn_prefill_serial_kernel<D, kBf16><<<(unsigned)(bh * q_tiles), kThreads, L::kAlloc, stream>>>(
-      tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, p.B, q_tiles, status);
+      tq, tk, tv, p.o, p.H, p.Hk, p.Nq, p.Nk, p.causal, scale_log2, p.B, q_tiles, heads_per_group, status);
   KFB_LAUNCH_CHECK("attn_prefill_serial_kernel");
   return KFB_OK;
 }

@@ -44,6 +44,9 @@ _SIGNATURES = {
     "kfb_rope_kv_write": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "kfb_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "kfb_fp16_gemv_argmax": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "kfb_decode_finalize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "kfb_embed_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "kfb_flash_attn_decode_kvlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_float, ctypes.POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
     "kfb_flash_attn_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -11,7 +11,10 @@ Prefill uses torch for everything that is not one of the two hot paths (embeddin
 residual adds, lm_head), as the reference does.  The decode step is launch-bound at batch 1, so there those
 element-wise steps run as three fused kernels (ops.add_rmsnorm, ops.rope_kv_write, ops.silu_mul) and q/k/v and
 gate/up are stored as one quantised matrix each: 11 kernels per layer instead of ~48 (2.39 -> 0.85 ms per step
-on the TinyLlama-1.1B architecture).  Embedding lookup, the fp16 lm_head and argmax stay torch.
+on the TinyLlama-1.1B architecture).  The embedding lookup is fused into the first norm (ops.embed_rmsnorm), the fp16
+lm_head is this library's streaming GEMV with the greedy argmax fused (ops.lm_head_argmax: the lm_head is the largest
+single read of a step), and one kernel publishes the token and advances the device-side counters
+(ops.decode_finalize).
 
 Tensor parallelism (one process per GPU, `group` given): every decoder linear is sharded over its OUTPUT features, so
 no reduction is ever needed.  Rank r owns a block of query heads with their KV heads (a KV head is replicated when
@@ -134,6 +137,7 @@ class LlamaInt4Decoder:
         self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)        # position of the token being fed
         self.kv_len = torch.zeros(batch, dtype=torch.int32, device=self.dev)
         self.step_logits = torch.zeros(batch, s.vocab, dtype=torch.float16, device=self.dev)
+        self.best = torch.zeros(batch, dtype=torch.int64, device=self.dev)   # argmax keys of the step, see ops.lm_head_argmax
         self.graph = None
         # Host mirror of `pos`: the number of cache rows in use.  The step graph reads the position on the device,
         # so the host checks here that a replay can never be asked to write past the cache.
@@ -240,13 +244,18 @@ class LlamaInt4Decoder:
     # ------------------------------------------------------------------ one decode step (graph body)
     @torch.no_grad()
     def _step(self):
-        """One decode step: 11 kernels per layer (norm, qkv, rope + cache write, attention x2, o, add + norm,
-        gate_up, silu * up, down; the last residual add is fused into the next layer's norm)."""
+        """One decode step: 10 or 11 kernels per layer (norm, qkv, rope + cache write, attention (+ merge when the keys
+        are split), o, add + norm, gate_up, silu * up, down; the last residual add is fused into the next layer's
+        norm; the embedding gather is fused into the first norm), then final norm, lm_head with fused argmax, and
+        one kernel that publishes the token and advances position and KV length.  Every kernel of the step is one
+        of this library's: no torch or cuBLAS kernel is left in the graph."""
         s, b = self.s, self.b
-        x = self.embed[self.tok]                                   # [B, hidden]
         res = None                                                 # pending residual branch output
         for li, L in enumerate(self.layers):
-            h, x = ops.add_rmsnorm(x, L["in_norm"], s.rms_eps, res)
+            if li == 0:
+                h, x = ops.embed_rmsnorm(self.tok, self.embed, L["in_norm"], s.rms_eps)   # [B, hidden] each
+            else:
+                h, x = ops.add_rmsnorm(x, L["in_norm"], s.rms_eps, res)
             qkv = L["qkv"](h)
             q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
             a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len)
@@ -256,11 +265,8 @@ class LlamaInt4Decoder:
             act = self._gather(ops.silu_mul(L["gate_up"](h)), "inter_bounds")
             res = self._gather(L["down"](act), "hidden_bounds")
         h, x = ops.add_rmsnorm(x, self.final_norm, s.rms_eps, res)
-        logits = h @ self.lm_head.T
-        self.step_logits.copy_(logits)
-        self.tok.copy_(logits.float().argmax(-1))
-        self.pos.add_(1)
-        self.kv_len.add_(1)
+        ops.lm_head_argmax(h, self.lm_head, self.step_logits, self.best)
+        ops.decode_finalize(self.best, self.tok, self.pos, self.kv_len)
 
     def capture(self):
         """Captures one decode step.  State is saved and restored around the warm-up / capture runs (the warm-up

@@ -366,3 +366,37 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     with _capi.on_device(gate_up.device):
         _capi.check(_capi.lib().kfb_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two // 2, _capi.stream_ptr(gate_up.device)))
     return out
+
+
+def lm_head_argmax(h: torch.Tensor, lm_head: torch.Tensor, logits: torch.Tensor | None = None,
+                   best: torch.Tensor | None = None) -> torch.Tensor:
+    """logits[M, V] = h[M, K] @ lm_head[V, K]^T (fp16, FP32 accumulation) for M <= 32 with the weight streamed once.
+    `best` (int64 CUDA tensor [M], zero before the call) receives the greedy-argmax keys, see kfb_fp16_gemv_argmax;
+    `decode_finalize` turns them into token ids."""
+    m, k = h.shape
+    v = lm_head.shape[0]
+    if logits is None:
+        logits = torch.empty(m, v, dtype=torch.float16, device=h.device)
+    with _capi.on_device(h.device):
+        _capi.check(_capi.lib().kfb_fp16_gemv_argmax(h.data_ptr(), lm_head.data_ptr(), logits.data_ptr(),
+                                                     best.data_ptr() if best is not None else None, m, v, k,
+                                                     _capi.stream_ptr(h.device)))
+    return logits
+
+
+def decode_finalize(best: torch.Tensor, tok: torch.Tensor, pos: torch.Tensor, kv_len: torch.Tensor) -> None:
+    """tok <- argmax indices held in `best`, best <- 0, kv_len += 1, pos += 1 (one launch)."""
+    with _capi.on_device(tok.device):
+        _capi.check(_capi.lib().kfb_decode_finalize(best.data_ptr(), tok.data_ptr(), pos.data_ptr(), kv_len.data_ptr(),
+                                                    tok.numel(), _capi.stream_ptr(tok.device)))
+
+
+def embed_rmsnorm(tok: torch.Tensor, embed: torch.Tensor, weight: torch.Tensor, eps: float):
+    """(y, x): x = embed[tok] (tok int64 [rows]), y = RMSNorm(x) * weight, in one pass."""
+    rows, (vocab, hidden) = tok.numel(), embed.shape
+    y = torch.empty(rows, hidden, dtype=torch.float16, device=embed.device)
+    x = torch.empty_like(y)
+    with _capi.on_device(embed.device):
+        _capi.check(_capi.lib().kfb_embed_rmsnorm(tok.data_ptr(), embed.data_ptr(), weight.data_ptr(), y.data_ptr(), x.data_ptr(),
+                                                  rows, hidden, vocab, eps, _capi.stream_ptr(embed.device)))
+    return y, x

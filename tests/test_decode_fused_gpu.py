@@ -95,3 +95,38 @@ def test_silu_mul(rows, inter):
     out = ops.silu_mul(gu)
     ref = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
     assert (out.float() - ref.float()).abs().max().item() <= 4e-3 * ref.float().abs().max().item()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 32])
+@pytest.mark.parametrize("v,k", [(32000, 2048), (1000, 256), (77, 64)])
+def test_lm_head_gemv_with_fused_argmax(m, v, k):
+    """fp16 lm_head GEMV against an FP32 matmul of the same bits; the fused argmax must equal torch.argmax of the
+    logits the kernel itself produced (ties to the lowest index), and decode_finalize must publish it."""
+    g = torch.Generator().manual_seed(m + v)
+    h = torch.randn(m, k, generator=g).half()
+    w = (torch.randn(v, k, generator=g) * 0.05).half()
+    w[5] = w[3]                                        # two identical rows: equal logits, the tie goes to row 3
+    ref = h.float() @ w.float().T
+    best = torch.zeros(m, dtype=torch.int64, device="cuda")
+    logits = ops.lm_head_argmax(h.cuda(), w.cuda(), None, best)
+    err = (logits.float().cpu() - ref).abs().max().item()
+    floor = (ref.half().float() - ref).abs().max().item()
+    assert err <= 2e-3 * ref.abs().max().item() and err <= 4 * floor + 1e-6
+    tok = torch.zeros(m, dtype=torch.int64, device="cuda")
+    pos = torch.tensor([41], device="cuda")
+    kv_len = torch.full((m,), 42, dtype=torch.int32, device="cuda")
+    ops.decode_finalize(best, tok, pos, kv_len)
+    assert torch.equal(tok.cpu(), logits.float().cpu().argmax(-1))
+    assert int(pos.item()) == 42 and bool((kv_len == 43).all()) and bool((best == 0).all())
+
+
+@pytest.mark.parametrize("rows,hidden,vocab", [(1, 2048, 32000), (32, 2048, 32000), (3, 256, 50)])
+def test_embed_rmsnorm(rows, hidden, vocab):
+    g = torch.Generator().manual_seed(rows + hidden)
+    emb = torch.randn(vocab, hidden, generator=g).half().cuda()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).half().cuda()
+    tok = torch.randint(0, vocab, (rows,), generator=g).cuda()
+    y, x = ops.embed_rmsnorm(tok, emb, w, 1e-5)
+    assert torch.equal(x, emb[tok])
+    y_ref, _ = ops.add_rmsnorm(emb[tok].contiguous(), w, 1e-5)
+    assert torch.equal(y, y_ref)

@@ -70,3 +70,26 @@ def test_rejections():
         ko.quantize_weight(np.zeros((16, 256), np.float32), 32)
     with pytest.raises(ValueError, match=r"\[-8, 7\]"):
         ko.pack_int4(np.full((1, 8), 9, np.int8))
+
+
+def test_torch_restatement_matches_the_same_fixtures():
+    """oracle/kf_oracle_torch.py (the torch-on-CPU form that bench.py times as the CPU baseline) against the fixtures
+    the reference's own code produced: unpack / dequantise bit-exact, linear and attention to FP32 summation order."""
+    import torch
+    from oracle import kf_oracle_torch as kt
+    for path in sorted(glob.glob(str(GOLDEN / "*.npz"))):
+        z = np.load(path)
+        name = path.split("/")[-1]
+        if name.startswith("quant_"):
+            packed, scales = torch.from_numpy(z["packed"]), torch.from_numpy(z["scales"])
+            assert np.array_equal(kt.unpack_int4(packed).numpy(), z["q"]), name
+            assert np.array_equal(kt.dequantize(packed, scales, int(z["group"])).numpy(), z["deq32"]), name
+        elif name.startswith("int4_linear_"):
+            y = kt.int4_linear(torch.from_numpy(z["x"]), torch.from_numpy(z["packed"]), torch.from_numpy(z["scales"]),
+                               int(z["group"])).numpy()
+            assert np.abs(y - z["ref"]).max() <= 2e-5 * np.abs(z["ref"]).max(), name
+        elif name.startswith("attn_"):
+            scale = float(z["scale"]) if "scale" in z.files else None
+            o = kt.attention(torch.from_numpy(z["q"]), torch.from_numpy(z["k"]), torch.from_numpy(z["v"]),
+                             bool(z["causal"]), scale).numpy()
+            assert np.abs(o - z["ref"]).max() <= 2e-6, name
