@@ -701,6 +701,13 @@ def single_kernel_main(args):
         print(json.dumps({"metric": "decode attention HBM GB/s (% peak)", "unit": "GB/s", "value": r["gbs"], "n_gpus": 1,
                           "config": {"workload": f"decode attn Hq=32 Hkv=4 D=64 B={b} Nk={nk}"}, "detail": r,
                           "roofline": roofline("hbm", r["gbs"], peaks, kind)}))
+    elif args.workload == "decode_step":
+        from kernelforge.llama_decode import TINYLLAMA_1B
+        batch = int(args.shape) if args.shape else 1
+        r = bench_decode_e2e(args, device, batch, llama_weights(TINYLLAMA_1B), new_tokens=3 + max(1, args.steps))
+        print(json.dumps({"metric": "decode tok/s", "unit": "tok/s", "value": r["tok_per_s"], "n_gpus": 1,
+                          "config": {"workload": f"greedy decode, TinyLlama-1.1B architecture, batch {batch}, prompt 512"}, "detail": r,
+                          "roofline": roofline("hbm", r["hbm_gbs"], peaks, kind)}))
     else:  # flash_attn_only
         cfg = HEADLINE
         if args.shape:
@@ -724,10 +731,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "int4_gemm", "decode_attn"],
+    ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "int4_gemm", "decode_attn", "decode_step"],
                     help="flash_attn = headline + every other part of the metric under `also`; the others run one kernel only "
                          "(few launches, for profiler captures)")
-    ap.add_argument("--shape", default=None, help="override: B,H,N,D (flash_attn_only) / N,K (int4_gemv) / M,N,K (int4_gemm) / B,NK (decode_attn)")
+    ap.add_argument("--shape", default=None, help="override: B,H,N,D (flash_attn_only) / N,K (int4_gemv) / M,N,K (int4_gemm) / B,NK (decode_attn) / B (decode_step)")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` groups")

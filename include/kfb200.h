@@ -65,6 +65,16 @@ int kfb_device_status_reset(void* stream);
  * reference (csrc/common/check.cuh:11-24 turns CUDA errors into exceptions; it has no in-kernel waits). */
 int kfb_selftest_wait_expiry(unsigned long long timeout_ns, unsigned int* outcome_dev, void* stream);
 
+/* Programmatic dependent launch for every kernel of a decode step (the INT4 GEMVs, decode attention, the fused
+ * element-wise kernels, lm_head, finalize).  When on, launches carry the CUDA attribute that lets a kernel become
+ * resident while the one in front of it in the stream is still running; each kernel waits for that one
+ * (griddepcontrol.wait) before it touches any activation and only then releases its own successor, so results are
+ * those of the plain stream order while launch latency -- and, for the GEMVs and the lm_head, the first round trip
+ * of the weight stream -- is hidden behind the previous kernel.  Works in CUDA-graph capture.  Process-wide switch,
+ * off by default; returns the previous setting.  The reference has no counterpart (its decode step is launch-bound:
+ * docs/phase5-notes.md). */
+int kfb_set_programmatic_launch(int enable);
+
 /* ---------------------------------------------------------------------------------------
  * INT4 weight format (kernelforge/quantize.py).  packed: int32 [N, K/8], nibble position i
  * (bits 4i..4i+3) of word j holds q[8j + (0,2,4,6,1,3,5,7)[i]] + 8; scales: fp16 [N, K/G].
@@ -114,6 +124,18 @@ int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y
  * honoured for M <= 8 only. */
 int kfb_int4_small_batch(const void* x, const void* packed, const void* scales, void* y,
                          int M, int N, int K, int group, int flags, void* stream);
+
+/* int4_gemv for 1 <= M <= 2 with the element-wise neighbours of a decode step fused in (the reference runs each of
+ * them as a separate torch kernel: RMSNorm and SiLU * up in the Hugging Face modules it leaves untouched,
+ * kernelforge/modules.py:51-68; the bias as `y + bias`, kernelforge/ops.py:300-301):
+ *   xform 0: x [M, K] is used as given;
+ *   xform 1: x [M, K] is the residual stream; the product uses fp16(fp16(x * rsqrt(mean(x^2) + eps)) * norm_weight[K]);
+ *   xform 2: x [M, 2 K] is gate | up; the product uses fp16(fp16(silu(gate)) * up)   (K <= 8192 for xform 1, 2);
+ *   then y = fp16(sum), + bias[N] when not NULL, + residual[M, N] when not NULL (fp16 additions, in that order).
+ * Larger M: KFB_ERR_UNSUPPORTED (run the separate kernels).  flags: bit 0 as kfb_int4_gemv. */
+int kfb_int4_gemv_fused(const void* x, const void* packed, const void* scales, void* y,
+                        int M, int N, int K, int group, int xform, const void* norm_weight, float eps,
+                        const void* bias, const void* residual, int flags, void* stream);
 
 /* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
  * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),

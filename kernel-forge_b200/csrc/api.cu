@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -243,6 +244,15 @@ extern "C" int kfb_selftest_wait_expiry(unsigned long long timeout_ns, unsigned 
   KFB_LAUNCH_CHECK("wait_expiry_selftest_kernel");
   return KFB_OK;
 }
+
+namespace kfb {
+namespace {
+std::atomic<int> g_pdl{0};
+}
+bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+}  // namespace kfb
+
+extern "C" int kfb_set_programmatic_launch(int enable) { return kfb::g_pdl.exchange(enable ? 1 : 0); }
 
 extern "C" int kfb_version(void) { return 200; }
 

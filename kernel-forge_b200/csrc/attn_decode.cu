@@ -138,6 +138,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();               // q, the cache rows and kv_len may be the output of the kernel in front
+  pdl_launch_dependents();
   if (*abort_word != 0) return;  // uniform: written before the barrier, nothing has been issued yet
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -327,6 +329,8 @@ __global__ void __launch_bounds__(D)
 attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ o, int H, int Hk, int splits) {
   constexpr int kPer = kRows * (D + 2);
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   const int G = H / Hk;
   const int chunks = (G + kRows - 1) / kRows;
   const int hk = h / G, within = h % G;
@@ -402,13 +406,13 @@ int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const
     configured[dev] = true;
   }
   const dim3 grid(plan.splits, p.Hk * plan.chunks, p.B);
-  kernel<<<grid, kThreads, L::kAlloc, stream>>>(tk, tv, (const uint16_t*)p.q, (uint16_t*)p.o, partial, p.H, p.Hk, p.Nk,
-                                               plan.keys_per_split, p.scale * 1.4426950408889634f, status, p.kv_len_dev);
-  KFB_LAUNCH_CHECK("attn_decode_kernel");
-  if (plan.splits > 1) {
-    attn_decode_merge_kernel<D, kBf16><<<dim3(p.H, p.B), D, 0, stream>>>(partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits);
-    KFB_LAUNCH_CHECK("attn_decode_merge_kernel");
-  }
+  if (int rc = launch_kernel("attn_decode_kernel", kernel, grid, dim3(kThreads), L::kAlloc, stream, pdl_enabled(), tk, tv,
+                             (const uint16_t*)p.q, (uint16_t*)p.o, partial, p.H, p.Hk, p.Nk, plan.keys_per_split,
+                             p.scale * 1.4426950408889634f, status, p.kv_len_dev))
+    return rc;
+  if (plan.splits > 1)
+    return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16>, dim3(p.H, p.B), dim3(D), 0, stream,
+                         pdl_enabled(), (const float*)partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits);
   return KFB_OK;
 }
 

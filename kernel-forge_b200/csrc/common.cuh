@@ -43,6 +43,37 @@ int require_sm100();
                          __FILE__, __LINE__);                                               \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched with the attribute may become resident while the kernel in front
+// of it in the stream is still running; it must call pdl_wait() before it touches anything that kernel wrote (or
+// still reads), and it releases its own successor with pdl_launch_dependents().  Every kernel of this library that
+// can be part of a decode step waits first and releases its successor right after, so at most two grids overlap and
+// the order of all memory operations is that of the plain stream.  Both instructions are no-ops in a kernel that
+// was launched without the attribute.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+// Whether launches carry the attribute (kfb_set_programmatic_launch; off by default).
+bool pdl_enabled();
+
+template <class... KArgs, class... Args>
+int launch_kernel(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) return fail(KFB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  return KFB_OK;
+}
+
 #define KFB_LAUNCH_CHECK(what)                                                              \
   do {                                                                                      \
     cudaError_t _e = cudaGetLastError();                                                    \

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kRmsThreads)
 add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ res, const __half* __restrict__ w,
                    __half* __restrict__ y, __half* __restrict__ sum_out, int hidden, float eps) {
   __shared__ float warp_part[kRmsThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t base = (size_t)blockIdx.x * hidden;
   const int nvec = hidden / 8;
   __half2 vals[kMaxVec][4];
@@ -88,6 +90,8 @@ __global__ void rope_kv_write_kernel(const __half* __restrict__ qkv, const float
                                      __half* __restrict__ q_out, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                      int H, int Hk, int D, int Lmax, unsigned int* status) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x, half = D / 2;
+  pdl_wait();
+  pdl_launch_dependents();
   const long long pos = pos_ptr[0];
   // The position comes from device memory (a graph replay advances it), so it is checked here: a position outside
   // the cache / the rotary tables writes nothing and reads nothing, and leaves a code in the device status word.
@@ -116,6 +120,8 @@ __global__ void rope_kv_write_kernel(const __half* __restrict__ qkv, const float
 // gu: [rows, 2 * inter] (gate | up) -> out [rows, inter]
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int rows, int inter) {
   const int per_row = inter / 2;  // half2 per row
+  pdl_wait();
+  pdl_launch_dependents();
   const long long total = (long long)rows * per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / per_row;
@@ -143,10 +149,9 @@ extern "C" int kfb_add_rmsnorm(const void* x, const void* residual, const void* 
   if (!x || !weight || !y) return fail(KFB_ERR_INVALID, "null pointer");
   if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || (residual && !aligned16(residual)) || (sum_out && !aligned16(sum_out)))
     return fail(KFB_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
-  fused::add_rmsnorm_kernel<<<rows, fused::kRmsThreads, 0, (cudaStream_t)stream>>>(
-      (const __half*)x, (const __half*)residual, (const __half*)weight, (__half*)y, (__half*)sum_out, hidden, eps);
-  KFB_LAUNCH_CHECK("add_rmsnorm_kernel");
-  return KFB_OK;
+  return launch_kernel("add_rmsnorm_kernel", fused::add_rmsnorm_kernel, dim3(rows), dim3(fused::kRmsThreads), 0,
+                       (cudaStream_t)stream, pdl_enabled(), (const __half*)x, (const __half*)residual, (const __half*)weight,
+                       (__half*)y, (__half*)sum_out, hidden, eps);
 }
 
 extern "C" int kfb_rope_kv_write(const void* qkv, const void* cos_table, const void* sin_table, const void* pos_dev,
@@ -158,11 +163,10 @@ extern "C" int kfb_rope_kv_write(const void* qkv, const void* cos_table, const v
   if (!qkv || !cos_table || !sin_table || !pos_dev || !q_out || !k_cache || !v_cache) return fail(KFB_ERR_INVALID, "null pointer");
   unsigned int* status = device_status_word();
   if (!status) return fail(KFB_ERR_CUDA, "cannot resolve the device status word");
-  fused::rope_kv_write_kernel<<<dim3(H + 2 * Hk, B), D / 2, 0, (cudaStream_t)stream>>>(
-      (const __half*)qkv, (const float*)cos_table, (const float*)sin_table, (const long long*)pos_dev, (__half*)q_out,
-      (__half*)k_cache, (__half*)v_cache, H, Hk, D, Lmax, status);
-  KFB_LAUNCH_CHECK("rope_kv_write_kernel");
-  return KFB_OK;
+  return launch_kernel("rope_kv_write_kernel", fused::rope_kv_write_kernel, dim3(H + 2 * Hk, B), dim3(D / 2), 0,
+                       (cudaStream_t)stream, pdl_enabled(), (const __half*)qkv, (const float*)cos_table,
+                       (const float*)sin_table, (const long long*)pos_dev, (__half*)q_out, (__half*)k_cache,
+                       (__half*)v_cache, H, Hk, D, Lmax, status);
 }
 
 extern "C" int kfb_silu_mul(const void* gate_up, void* out, int rows, int inter, void* stream) {
@@ -174,7 +178,6 @@ extern "C" int kfb_silu_mul(const void* gate_up, void* out, int rows, int inter,
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  fused::silu_mul_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)gate_up, (__half*)out, rows, inter);
-  KFB_LAUNCH_CHECK("silu_mul_kernel");
-  return KFB_OK;
+  return launch_kernel("silu_mul_kernel", fused::silu_mul_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream,
+                       pdl_enabled(), (const __half*)gate_up, (__half*)out, rows, inter);
 }

@@ -48,10 +48,6 @@ __device__ __forceinline__ uint4 ldg_cached(const uint4* p) {
   return v;
 }
 
-// Programmatic dependent launch: both are no-ops when the kernel was launched normally.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
@@ -116,14 +112,39 @@ __device__ __forceinline__ void unpack32(const uint4& wv, uint32_t (&q)[16]) {
   unpack8(wv.w, t); q[12] = t[0]; q[13] = t[1]; q[14] = t[2]; q[15] = t[3];
 }
 
-// M: activation rows; R: weight rows per warp; G: group size.
+// What the kernel does to its activations before the product, and to its result after it (decode-step fusions; the
+// reference leaves all of these to separate torch kernels, kernelforge/modules.py:51-68, kernelforge/ops.py:300-301).
+//   kXformNone     x is used as given
+//   kXformRmsNorm  x is the residual stream s; the product uses fp16(fp16(s * rsqrt(mean(s^2) + eps)) * norm_w)
+//   kXformSiluMul  x is [M, 2 K] = gate | up; the product uses fp16(fp16(silu(gate)) * up)
+// Epilogue (any transform): y = fp16(acc), then + bias[n], then + residual[m, n], each an fp16 addition like the
+// separate torch kernels it replaces.
+enum Xform : int { kXformNone = 0, kXformRmsNorm = 1, kXformSiluMul = 2 };
+
+struct Fusion {
+  const __half* norm_w;    // kXformRmsNorm: [K]
+  float eps;
+  const __half* bias;      // [N] or nullptr
+  const __half* residual;  // [M, N] or nullptr
+};
+
+// One rounding of the FP32 sum to fp16, then the optional bias and residual as fp16 additions.
+__device__ __forceinline__ __half finish(float acc, const Fusion& fu, int m, int n, int N) {
+  __half v = __float2half_rn(acc);
+  if (fu.bias) v = __hadd(v, fu.bias[n]);
+  if (fu.residual) v = __hadd(v, fu.residual[(size_t)m * N + n]);
+  return v;
+}
+
+// M: activation rows; R: weight rows per warp; G: group size; XF: the transform above (a transformed x is built once
+// per CTA in shared memory, M * K halfs, and the main loop reads it from there).
 // `ksplit_log2`: 2^ksplit_log2 warps of a CTA share one row tile and split its K chunks.
-template <int M, int R, int G>
+template <int M, int R, int G, int XF = kXformNone>
 __global__ void __launch_bounds__(kThreads)
 int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed, const __half* __restrict__ scales,
-                 __half* __restrict__ y, int N, int K, int ksplit_log2) {
+                 __half* __restrict__ y, int N, int K, int ksplit_log2, const Fusion fu) {
   __shared__ float red[kWarps][M * R];
-  pdl_launch_dependents();
+  extern __shared__ uint4 xs_raw[];   // XF != 0: the transformed activations
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksplit = 1 << ksplit_log2;
@@ -140,88 +161,182 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
 
-  bool waited = false;
-  if (r0 < N) {
-    const uint4* wrow[R];
-    const __half* srow[R];
+  // Weights and scales are constants: the first two chunks of every lane are fetched BEFORE waiting for the kernel in
+  // front (programmatic dependent launch: this grid is already resident while that kernel finishes, so its launch
+  // latency and the first DRAM round trip are hidden); x (and y, in the epilogue) are touched only after the wait.
+  // The dependents of this grid are released right after its own wait has returned, so at most two grids overlap.
+  const uint4* wrow[R];
+  const __half* srow[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int row = min(r0 + r, N - 1);  // rows past N are computed on a clamped row and never stored
-      wrow[r] = packed + (size_t)row * KC;
-      srow[r] = scales + (size_t)row * SG;
+  for (int r = 0; r < R; ++r) {
+    const int row = min(r0 + r, N - 1);  // rows past N are computed on a clamped row and never stored
+    wrow[r] = packed + (size_t)row * KC;
+    srow[r] = scales + (size_t)row * SG;
+  }
+  const int stride = 32 * ksplit;
+  const int c_first = r0 < N ? kpart * 32 + lane : KC;   // a tile past N does nothing
+  uint4 wbuf[2][R];
+  float sbuf[2][R];
+  auto fetch = [&](int slot, int c) {
+    if (c < KC) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) wbuf[slot][r] = ldg_stream(wrow[r] + c);
+#pragma unroll
+      for (int r = 0; r < R; ++r) sbuf[slot][r] = __half2float(srow[r][c / kChunksPerGroup]);
     }
-    for (int c = kpart * 32 + lane; c < KC; c += 32 * ksplit) {
-      uint4 wv[R];
-      float sc[R];
+  };
+  fetch(0, c_first);
+  fetch(1, c_first + stride);
+  if constexpr (XF == kXformNone) pdl_wait();   // (with a transform the wait opens the prologue below)
+  if constexpr (XF != kXformNone) {
+    __half* xs = reinterpret_cast<__half*>(xs_raw);
+    pdl_wait();   // x is the previous kernel's output
+    const int nvec = K / 8;
+    if constexpr (XF == kXformRmsNorm) {
+      __shared__ float part[M][kWarps];
+      constexpr int kMaxVec = 4;   // K <= 256 * 8 * 4
+      uint4 keep[M][kMaxVec];
 #pragma unroll
-      for (int r = 0; r < R; ++r) wv[r] = ldg_stream(wrow[r] + c);
+      for (int m = 0; m < M; ++m) {
+        float ss = 0.f;
 #pragma unroll
-      for (int r = 0; r < R; ++r) sc[r] = __half2float(srow[r][c / kChunksPerGroup]);
-      if (!waited) {  // weights and scales are constants and may be fetched before the
-        pdl_wait();   // previous kernel has finished; x may be its output
-        waited = true;
-      }
-      const uint4* xc = reinterpret_cast<const uint4*>(x) + (size_t)c * 4;
-      if constexpr (M <= 2) {
-        // Decode path.  The kernel is issue-bound, so the nibbles are NOT converted to q: the masked
-        // forms A = 1024 + u (nibble pairs 0, 2) and B = 1024 + 16u (pairs 1, 3) go straight into the
-        // FP32 mixed-precision FMA (products of two 11-bit significands are exact in FP32) and the
-        // offsets are removed per 32-weight chunk with the class sums of x, shared by all R rows:
-        //   sum q x = (sum_A (1024+u) x - 1032 SxA) + (sum_B (1024+16u) x / 16 - 72 SxB).
-        uint4 xv[M][4];
-        unsigned short xl[M][16], xh[M][16];
-        float sxa[M], sxb[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
-          const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) asm("mov.b32 {%0, %1}, %2;" : "=h"(xl[m][i]), "=h"(xh[m][i]) : "r"(xs[i]));
-          float a = 0.f, b = 0.f;
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            a = dot2_acc_split(0x3C003C00u, xl[m][i], xh[m][i], a);      // half2(1, 1)
-            b = dot2_acc_split(0x3C003C00u, xl[m][i + 1], xh[m][i + 1], b);
-          }
-          sxa[m] = a * -1032.0f;
-          sxb[m] = b * -72.0f;
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            float pa = 0.f, pb = 0.f;
+        for (int i = 0; i < kMaxVec; ++i) {
+          const int v = threadIdx.x + i * kThreads;
+          if (v < nvec) {
+            keep[m][i] = reinterpret_cast<const uint4*>(x + (size_t)m * K)[v];
+            const __half2* h = reinterpret_cast<const __half2*>(&keep[m][i]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              constexpr uint32_t kMagic = 0x64006400u;
-              const uint32_t w = wr[j], h = w >> 8;
-              pa = dot2_acc_split((w & 0x000F000Fu) | kMagic, xl[m][4 * j + 0], xh[m][4 * j + 0], pa);
-              pb = dot2_acc_split((w & 0x00F000F0u) | kMagic, xl[m][4 * j + 1], xh[m][4 * j + 1], pb);
-              pa = dot2_acc_split((h & 0x000F000Fu) | kMagic, xl[m][4 * j + 2], xh[m][4 * j + 2], pa);
-              pb = dot2_acc_split((h & 0x00F000F0u) | kMagic, xl[m][4 * j + 3], xh[m][4 * j + 3], pb);
+              const float2 f = __half22float2(h[j]);
+              ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
             }
-            acc[m][r] = fmaf(sc[r], (pa + sxa[m]) + fmaf(pb, 0.0625f, sxb[m]), acc[m][r]);
           }
         }
-      } else {
-        // weights resident (unpacked once), activations streamed per m
-        uint32_t q[R][16];
 #pragma unroll
-        for (int r = 0; r < R; ++r) unpack32(wv[r], q[r]);
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if ((threadIdx.x & 31) == 0) part[m][threadIdx.x >> 5] = ss;
+      }
+      __syncthreads();
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          uint4 xv[4];
+      for (int m = 0; m < M; ++m) {
+        float tot = 0.f;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) xv[j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+        for (int i = 0; i < kWarps; ++i) tot += part[m][i];
+        const float inv = rsqrtf(tot / (float)K + fu.eps);
 #pragma unroll
-          for (int r = 0; r < R; ++r) acc[m][r] = fmaf(sc[r], dot32(q[r], xv), acc[m][r]);
+        for (int i = 0; i < kMaxVec; ++i) {
+          const int v = threadIdx.x + i * kThreads;
+          if (v < nvec) {
+            const uint4 wv = reinterpret_cast<const uint4*>(fu.norm_w)[v];
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+            const __half2* h = reinterpret_cast<const __half2*>(&keep[m][i]);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(h[j]);
+              oh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
+            }
+            reinterpret_cast<uint4*>(xs + (size_t)m * K)[v] = o;
+          }
         }
       }
+    } else {
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+        for (int v = threadIdx.x; v < nvec; v += kThreads) {
+          const uint4 gv = reinterpret_cast<const uint4*>(x + (size_t)m * 2 * K)[v];
+          const uint4 uv = reinterpret_cast<const uint4*>(x + (size_t)m * 2 * K + K)[v];
+          const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+          const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+          uint4 o;
+          __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 gf = __half22float2(gh[j]);
+            oh[j] = __hmul2(__floats2half2_rn(gf.x / (1.0f + __expf(-gf.x)), gf.y / (1.0f + __expf(-gf.y))), uh[j]);
+          }
+          reinterpret_cast<uint4*>(xs + (size_t)m * K)[v] = o;
+        }
+    }
+    __syncthreads();
+  }
+  pdl_launch_dependents();
+
+  auto process = [&](const uint4 (&wv)[R], const float (&sc)[R], int c) {
+      const uint4* xc = reinterpret_cast<const uint4*>(x) + (size_t)c * 4;
+    if constexpr (M <= 2) {
+      // Decode path.  The kernel is issue-bound, so the nibbles are NOT converted to q: the masked
+      // forms A = 1024 + u (nibble pairs 0, 2) and B = 1024 + 16u (pairs 1, 3) go straight into the
+      // FP32 mixed-precision FMA (products of two 11-bit significands are exact in FP32) and the
+      // offsets are removed per 32-weight chunk with the class sums of x, shared by all R rows:
+      //   sum q x = (sum_A (1024+u) x - 1032 SxA) + (sum_B (1024+16u) x / 16 - 72 SxB).
+      uint4 xv[M][4];
+      unsigned short xl[M][16], xh[M][16];
+      float sxa[M], sxb[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (XF != kXformNone) xv[m][j] = xs_raw[(size_t)m * (K / 8) + (size_t)c * 4 + j];
+          else xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+        }
+        const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) asm("mov.b32 {%0, %1}, %2;" : "=h"(xl[m][i]), "=h"(xh[m][i]) : "r"(xs[i]));
+        float a = 0.f, b = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          a = dot2_acc_split(0x3C003C00u, xl[m][i], xh[m][i], a);      // half2(1, 1)
+          b = dot2_acc_split(0x3C003C00u, xl[m][i + 1], xh[m][i + 1], b);
+        }
+        sxa[m] = a * -1032.0f;
+        sxb[m] = b * -72.0f;
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float pa = 0.f, pb = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            constexpr uint32_t kMagic = 0x64006400u;
+            const uint32_t w = wr[j], h = w >> 8;
+            pa = dot2_acc_split((w & 0x000F000Fu) | kMagic, xl[m][4 * j + 0], xh[m][4 * j + 0], pa);
+            pb = dot2_acc_split((w & 0x00F000F0u) | kMagic, xl[m][4 * j + 1], xh[m][4 * j + 1], pb);
+            pa = dot2_acc_split((h & 0x000F000Fu) | kMagic, xl[m][4 * j + 2], xh[m][4 * j + 2], pa);
+            pb = dot2_acc_split((h & 0x00F000F0u) | kMagic, xl[m][4 * j + 3], xh[m][4 * j + 3], pb);
+          }
+          acc[m][r] = fmaf(sc[r], (pa + sxa[m]) + fmaf(pb, 0.0625f, sxb[m]), acc[m][r]);
+        }
+      }
+    } else {
+      // weights resident (unpacked once), activations streamed per m
+      uint32_t q[R][16];
+#pragma unroll
+      for (int r = 0; r < R; ++r) unpack32(wv[r], q[r]);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        uint4 xv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (XF != kXformNone) xv[j] = xs_raw[(size_t)m * (K / 8) + (size_t)c * 4 + j];
+          else xv[j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[m][r] = fmaf(sc[r], dot32(q[r], xv), acc[m][r]);
+      }
+    }
+  };
+  for (int c = c_first; c < KC; c += 2 * stride) {
+    process(wbuf[0], sbuf[0], c);
+    fetch(0, c + 2 * stride);
+    if (c + stride < KC) {
+      process(wbuf[1], sbuf[1], c + stride);
+      fetch(1, c + 3 * stride);
     }
   }
-  if (!waited) pdl_wait();  // y may still be read by the previous kernel
 
 #pragma unroll
   for (int m = 0; m < M; ++m)
@@ -239,7 +354,7 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
       for (int m = 0; m < M; ++m)
 #pragma unroll
         for (int r = 0; r < R; ++r)
-          if (r0 + r < N) y[(size_t)m * N + r0 + r] = __float2half_rn(acc[m][r]);
+          if (r0 + r < N) y[(size_t)m * N + r0 + r] = finish(acc[m][r], fu, m, r0 + r, N);
     }
     return;
   }
@@ -254,33 +369,42 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
     const int m = lane / R, r = lane % R;
     float v = 0.f;
     for (int p = 0; p < ksplit; ++p) v += red[warp + p][lane];  // fixed order
-    if (r0 + r < N) y[(size_t)m * N + r0 + r] = __float2half_rn(v);
+    if (r0 + r < N) y[(size_t)m * N + r0 + r] = finish(v, fu, m, r0 + r, N);
   }
 }
 
-template <int M, int R, int G>
+template <int M, int R, int G, int XF = kXformNone>
 int launch(const void* x, const void* packed, const void* scales, void* y, int N, int K, int ksplit_log2, int flags,
-           cudaStream_t stream) {
+           cudaStream_t stream, const Fusion& fu = Fusion{nullptr, 0.f, nullptr, nullptr}) {
   const int tiles = ceil_div(N, R);
   const int grid = ceil_div(tiles, kWarps >> ksplit_log2);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = XF != kXformNone ? (size_t)M * K * sizeof(__half) : 0;
   cfg.stream = stream;
+  if (cfg.dynamicSmemBytes > 48 * 1024) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    KFB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_kernel<M, R, G, XF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      configured[dev] = true;
+    }
+  }
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (flags & 1) ? 1 : 0;
-  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_gemv_kernel<M, R, G>, (const __half*)x, (const uint4*)packed,
-                                  (const __half*)scales, (__half*)y, N, K, ksplit_log2));
+  cfg.numAttrs = ((flags & 1) || pdl_enabled()) ? 1 : 0;
+  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_gemv_kernel<M, R, G, XF>, (const __half*)x, (const uint4*)packed,
+                                  (const __half*)scales, (__half*)y, N, K, ksplit_log2, fu));
   return KFB_OK;
 }
 
-template <int M, int G>
+template <int M, int G, int XF = kXformNone>
 int pick_rows(const void* x, const void* packed, const void* scales, void* y, int N, int K, int flags,
-              cudaStream_t stream) {
+              cudaStream_t stream, const Fusion& fu = Fusion{nullptr, 0.f, nullptr, nullptr}) {
   // K split inside the CTA: aim at about two 16-byte chunks per lane, never less than one.
   const int KC = K / 32;
   int ksplit_log2 = 0;
@@ -291,13 +415,27 @@ int pick_rows(const void* x, const void* packed, const void* scales, void* y, in
   int R = kMaxR;
   while (R > 1 && ceil_div(ceil_div(N, R), kWarps >> ksplit_log2) < 2 * sms) R >>= 1;
   if constexpr (kMaxR == 8) {
-    if (R == 8) return launch<M, 8, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+    if (R == 8) return launch<M, 8, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
   }
   if constexpr (kMaxR >= 4) {
-    if (R == 4) return launch<M, 4, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+    if (R == 4) return launch<M, 4, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
   }
-  if (R == 2) return launch<M, 2, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
-  return launch<M, 1, G>(x, packed, scales, y, N, K, ksplit_log2, flags, stream);
+  if (R == 2) return launch<M, 2, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+  return launch<M, 1, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+}
+
+// The fused entry: M <= 2 only (the batch sizes at which this kernel is the one the dispatcher uses anyway).
+template <int G>
+int pick_fused(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int xform, int flags,
+               cudaStream_t stream, const Fusion& fu) {
+  if (M == 1) {
+    if (xform == kXformRmsNorm) return pick_rows<1, G, kXformRmsNorm>(x, packed, scales, y, N, K, flags, stream, fu);
+    if (xform == kXformSiluMul) return pick_rows<1, G, kXformSiluMul>(x, packed, scales, y, N, K, flags, stream, fu);
+    return pick_rows<1, G, kXformNone>(x, packed, scales, y, N, K, flags, stream, fu);
+  }
+  if (xform == kXformRmsNorm) return pick_rows<2, G, kXformRmsNorm>(x, packed, scales, y, N, K, flags, stream, fu);
+  if (xform == kXformSiluMul) return pick_rows<2, G, kXformSiluMul>(x, packed, scales, y, N, K, flags, stream, fu);
+  return pick_rows<2, G, kXformNone>(x, packed, scales, y, N, K, flags, stream, fu);
 }
 
 template <int G>
@@ -355,6 +493,27 @@ int gemv_entry(const char* what, int max_m, const void* x, const void* packed, c
 extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
                              int group, int flags, void* stream) {
   return gemv_entry("int4_gemv", 8, x, packed, scales, y, M, N, K, group, flags, stream);
+}
+
+extern "C" int kfb_int4_gemv_fused(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int group,
+                                   int xform, const void* norm_weight, float eps, const void* bias, const void* residual,
+                                   int flags, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (M < 1 || M > 2) return fail(KFB_ERR_UNSUPPORTED, "int4_gemv_fused handles M in [1, 2], got M=%d", M);
+  if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
+  if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
+  if (xform < 0 || xform > 2) return fail(KFB_ERR_INVALID, "unknown activation transform %d", xform);
+  if (xform != gemv::kXformNone && K > 8192) return fail(KFB_ERR_UNSUPPORTED, "fused transforms handle K <= 8192, got %d", K);
+  if (xform == gemv::kXformRmsNorm && !norm_weight) return fail(KFB_ERR_INVALID, "the RMSNorm transform needs its weight");
+  if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(x) || !aligned16(packed) || (norm_weight && !aligned16(norm_weight)))
+    return fail(KFB_ERR_ALIGNMENT, "x, packed and the norm weight must be 16-byte aligned");
+  if (flags & ~1) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
+  const gemv::Fusion fu{static_cast<const __half*>(norm_weight), eps, static_cast<const __half*>(bias),
+                        static_cast<const __half*>(residual)};
+  cudaStream_t s = (cudaStream_t)stream;
+  return group == 128 ? gemv::pick_fused<128>(x, packed, scales, y, M, N, K, xform, flags, s, fu)
+                      : gemv::pick_fused<64>(x, packed, scales, y, M, N, K, xform, flags, s, fu);
 }
 
 extern "C" int kfb_int4_small_batch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,

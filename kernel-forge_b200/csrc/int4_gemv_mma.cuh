@@ -103,11 +103,6 @@ __device__ __forceinline__ uint32_t sub_offset_a(uint32_t a) {
   return d;
 }
 
-// Programmatic dependent launch (no-ops unless the launch carries the attribute): the weight stream of this kernel does
-// not depend on the kernel before it in the stream, only x and y do.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 // Bounded wait for a stage.  Unlike sm100::mbar_wait it sleeps between polls: several chunks are in flight per warp,
 // so a late wake-up costs nothing, while a polling warp would take issue slots and integer-pipe cycles from the warps
 // that have data.
@@ -382,8 +377,8 @@ int4_gemv_mma_split_kernel(const __half* __restrict__ x, const __grid_constant__
 #pragma unroll
   for (int i = 0; i < S; ++i)
     if (i < n_c) issue(i);
-  pdl_launch_dependents();
   pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
+  pdl_launch_dependents();
 
   class_sums<G, NB>(x, M, K, sx);
 
@@ -531,8 +526,8 @@ int4_gemv_mma_stream_kernel(const __half* __restrict__ x, const __grid_constant_
   };
 #pragma unroll
   for (int i = 0; i < S; ++i) issue_next();
-  pdl_launch_dependents();
   pdl_wait();   // the kernel before this one has finished: x may be its output, y may be its input
+  pdl_launch_dependents();
 
   uint4* xs = reinterpret_cast<uint4*>(sx + (size_t)rounds * 8 * NB);   // 16-byte aligned: rounds * 32 NB bytes after sx
   if constexpr (XS) {
@@ -627,7 +622,7 @@ int launch_ex(void (*kernel)(KArgs...), int grid, int threads, size_t smem, cuda
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = (pdl || pdl_enabled()) ? 1 : 0;
   KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
   return KFB_OK;
 }

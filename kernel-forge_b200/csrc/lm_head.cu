@@ -55,7 +55,11 @@ lm_head_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = (blockIdx.x * kWarps + warp) * kRowsPerWarp;
-  if (row0 >= N) return;
+  if (row0 >= N) {
+    pdl_wait();
+    pdl_launch_dependents();
+    return;
+  }
   const int ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);   // rows past N: a valid row, never stored
   const uint4* wa = reinterpret_cast<const uint4*>(w + (size_t)ra * K) + t;
   const uint4* wb = reinterpret_cast<const uint4*>(w + (size_t)rb * K) + t;
@@ -77,6 +81,10 @@ lm_head_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, 
       const int c = min(c0 + u, chunks - 1);
       va[u] = ldg_stream(wa + c * 4);
       vb[u] = ldg_stream(wb + c * 4);
+    }
+    if (c0 == 0) {   // the weights are constants: the first loads are in flight before the wait for the kernel in front
+      pdl_wait();
+      pdl_launch_dependents();
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -128,6 +136,8 @@ lm_head_gemv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, 
 __global__ void decode_finalize_kernel(unsigned long long* __restrict__ best, long long* __restrict__ tok, long long* __restrict__ pos,
                                        int* __restrict__ kv_len, int M) {
   const int m = threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   if (m < M) {
     const unsigned long long key = best[m];
     tok[m] = (long long)(0xFFFFFFFFu - (uint32_t)(key & 0xFFFFFFFFull));
@@ -143,6 +153,8 @@ __global__ void __launch_bounds__(kThreads)
 embed_rmsnorm_kernel(const long long* __restrict__ tok, const __half* __restrict__ embed, const __half* __restrict__ w,
                      __half* __restrict__ y, __half* __restrict__ x_out, int hidden, int vocab, float eps) {
   __shared__ float warp_part[kWarps];
+  pdl_wait();
+  pdl_launch_dependents();
   long long id = tok[blockIdx.x];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // an id outside the table reads a valid row instead of faulting
   const size_t src = (size_t)id * hidden, dst = (size_t)blockIdx.x * hidden;
@@ -209,24 +221,23 @@ extern "C" int kfb_fp16_gemv_argmax(const void* x, const void* w, void* y, void*
   const auto* xp = static_cast<const __half*>(x);
   const auto* wp = static_cast<const __half*>(w);
   auto* yp = static_cast<__half*>(y);
+  const dim3 gd(grid), bd(lmhead::kThreads);
+  const bool pdl = pdl_enabled();
   switch (ceil_div(M, 8)) {
-    case 1: lmhead::lm_head_gemv_kernel<1><<<grid, lmhead::kThreads, 0, s>>>(xp, wp, yp, b, M, N, K); break;
-    case 2: lmhead::lm_head_gemv_kernel<2><<<grid, lmhead::kThreads, 0, s>>>(xp, wp, yp, b, M, N, K); break;
-    case 3: lmhead::lm_head_gemv_kernel<3><<<grid, lmhead::kThreads, 0, s>>>(xp, wp, yp, b, M, N, K); break;
-    default: lmhead::lm_head_gemv_kernel<4><<<grid, lmhead::kThreads, 0, s>>>(xp, wp, yp, b, M, N, K); break;
+    case 1: return launch_kernel("lm_head_gemv_kernel", lmhead::lm_head_gemv_kernel<1>, gd, bd, 0, s, pdl, xp, wp, yp, b, M, N, K);
+    case 2: return launch_kernel("lm_head_gemv_kernel", lmhead::lm_head_gemv_kernel<2>, gd, bd, 0, s, pdl, xp, wp, yp, b, M, N, K);
+    case 3: return launch_kernel("lm_head_gemv_kernel", lmhead::lm_head_gemv_kernel<3>, gd, bd, 0, s, pdl, xp, wp, yp, b, M, N, K);
+    default: return launch_kernel("lm_head_gemv_kernel", lmhead::lm_head_gemv_kernel<4>, gd, bd, 0, s, pdl, xp, wp, yp, b, M, N, K);
   }
-  KFB_LAUNCH_CHECK("lm_head_gemv_kernel");
-  return KFB_OK;
 }
 
 extern "C" int kfb_decode_finalize(void* best, void* tok, void* pos, void* kv_len, int M, void* stream) {
   if (int rc = require_sm100()) return rc;
   if (M < 1 || M > 1024) return fail(KFB_ERR_INVALID, "decode_finalize handles 1..1024 sequences, got %d", M);
   if (!best || !tok || !pos || !kv_len) return fail(KFB_ERR_INVALID, "null pointer");
-  lmhead::decode_finalize_kernel<<<1, ((M + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(
-      static_cast<unsigned long long*>(best), static_cast<long long*>(tok), static_cast<long long*>(pos), static_cast<int*>(kv_len), M);
-  KFB_LAUNCH_CHECK("decode_finalize_kernel");
-  return KFB_OK;
+  return launch_kernel("decode_finalize_kernel", lmhead::decode_finalize_kernel, dim3(1), dim3(((M + 31) / 32) * 32), 0,
+                       (cudaStream_t)stream, pdl_enabled(), static_cast<unsigned long long*>(best), static_cast<long long*>(tok),
+                       static_cast<long long*>(pos), static_cast<int*>(kv_len), M);
 }
 
 extern "C" int kfb_embed_rmsnorm(const void* tok, const void* embed, const void* weight, void* y, void* x_out, int rows,
@@ -238,9 +249,7 @@ extern "C" int kfb_embed_rmsnorm(const void* tok, const void* embed, const void*
   if (!tok || !embed || !weight || !y || !x_out) return fail(KFB_ERR_INVALID, "null pointer");
   if (!aligned16(embed) || !aligned16(weight) || !aligned16(y) || !aligned16(x_out))
     return fail(KFB_ERR_ALIGNMENT, "pointers must be 16-byte aligned");
-  lmhead::embed_rmsnorm_kernel<<<rows, lmhead::kThreads, 0, (cudaStream_t)stream>>>(
-      static_cast<const long long*>(tok), static_cast<const __half*>(embed), static_cast<const __half*>(weight),
-      static_cast<__half*>(y), static_cast<__half*>(x_out), hidden, vocab, eps);
-  KFB_LAUNCH_CHECK("embed_rmsnorm_kernel");
-  return KFB_OK;
+  return launch_kernel("embed_rmsnorm_kernel", lmhead::embed_rmsnorm_kernel, dim3(rows), dim3(lmhead::kThreads), 0,
+                       (cudaStream_t)stream, pdl_enabled(), static_cast<const long long*>(tok), static_cast<const __half*>(embed),
+                       static_cast<const __half*>(weight), static_cast<__half*>(y), static_cast<__half*>(x_out), hidden, vocab, eps);
 }

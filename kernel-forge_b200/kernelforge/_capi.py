@@ -25,12 +25,15 @@ _SIGNATURES = {
     "kfb_last_error": (c_char_p, []),
     "kfb_device_status": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "kfb_device_status_reset": (c_int, [c_void_p]),
+    "kfb_set_programmatic_launch": (c_int, [c_int]),
     "kfb_selftest_wait_expiry": (c_int, [ctypes.c_ulonglong, c_void_p, c_void_p]),
     "kfb_quantize_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "kfb_unpack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "kfb_pack_int4": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "kfb_dequantize": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "kfb_int4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "kfb_int4_gemv_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+                                    c_void_p, c_void_p, c_int, c_void_p]),
     "kfb_int4_small_batch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "kfb_int4_gemm_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "kfb_int4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
@@ -114,6 +117,22 @@ def raise_on_device_status(device: torch.device) -> None:
         raise DeviceStatusError(
             f"kfb200 device status 0x{code:x} on {device}: a kernel gave up a bounded wait or rejected a device-side "
             "argument; results enqueued since then are not valid (see kfb_device_status_reset in include/kfb200.h)")
+
+
+class programmatic_launch:
+    """Context manager: the kernels launched inside carry the programmatic-dependent-launch attribute
+    (kfb_set_programmatic_launch).  Process-wide; restores the previous setting on exit."""
+
+    def __init__(self, enable: bool = True):
+        self.enable, self.prev = enable, 0
+
+    def __enter__(self):
+        self.prev = lib().kfb_set_programmatic_launch(1 if self.enable else 0)
+        return self
+
+    def __exit__(self, *exc):
+        lib().kfb_set_programmatic_launch(self.prev)
+        return False
 
 
 def dtype_code(dtype: torch.dtype) -> int:

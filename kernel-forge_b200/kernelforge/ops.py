@@ -100,6 +100,33 @@ def int4_gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group
     return _gemv_launch(x, packed, scales, int(group_size))
 
 
+FUSED_GEMV_MAX_M = 2
+XFORM_NONE, XFORM_RMSNORM, XFORM_SILU_MUL = 0, 1, 2
+
+
+def int4_gemv_fused(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128, xform: int = XFORM_NONE,
+                    norm_weight: torch.Tensor | None = None, eps: float = 0.0, bias: torch.Tensor | None = None,
+                    residual: torch.Tensor | None = None) -> torch.Tensor:
+    """INT4 GEMV for M <= 2 with a decode step's element-wise neighbours fused in (see kfb_int4_gemv_fused):
+    xform = XFORM_RMSNORM applies RMSNorm(x) * norm_weight first, XFORM_SILU_MUL takes x = [M, 2K] (gate | up) and
+    multiplies silu(gate) * up first; bias [N] and residual [M, N] are added to the fp16 result."""
+    m = x.shape[0]
+    k = x.shape[1] // 2 if xform == XFORM_SILU_MUL else x.shape[1]
+    n = packed.shape[0]
+    if m > FUSED_GEMV_MAX_M:
+        raise ValueError(f"int4_gemv_fused handles M in [1, {FUSED_GEMV_MAX_M}], got M={m}")
+    if packed.shape[1] * 8 != k:
+        raise ValueError(f"packed has K/8={packed.shape[1]} columns but the activations have K={k}")
+    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_fused(
+            x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(), m, n, k, int(group_size), int(xform),
+            norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+            bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None,
+            0, _capi.stream_ptr(x.device)))
+    return y
+
+
 def int4_small_batch(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
     """The GEMV's weight-streaming kernel for M in [1, SMALL_BATCH_MAX_M]: every block of 8 batch rows is one more
     MMA on the already unpacked weight fragment.  Not in the reference (its GEMV stops at M = 8)."""
@@ -320,6 +347,10 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
         x2 = x2.contiguous()
     _check_int4(x2, packed, scales, group_size)
     if _plain_eager(x2):
+        if bias is not None and x2.shape[0] <= FUSED_GEMV_MAX_M and bias.dtype == torch.float16 and bias.is_contiguous():
+            # decode-sized call: the bias goes into the GEMV epilogue (same two roundings as `y + bias`)
+            _check_int4_storage(x2, packed, scales, group_size)
+            return int4_gemv_fused(x2, packed, scales, int(group_size), bias=bias).reshape(*lead, packed.shape[0])
         y = int4_matmul(x2, packed, scales, int(group_size))
     else:
         y = _int4_matmul_op(x2, packed, scales, int(group_size))

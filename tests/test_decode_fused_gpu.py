@@ -130,3 +130,52 @@ def test_embed_rmsnorm(rows, hidden, vocab):
     assert torch.equal(x, emb[tok])
     y_ref, _ = ops.add_rmsnorm(emb[tok].contiguous(), w, 1e-5)
     assert torch.equal(y, y_ref)
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("n,k", [(2560, 2048), (2048, 5632), (11264, 2048), (100, 256)])
+def test_int4_gemv_fused_matches_the_separate_kernels(m, n, k):
+    """ops.int4_gemv_fused against the sequence of separate kernels it replaces (same roundings): bias + residual
+    epilogue and the SiLU * up prologue bit for bit; the RMSNorm prologue up to the summation order of mean(x^2)."""
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(n + k + m)
+    qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).cuda(), 128)
+    x = torch.randn(m, k, generator=g).half().cuda()
+    bias = torch.randn(n, generator=g).half().cuda()
+    res = torch.randn(m, n, generator=g).half().cuda()
+    def cuda_core_gemv(xx):   # the same kernel family as the fused entry (flag bit 1), so results can be compared bit for bit
+        from kernelforge import _capi
+        y = torch.empty(xx.shape[0], n, dtype=torch.float16, device="cuda")
+        _capi.check(_capi.lib().kfb_int4_gemv(xx.data_ptr(), qw.packed.data_ptr(), qw.scales.data_ptr(), y.data_ptr(),
+                                              xx.shape[0], n, k, 128, 2, _capi.stream_ptr(torch.device("cuda", 0))))
+        return y
+
+    plain = cuda_core_gemv(x)
+    fused = ops.int4_gemv_fused(x, qw.packed, qw.scales, 128, bias=bias, residual=res)
+    assert torch.equal(fused, (plain + bias) + res)
+    assert torch.equal(ops.int4_gemv_fused(x, qw.packed, qw.scales, 128), plain)
+    # SiLU * up prologue
+    gu = torch.randn(m, 2 * k, generator=g).half().cuda()
+    want = cuda_core_gemv(ops.silu_mul(gu)) + res
+    got = ops.int4_gemv_fused(gu, qw.packed, qw.scales, 128, ops.XFORM_SILU_MUL, residual=res)
+    assert torch.equal(got, want)
+    # RMSNorm prologue
+    w = (1 + 0.1 * torch.randn(k, generator=g)).half().cuda()
+    normed, _ = ops.add_rmsnorm(x, w, 1e-5)
+    want = cuda_core_gemv(normed)
+    got = ops.int4_gemv_fused(x, qw.packed, qw.scales, 128, ops.XFORM_RMSNORM, w, 1e-5)
+    assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
+
+
+def test_int4_linear_bias_goes_through_the_fused_epilogue():
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(3)
+    qw = kq.quantize_weight((torch.randn(1536, 1536, generator=g) * 0.02).cuda(), 128)
+    bias = torch.randn(1536, generator=g).half().cuda()
+    for m in (1, 2, 5):
+        x = torch.randn(m, 1536, generator=g).half().cuda()
+        got, want = ops.int4_linear(x, qw.packed, qw.scales, 128, bias), ops.int4_linear(x, qw.packed, qw.scales, 128) + bias
+        if m == 2:   # without a bias M = 2 runs on the mma kernel: same sums, another order
+            assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
+        else:
+            assert torch.equal(got, want)
