@@ -554,19 +554,31 @@ def bench_sharded_linear(args, world, device, m=128, n=8960, k=1536, group=128) 
     qw = kq.quantize_weight((torch.randn(n, k, generator=g) * 0.02).to(device), group)
     lin = kp.ShardedInt4Linear.from_full(qw)
     x = torch.randn(m, k, generator=g).half().to(device)
-    steps = max(20, args.steps)
-    r = time_blocks(lambda i: lin(x), steps, args.warmup, world, min_blocks=5, min_seconds=0.05, graph=False)
-    us = 1e3 * r["block_ms"] / steps
-    out = {"us_per_call": us, "tflops": 2.0 * m * n * k / (us * 1e-6) / 1e12, "rows_per_rank": n // world,
-           "collective": "nccl all_gather_into_tensor"}
-    try:
-        fused = kp.FusedShardedInt4Linear.from_full(qw, max_m=m, alias=True)
-        r = time_blocks(lambda i: fused(x), steps, args.warmup, world, min_blocks=5, min_seconds=0.05, graph=False)
-        us_f = 1e3 * r["block_ms"] / steps
-        out["fused_peer_store"] = {"us_per_call": us_f, "tflops": 2.0 * m * n * k / (us_f * 1e-6) / 1e12,
-                                   "how": "GEMM epilogue stores its tile into every rank's symmetric buffer"}
-    except Exception as exc:  # report, never hide
-        out["fused_peer_store"] = {"error": repr(exc)[:300]}
+    steps = 2 * max(10, args.steps // 2)   # even: the fused path alternates two result buffers
+    keep = []
+
+    def run(mod):
+        def step(i):
+            keep.append(mod(x))
+            if len(keep) > 4:
+                keep.pop(0)
+        return step
+
+    out = {"rows_per_rank": n // world}
+    for name, build, how in (
+            ("nccl_all_gather", lambda: lin, "local GEMM + nccl all_gather_into_tensor"),
+            ("fused_peer_store", lambda: kp.FusedShardedInt4Linear.from_full(qw, max_m=m, alias=True),
+             "GEMM epilogue stores its tile into every rank's symmetric buffer; device-side rendezvous (no NCCL kernel)")):
+        try:
+            mod = build()
+            rec = {"how": how}
+            for mode, graph in (("eager", False), ("graph", True)):
+                r = time_blocks(run(mod), steps, args.warmup, world, min_blocks=5, min_seconds=0.05, graph=graph)
+                us = 1e3 * r["block_ms"] / steps
+                rec[mode] = {"us_per_call": us, "tflops": 2.0 * m * n * k / (us * 1e-6) / 1e12}
+            out[name] = rec
+        except Exception as exc:  # report, never hide
+            out[name] = {"error": repr(exc)[:300]}
     return out
 
 

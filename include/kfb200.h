@@ -152,12 +152,32 @@ int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y
  * stores that block into ALL n_buffers output buffers (y_all[i]: fp16 [M, ld], the peer-mapped address of
  * GPU i's full result, this GPU's own buffer included) with plain peer stores over NVLink, tile by tile
  * as the tiles finish, so no separate all-gather kernel runs.  Stores only: nothing is loaded from a
- * peer.  The caller orders the call against the peers (a barrier on the stream after the call, before
- * anyone reads y; and no peer may still be reading a buffer that this call overwrites).
+ * peer.  The caller orders the call against the peers (kfb_peer_signal_wait on the stream after the call, before
+ * anyone reads y; and no peer may still be reading a buffer that this call overwrites: alternate two buffers).
  * Workspace: kfb_int4_gemm_ws_bytes(M, N_local, K, group). */
 int kfb_int4_gemm_allgather(const void* x, const void* packed, const void* scales, void* const* y_all,
                             int n_buffers, int M, int N_local, int K, int group, int ld, int col0,
                             void* ws, size_t ws_bytes, void* stream);
+
+/* Device-side rendezvous of the ranks of one node, enqueued on the stream (no host synchronisation, CUDA-graph
+ * capturable): adds 1 to the arrival counter of every rank (peer_counters[i] = peer-mapped address of rank i's counter,
+ * this rank's own included) after a system-scope fence -- so everything this stream stored into peer memory before,
+ * e.g. by kfb_int4_gemm_allgather, is visible to a rank that sees the arrival -- and then waits until this rank's own
+ * counter has received n_ranks more arrivals than the target recorded in *local_target (device uint64, advanced by
+ * the kernel).  The wait is bounded: after timeout_ns (1 us .. 10 s) the kernel records 0x801 in the device status
+ * word and returns.  Counters are uint64, zero-initialised, in memory every rank can address (symmetric memory);
+ * only stores and atomic adds cross the link.  No counterpart in the reference (single GPU). */
+int kfb_peer_signal_wait(void* const* peer_counters, int n_ranks, const void* local_counter, void* local_target,
+                         unsigned long long timeout_ns, void* stream);
+
+/* All-gather of column blocks over peer memory in one launch: src [M, w_local] fp16 (dense rows) is stored into columns
+ * [col0, col0 + w_local) of every rank's [M, ld] fp16 buffer dst_all[i], then the ranks rendezvous as in
+ * kfb_peer_signal_wait (every rank launches the same number of CTAs, each signals once).  When the call returns on the
+ * stream, every rank's block has arrived in this rank's buffer.  A buffer may be overwritten by the call after the
+ * next one at the earliest (alternate two buffers, each with its own counter and target). */
+int kfb_peer_allgather(const void* src, void* const* dst_all, void* const* peer_counters, int n_ranks, int M,
+                       int w_local, int ld, int col0, const void* local_counter, void* local_target,
+                       unsigned long long timeout_ns, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused attention forward  O = softmax(scale * Q K^T + causal mask) V

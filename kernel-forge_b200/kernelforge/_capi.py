@@ -40,6 +40,9 @@ _SIGNATURES = {
                               c_void_p]),
     "kfb_int4_gemm_allgather": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "kfb_peer_signal_wait": (c_int, [ctypes.POINTER(c_void_p), c_int, c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p]),
+    "kfb_peer_allgather": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p]),
     "kfb_flash_attn_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "kfb_flash_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_float, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),

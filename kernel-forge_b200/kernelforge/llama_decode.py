@@ -92,11 +92,12 @@ class LlamaInt4Decoder:
     """fp16 activations, INT4 g128 decoder linears, fused attention, static KV cache."""
 
     def __init__(self, shape: LlamaShape, weights: dict, device, batch: int, max_len: int, group: int = 128, tp_group=None,
-                 programmatic_launch: bool = True):
+                 programmatic_launch: bool = True, peer_gather: bool = True):
         self.s, self.dev, self.b, self.max_len = shape, torch.device(device), batch, max_len
         # decode steps are launched with programmatic dependent launch (every kernel of the step waits for its
-        # predecessor before touching activations); not with tensor parallelism, whose NCCL kernels sit in between
-        self.pdl = programmatic_launch and tp_group is None
+        # predecessor before touching activations); with tensor parallelism only when the gathers are this library's
+        # peer-memory kernels too (NCCL kernels in between know nothing of the protocol)
+        self.pdl = programmatic_launch and (tp_group is None or peer_gather)
         # The 6-kernels-per-layer step (_step_fused, batch <= 2) is available but not the default: with programmatic
         # dependent launch the separate small kernels hide their launch behind their predecessor, while a fused prologue
         # (norm / SiLU over the whole row, two block barriers) sits on every GEMV's critical path.  Measured, ms per
@@ -110,6 +111,11 @@ class LlamaInt4Decoder:
             import torch.distributed as dist
             self.world, self.rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
         self.plan = tp_plan(s, self.rank, self.world) if self.world > 1 else None
+        self._xchg = None
+        if self.plan is not None and peer_gather:
+            from .parallel import PeerExchange
+            widest = max(s.hidden, s.intermediate, s.heads * s.head_dim)
+            self._xchg = PeerExchange(batch, widest, tp_group, self.dev)   # 4 gathers per layer: an even number per step
         # local sizes (the whole model when not tensor-parallel)
         self.h_loc = s.heads if self.plan is None else self.plan["q_heads"][1] - self.plan["q_heads"][0]
         self.hk_loc = s.kv_heads if self.plan is None else self.plan["kv_heads"][1] - self.plan["kv_heads"][0]
@@ -155,9 +161,14 @@ class LlamaInt4Decoder:
 
     # ------------------------------------------------------------------ construction helpers
     def _gather(self, y_local: torch.Tensor, bounds_key: str) -> torch.Tensor:
-        """All-gather of the ranks' column blocks ([rows, n_local] -> [rows, n]); the identity without tensor parallelism."""
+        """All-gather of the ranks' column blocks ([rows, n_local] -> [rows, n]); the identity without tensor parallelism.
+        Decode-sized blocks go over peer memory (parallel.PeerExchange: one launch of this library's kernel per gather,
+        no NCCL kernel in the step graph); larger ones (prefill) through NCCL."""
         if self.plan is None:
             return y_local
+        rows = y_local.shape[0]
+        if self._xchg is not None and rows <= self.b:
+            return self._xchg.allgather_columns(y_local, self.plan[bounds_key])
         from .parallel import gather_columns
         return gather_columns(y_local, self.plan[bounds_key], self.tp_group)
 

@@ -126,16 +126,98 @@ def gather_columns(y_local: torch.Tensor, bounds: list[tuple[int, int]], group=N
     return torch.cat([recv[r, :, :w] for r, w in enumerate(widths)], dim=1)
 
 
+def expected_arrivals(world: int, ctas_per_rank: int = 1) -> int:
+    """Arrivals one rank receives per device-side rendezvous: every rank signals once per signalling CTA."""
+    return world * ctas_per_rank
+
+
+class PeerExchange:
+    """Symmetric-memory buffers and arrival counters for device-side exchanges between the ranks of a group
+    (kfb_peer_signal_wait / kfb_peer_allgather: plain peer stores and system-scope atomic adds over NVLink, a bounded
+    wait, no NCCL kernel and no host synchronisation, so the calls can sit inside a captured CUDA graph).
+
+    Two result buffers alternate.  A rank that runs ahead cannot overwrite a result a slower peer is still reading:
+    before it may store into a buffer again it must have passed the rendezvous of the call in between, which needs that
+    peer's arrival, which the peer sends only after -- in its own stream order -- the consumers of its earlier result
+    were enqueued ahead of its next call.  A graph that is replayed must therefore hold an EVEN number of calls.
+    """
+
+    def __init__(self, rows: int, cols: int, group: dist.ProcessGroup | None = None, device=None, timeout_s: float = 2.0):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.rows, self.cols = rows, cols
+        self.timeout_ns = int(timeout_s * 1e9)
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        data_elems = 2 * rows * cols
+        pad = (-data_elems) % 8
+        # one symmetric allocation: two fp16 result buffers, then two uint64 arrival counters (as four fp16 each)
+        self._mem = symm.empty(data_elems + pad + 8, dtype=torch.float16, device=dev)
+        self._mem.zero_()
+        hdl = symm.rendezvous(self._mem, self.group.group_name)
+        base = [int(p) for p in hdl.buffer_ptrs]
+        self._data_ptrs = [[b + t * rows * cols * 2 for b in base] for t in range(2)]
+        self._counter_ptrs = [[b + (data_elems + pad) * 2 + t * 8 for b in base] for t in range(2)]
+        self._targets = torch.zeros(2, dtype=torch.int64, device=dev)   # advanced by the kernels
+        self._turn = 0
+        self.calls = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)   # every rank has zeroed its counters before anyone signals
+
+    def buffer(self, turn: int, m: int, n: int) -> torch.Tensor:
+        """The local result buffer of `turn` viewed as [m, n] (a view of the symmetric allocation)."""
+        return self._mem[turn * self.rows * self.cols: turn * self.rows * self.cols + m * n].view(m, n)
+
+    def next_turn(self) -> int:
+        turn = self._turn
+        self._turn ^= 1
+        self.calls += 1
+        return turn
+
+    def _ptr_array(self, ptrs):
+        import ctypes
+        return (ctypes.c_void_p * self.world)(*ptrs)
+
+    def signal_wait(self, turn: int) -> None:
+        """Rendezvous on the current stream: everything this stream stored into the peers is visible to a rank once it
+        has seen the arrival; returns (on the stream) when every rank has arrived."""
+        from . import _capi
+        with _capi.on_device(self.dev):
+            _capi.check(_capi.lib().kfb_peer_signal_wait(self._ptr_array(self._counter_ptrs[turn]), self.world,
+                                                         self._counter_ptrs[turn][self.rank], self._targets[turn:].data_ptr(),
+                                                         self.timeout_ns, _capi.stream_ptr(self.dev)))
+
+    def allgather_columns(self, y_local: torch.Tensor, bounds: list[tuple[int, int]]) -> torch.Tensor:
+        """All-gather of column blocks: returns the full [M, N] as a view of this rank's buffer (valid until the call after
+        the next one)."""
+        from . import _capi
+        m, w = y_local.shape
+        n = bounds[-1][1]
+        lo, hi = bounds[self.rank]
+        if hi - lo != w or m * n > self.rows * self.cols:
+            raise ValueError(f"block {tuple(y_local.shape)} does not match columns [{lo}, {hi}) or exceeds the buffer")
+        if y_local.dtype != torch.float16 or not y_local.is_contiguous():
+            y_local = y_local.to(torch.float16).contiguous()
+        turn = self.next_turn()
+        with _capi.on_device(self.dev):
+            _capi.check(_capi.lib().kfb_peer_allgather(y_local.data_ptr(), self._ptr_array(self._data_ptrs[turn]),
+                                                       self._ptr_array(self._counter_ptrs[turn]), self.world, m, w, n, lo,
+                                                       self._counter_ptrs[turn][self.rank], self._targets[turn:].data_ptr(),
+                                                       self.timeout_ns, _capi.stream_ptr(self.dev)))
+        return self.buffer(turn, m, n)
+
+
 class FusedShardedInt4Linear(torch.nn.Module):
     """Output-feature-parallel INT4 linear whose all-gather is fused into the GEMM epilogue.
 
-    Every rank owns two result buffers [max_m, N] in symmetric memory (torch.distributed._symmetric_memory:
-    each buffer is mapped into every process of the group).  `kfb_int4_gemm_allgather` stores this rank's
-    column block into the current buffer of EVERY rank with plain peer stores over NVLink while the tiles are
-    still being produced; one tiny all-reduce on the stream then orders the ranks (when it has passed, every
-    rank's kernel -- and with it every store into this rank's buffer -- has completed).  The two buffers
-    alternate, so a rank that runs ahead never overwrites a result a slower peer is still reading (it cannot
-    get two calls ahead: its next all-reduce needs the peer).  Only stores cross the link, never loads.
+    Every rank owns two result buffers [max_m, N] in symmetric memory (torch.distributed._symmetric_memory: each
+    buffer is mapped into every process of the group).  `kfb_int4_gemm_allgather` stores this rank's column block into
+    the current buffer of EVERY rank with plain peer stores over NVLink while the tiles are still being produced; a
+    device-side rendezvous on the stream (PeerExchange.signal_wait: arrival counters in peer memory, bounded wait)
+    then orders the ranks -- when it has passed, every rank's kernel, and with it every store into this rank's buffer,
+    has completed.  No NCCL kernel and no host synchronisation are involved, so the call can be captured in a CUDA
+    graph.  Only stores and atomic adds cross the link, never loads.
 
     Lifetime of the result: by default forward() returns a private copy.  With `alias=True` it returns a view of
     the symmetric buffer itself (no copy): that view is valid only until the next-but-one forward() of this
@@ -147,7 +229,6 @@ class FusedShardedInt4Linear(torch.nn.Module):
     def __init__(self, qw_full_shape: tuple[int, int], local: kq.QuantizedWeight, max_m: int,
                  bias: torch.Tensor | None = None, group: dist.ProcessGroup | None = None, alias: bool = False):
         super().__init__()
-        import torch.distributed._symmetric_memory as symm
         self.alias = alias
         self.out_features, self.in_features = qw_full_shape
         self.group_size = local.group_size
@@ -159,14 +240,13 @@ class FusedShardedInt4Linear(torch.nn.Module):
         self.register_buffer("scales", local.scales)
         self.register_buffer("bias", None if bias is None else bias.detach().half())
         dev = local.packed.device
-        self._bufs, self._ptrs = [], []
-        for _ in range(2):
-            t = symm.empty(max_m, self.out_features, dtype=torch.float16, device=dev)
-            hdl = symm.rendezvous(t, self.group.group_name)
-            self._bufs.append(t)
-            self._ptrs.append([int(p) for p in hdl.buffer_ptrs])
-        self._flag = torch.zeros(1, dtype=torch.float32, device=dev)
-        self._turn = 0
+        self._xchg = PeerExchange(max_m, self.out_features, self.group, dev)
+        from . import _capi
+        lo, hi = self.bounds[self.rank]
+        # split-K workspace for the largest call, allocated once
+        ws_bytes = max(_capi.lib().kfb_int4_gemm_ws_bytes(m, hi - lo, self.in_features, self.group_size)
+                       for m in {1, 16, 32, 64, 128, 256, max_m} if m <= max_m)
+        self._ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
 
     @classmethod
     def from_full(cls, qw: kq.QuantizedWeight, max_m: int, bias=None, group=None, alias: bool = False) -> "FusedShardedInt4Linear":
@@ -183,18 +263,18 @@ class FusedShardedInt4Linear(torch.nn.Module):
             raise ValueError(f"M={m} exceeds the symmetric buffers (max_m={self.max_m})")
         ops._check_int4(x2, self.packed, self.scales, self.group_size)
         lo, hi = self.bounds[self.rank]
-        turn = self._turn
-        self._turn ^= 1
+        turn = self._xchg.next_turn()
         lib = _capi.lib()
         ws_bytes = lib.kfb_int4_gemm_ws_bytes(m, hi - lo, k, self.group_size)
-        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x2.device)
-        ptrs = (ctypes.c_void_p * self.world)(*self._ptrs[turn])
+        if ws_bytes > self._ws.numel():
+            self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x2.device)
+        ptrs = (ctypes.c_void_p * self.world)(*self._xchg._data_ptrs[turn])
         with _capi.on_device(x2.device):
             _capi.check(lib.kfb_int4_gemm_allgather(x2.data_ptr(), self.packed.data_ptr(), self.scales.data_ptr(), ptrs,
                                                     self.world, m, hi - lo, k, self.group_size, self.out_features, lo,
-                                                    ws.data_ptr(), ws_bytes, _capi.stream_ptr(x2.device)))
-        dist.all_reduce(self._flag, group=self.group)  # stream-ordered rendezvous: every rank's stores have landed
-        y = self._bufs[turn][:m]
+                                                    self._ws.data_ptr(), ws_bytes, _capi.stream_ptr(x2.device)))
+        self._xchg.signal_wait(turn)   # device-side rendezvous: every rank's stores have landed
+        y = self._xchg.buffer(turn, m, self.out_features)
         if self.bias is not None:
             y = y + self.bias          # a new tensor already
         elif not self.alias:

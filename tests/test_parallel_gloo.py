@@ -95,3 +95,59 @@ def test_tensor_parallel_plan_partitions_heads_rows_and_features():
     import pytest
     with pytest.raises(ValueError, match="cannot split"):
         tp_plan(LlamaShape(heads=12, kv_heads=4), 0, 8)
+
+
+class _HostPeerModel:
+    """Host-side model of the device rendezvous protocol (kfb_peer_signal_wait / kfb_peer_allgather): per turn one arrival
+    counter per rank and one target per rank; a rank signals every peer (gloo all-reduce of its increments stands in
+    for the atomic adds over NVLink), then polls its own counter with a time limit.  Mirrors parallel.PeerExchange:
+    alternating turns, target += expected_arrivals(world, ctas)."""
+
+    def __init__(self, world, rank, ctas=1):
+        from kernelforge import parallel as kp
+        self.world, self.rank, self.inc = world, rank, kp.expected_arrivals(world, ctas)
+        self.ctas = ctas
+        self.counter = [0, 0]
+        self.target = [0, 0]
+        self.turn = 0
+        self.status = 0
+
+    def call(self, drop_signal_from=None):
+        turn, self.turn = self.turn, self.turn ^ 1
+        sent = torch.zeros(self.world, dtype=torch.int64)            # arrivals this rank adds to each peer's counter
+        if drop_signal_from != self.rank:
+            sent += self.ctas
+        dist.all_reduce(sent)                                        # sent[r] = what rank r receives in total
+        self.counter[turn] += int(sent[self.rank])
+        self.target[turn] += self.inc
+        if self.counter[turn] < self.target[turn]:                   # the bounded wait ran out
+            self.status = self.status or 0x801
+            return False
+        return True
+
+
+def _peer_protocol_worker(rank, world, port):
+    for p in (str(ROOT), str(ROOT / "kernel-forge_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        for ctas in (1, 8):
+            m = _HostPeerModel(world, rank, ctas)
+            for _ in range(6):                                       # both buffers, several rounds: targets stay in step
+                assert m.call()
+            assert m.counter == m.target == [3 * world * ctas, 3 * world * ctas] and m.status == 0
+            # a rank that never signals: every rank's wait for that call gives up and the status code is recorded,
+            # nothing waits forever; the shortfall is permanent for that turn (the host must reset), the other turn is fine
+            assert not m.call(drop_signal_from=1)
+            assert m.status == 0x801
+            assert m.call()            # the other turn's counter is unaffected
+            assert not m.call()        # the turn that lost an arrival stays short
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_rendezvous_protocol_on_gloo_ranks():
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_peer_protocol_worker, args=(2, port), nprocs=2, join=True)

@@ -53,6 +53,38 @@ def _worker(rank, world, port):
             fused(torch.randn(16, 512, generator=g).half().to(dev))
         torch.cuda.synchronize()
         assert torch.equal(keep, saved)
+        # the peer-memory all-gather on its own (ragged column blocks), eagerly and replayed from a CUDA graph holding an
+        # even number of calls (the two result buffers alternate)
+        xchg = kp.PeerExchange(4, 1000, device=dev)
+        bounds = kp.row_bounds(1000, world)          # 500 / 500
+        rag = [(0, 333), (333, 1000)]                # ragged: not multiples of 8
+        for bnd in (bounds, rag):
+            lo, hi = bnd[rank]
+            full_ref = torch.arange(4 * 1000, dtype=torch.float32).reshape(4, 1000).half()
+            mine = full_ref[:, lo:hi].contiguous().to(dev)
+            for _ in range(3):
+                got = xchg.allgather_columns(mine, bnd)
+                torch.cuda.synchronize()
+                assert torch.equal(got.cpu(), full_ref)
+        if xchg.calls % 2:
+            xchg.allgather_columns(mine, rag)
+        src = torch.zeros(4, 500, dtype=torch.float16, device=dev)
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                a = xchg.allgather_columns(src, bounds)
+                a_copy = a.clone()
+                b = xchg.allgather_columns(src + 1, bounds)
+                b_copy = b.clone()
+        for it in range(4):
+            src.fill_(float(10 * it + rank))
+            graph.replay()
+            torch.cuda.synchronize()
+            want = torch.cat([torch.full((4, 500), float(10 * it + r)) for r in range(world)], 1).half()
+            assert torch.equal(a_copy.cpu(), want) and torch.equal(b_copy.cpu(), want + 1)
+        from kernelforge import _capi
+        assert _capi.device_status(dev) == 0
         torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()

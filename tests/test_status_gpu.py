@@ -52,3 +52,28 @@ def test_selftest_rejects_limits_out_of_range():
         _capi.check(_capi.lib().kfb_selftest_wait_expiry(10, outcome.data_ptr(), None))
     with pytest.raises(ValueError):
         _capi.check(_capi.lib().kfb_selftest_wait_expiry(10**10, outcome.data_ptr(), None))
+
+
+def test_peer_wait_gives_up_when_an_arrival_never_comes():
+    """kfb_peer_signal_wait on one GPU with its own counter as the only 'peer': one arrival comes (its own); with the
+    target set ahead as if another rank were expected, the wait runs out after its limit (2 ms), records 0x801 and the
+    kernel returns.  With the right target the same call passes at once."""
+    dev = torch.device("cuda", 0)
+    lib = _capi.lib()
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)
+    target = torch.zeros(1, dtype=torch.int64, device=dev)
+    ptrs = (ctypes.c_void_p * 1)(counter.data_ptr())
+    with _capi.on_device(dev):
+        _capi.check(lib.kfb_peer_signal_wait(ptrs, 1, counter.data_ptr(), target.data_ptr(), 2_000_000, _capi.stream_ptr(dev)))
+    torch.cuda.synchronize()
+    assert int(counter.item()) == 1 and int(target.item()) == 1 and _capi.device_status(dev) == 0
+    target.fill_(5)   # as if four more arrivals were owed
+    try:
+        with _capi.on_device(dev):
+            _capi.check(lib.kfb_peer_signal_wait(ptrs, 1, counter.data_ptr(), target.data_ptr(), 2_000_000, _capi.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        assert _capi.device_status(dev) == 0x801
+    finally:
+        _capi.device_status_reset(dev)
+        torch.cuda.synchronize()
+    assert _capi.device_status(dev) == 0
