@@ -146,6 +146,12 @@ size_t kfb_int4_gemm_ws_bytes(int M, int N, int K, int group);
 int kfb_int4_gemm(const void* x, const void* packed, const void* scales, void* y,
                   int M, int N, int K, int group, void* ws, size_t ws_bytes, void* stream);
 
+/* The same GEMM for bf16 activations: x and y bf16, scales stay fp16.  The weights are dequantised to bf16(q * s) (the
+ * product formed in FP32, one rounding), FP32 accumulation, one rounding to bf16.  Serves every M >= 1.  The reference
+ * takes fp16 activations only (README.md:103 lists bf16 as not done); this entry has no counterpart there. */
+int kfb_int4_gemm_bf16(const void* x, const void* packed, const void* scales, void* y,
+                       int M, int N, int K, int group, void* ws, size_t ws_bytes, void* stream);
+
 /* int4_gemm for an output-feature-sharded linear, fused with the all-gather that follows it.
  * The reference is single-GPU; this entry point has no counterpart there.
  * This rank holds N_local rows of packed / scales and computes y[:, col0 : col0 + N_local]; the epilogue
@@ -206,6 +212,22 @@ int kfb_flash_attn_decode_kvlen(const void* q, const void* k, const void* v, voi
                                 int B, int H, int Hk, int Nk, int D, float scale,
                                 const int64_t* kv_strides, const int32_t* kv_len_dev,
                                 void* ws, size_t ws_bytes, void* stream);
+
+/* Decode attention over a KV cache that is SHARDED ALONG THE SEQUENCE (one shard per GPU for a single long sequence,
+ * or any other split the caller makes).  The reference is single-GPU; these entries have no counterpart there.
+ *   kfb_flash_attn_decode_partial: runs the split-KV kernel on one shard (k, v: [B, Hk, Nk, D] of this shard, kv_len_dev
+ *     as in kfb_flash_attn_decode_kvlen or NULL) and leaves the softmax partials in `partial`: per (batch, kv-head
+ *     slot, key split) the unnormalised O (FP32), the running maximum m (log2 units) and the sum l.
+ *     kfb_flash_attn_decode_partial_bytes gives the buffer size (and the number of key splits) for the shard shape.
+ *   kfb_flash_attn_merge_partials: combines n_sets such buffers (set_stride_bytes apart, e.g. the result of an
+ *     all-gather; every set made with the same shard shape Nk_per_set) in set order and writes o [B, H, 1, D].
+ *     A shard with no valid key contributes nothing; if no shard has any, the output is zero. */
+size_t kfb_flash_attn_decode_partial_bytes(int B, int H, int Hk, int Nk, int D, int* splits_out);
+int kfb_flash_attn_decode_partial(const void* q, const void* k, const void* v, int dtype, int B, int H, int Hk,
+                                  int Nk, int D, float scale, const int64_t* kv_strides, const int32_t* kv_len_dev,
+                                  void* partial, size_t partial_bytes, void* stream);
+int kfb_flash_attn_merge_partials(const void* partials, int n_sets, size_t set_stride_bytes, void* o, int dtype,
+                                  int B, int H, int Hk, int Nk_per_set, int D, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused element-wise steps of a Llama-architecture decode step (fp16).  The reference leaves these to

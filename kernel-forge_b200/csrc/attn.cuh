@@ -25,7 +25,12 @@ int launch_prefill(const Problem& p, cudaStream_t stream);
 
 // Decode path (Nq == 1): split-KV, one CTA per (batch, kv head, split) (attn_decode.cu).
 size_t decode_ws_bytes(int B, int H, int Hk, int Nk, int D);
-int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream);
+int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream, bool partial_only = false);
+// Partial results only (no merge, no output): bytes of the (O, m, l) buffer and the number of key splits per
+// (batch, kv-head slot); and the merge of `sets` such buffers, `set_stride` floats apart, into the output.
+size_t decode_partial_bytes(int B, int H, int Hk, int Nk, int D, int* splits_out);
+int launch_merge(const float* partial, void* o, int dtype, int B, int H, int Hk, int D, int splits, int sets, long long set_stride,
+                 cudaStream_t stream);
 
 }  // namespace attn
 }  // namespace kfb

@@ -105,7 +105,8 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const uint16_t* __restrict__ q, uint16_t* __restrict__ o, float* __restrict__ partial, int H, int Hk,
-                   int Nk, int keys_per_split, float scale_log2, unsigned int* status, const int* __restrict__ kv_len) {
+                   int Nk, int keys_per_split, float scale_log2, unsigned int* status, const int* __restrict__ kv_len,
+                   int force_partial) {
   using L = Layout<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -296,7 +297,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
   }
   __syncthreads();
-  const bool direct = (splits == 1);
+  const bool direct = splits == 1 && !force_partial;   // otherwise (O, m, l) goes to `partial` for a later merge
   float* out_partial = partial + (((size_t)b * gridDim.y + blockIdx.y) * splits + split) * kPerWarp;
   for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
     const int r = idx / D, d = idx - r * D;
@@ -323,10 +324,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
 }
 
-// Combines the per-split partials of one (batch, query head) in split order.
+// Combines the per-split partials of one (batch, query head) in split order.  `sets` > 1: several partial buffers of
+// the same layout, `set_stride` floats apart (one per rank of a cache sharded along the sequence), combined in set
+// order, splits in order inside a set.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(D)
-attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ o, int H, int Hk, int splits) {
+attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ o, int H, int Hk, int splits, int sets,
+                         long long set_stride) {
   constexpr int kPer = kRows * (D + 2);
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   pdl_wait();
@@ -337,15 +341,17 @@ attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict
   const int slot = hk * chunks + within / kRows, r = within % kRows;
   const float* base_ptr = partial + ((size_t)b * (Hk * chunks) + slot) * splits * kPer;
   float m_all = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, base_ptr[(size_t)s * kPer + kRows * D + r]);
+  for (int t = 0; t < sets; ++t)
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, base_ptr[(size_t)t * set_stride + (size_t)s * kPer + kRows * D + r]);
   const float base = (m_all == -INFINITY) ? 0.f : m_all;
   float acc = 0.f, l_all = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* ps = base_ptr + (size_t)s * kPer;
-    const float f = ex2(ps[kRows * D + r] - base);
-    acc = fmaf(f, ps[r * D + d], acc);
-    l_all = fmaf(f, ps[kRows * D + kRows + r], l_all);
-  }
+  for (int t = 0; t < sets; ++t)
+    for (int s = 0; s < splits; ++s) {
+      const float* ps = base_ptr + (size_t)t * set_stride + (size_t)s * kPer;
+      const float f = ex2(ps[kRows * D + r] - base);
+      acc = fmaf(f, ps[r * D + d], acc);
+      l_all = fmaf(f, ps[kRows * D + kRows + r], l_all);
+    }
   o[((size_t)b * H + h) * D + d] = pack1<kBf16>(l_all > 0.f ? acc / l_all : 0.f);  // no valid key: zeros
 }
 
@@ -395,7 +401,7 @@ SplitPlan plan_splits(int B, int H, int Hk, int Nk, int D) {
 
 template <int D, bool kBf16>
 int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const CUtensorMap& tv, float* partial,
-           unsigned int* status, cudaStream_t stream) {
+           unsigned int* status, cudaStream_t stream, bool partial_only = false) {
   using L = Layout<D>;
   auto kernel = attn_decode_kernel<D, kBf16>;
   static bool configured[64] = {false};
@@ -408,11 +414,11 @@ int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const
   const dim3 grid(plan.splits, p.Hk * plan.chunks, p.B);
   if (int rc = launch_kernel("attn_decode_kernel", kernel, grid, dim3(kThreads), L::kAlloc, stream, pdl_enabled(), tk, tv,
                              (const uint16_t*)p.q, (uint16_t*)p.o, partial, p.H, p.Hk, p.Nk, plan.keys_per_split,
-                             p.scale * 1.4426950408889634f, status, p.kv_len_dev))
+                             p.scale * 1.4426950408889634f, status, p.kv_len_dev, partial_only ? 1 : 0))
     return rc;
-  if (plan.splits > 1)
+  if (plan.splits > 1 && !partial_only)
     return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16>, dim3(p.H, p.B), dim3(D), 0, stream,
-                         pdl_enabled(), (const float*)partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits);
+                         pdl_enabled(), (const float*)partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits, 1, 0LL);
   return KFB_OK;
 }
 
@@ -424,11 +430,33 @@ size_t decode_ws_bytes(int B, int H, int Hk, int Nk, int D) {
   return (size_t)B * Hk * plan.chunks * plan.splits * kRows * (D + 2) * sizeof(float);
 }
 
-int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+size_t decode_partial_bytes(int B, int H, int Hk, int Nk, int D, int* splits_out) {
+  const SplitPlan plan = plan_splits(B, H, Hk, Nk, D);
+  if (splits_out) *splits_out = plan.splits;
+  return (size_t)B * Hk * plan.chunks * plan.splits * kRows * (D + 2) * sizeof(float);
+}
+
+int launch_merge(const float* partial, void* o, int dtype, int B, int H, int Hk, int D, int splits, int sets, long long set_stride,
+                 cudaStream_t stream) {
+  if (H > 65535 || B > 65535) return fail(KFB_ERR_INVALID, "B and H must each be <= 65535");
+  const bool bf16 = dtype == KFB_BF16;
+  const dim3 grid(H, B);
+  if (D == 64)
+    return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, true>, grid, dim3(64), 0, stream, pdl_enabled(),
+                                partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
+                : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, false>, grid, dim3(64), 0, stream, pdl_enabled(),
+                                partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
+  return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, true>, grid, dim3(128), 0, stream, pdl_enabled(),
+                              partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
+              : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, false>, grid, dim3(128), 0, stream, pdl_enabled(),
+                              partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
+}
+
+int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream, bool partial_only) {
   if (p.Hk * ceil_div(p.H / p.Hk, kRows) > 65535 || p.B > 65535 || p.H > 65535)
     return fail(KFB_ERR_INVALID, "B, H and Hk * ceil(H/Hk/16) must each be <= 65535");
   const SplitPlan plan = plan_splits(p.B, p.H, p.Hk, p.Nk, p.D);
-  const size_t need = decode_ws_bytes(p.B, p.H, p.Hk, p.Nk, p.D);
+  const size_t need = partial_only ? decode_partial_bytes(p.B, p.H, p.Hk, p.Nk, p.D, nullptr) : decode_ws_bytes(p.B, p.H, p.Hk, p.Nk, p.D);
   if (need > 0 && (!ws || ws_bytes < need))
     return fail(KFB_ERR_WORKSPACE, "decode attention needs a %zu-byte workspace, got %zu", need, ws_bytes);
   if (need > 0 && !aligned16(ws)) return fail(KFB_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
@@ -444,10 +472,10 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stre
   const bool bf16 = p.dtype == KFB_BF16;
   float* partial = static_cast<float*>(ws);
   if (p.D == 64)
-    return bf16 ? launch<64, true>(p, plan, tk, tv, partial, status, stream)
-                : launch<64, false>(p, plan, tk, tv, partial, status, stream);
-  return bf16 ? launch<128, true>(p, plan, tk, tv, partial, status, stream)
-              : launch<128, false>(p, plan, tk, tv, partial, status, stream);
+    return bf16 ? launch<64, true>(p, plan, tk, tv, partial, status, stream, partial_only)
+                : launch<64, false>(p, plan, tk, tv, partial, status, stream, partial_only);
+  return bf16 ? launch<128, true>(p, plan, tk, tv, partial, status, stream, partial_only)
+              : launch<128, false>(p, plan, tk, tv, partial, status, stream, partial_only);
 }
 
 }  // namespace attn

@@ -45,6 +45,7 @@ struct OutSpec {
   int count;
   int ld;    // row stride of every buffer, in elements
   int col0;  // first column this rank writes
+  int bf16;  // the buffers hold bf16 instead of fp16 (the 16-bit stores are the same)
 };
 
 template <int MT>
@@ -80,8 +81,37 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s2) {
   return r;
 }
 
-// out: fp16 y [M, N] when splits == 1, else FP32 partial [splits][M][N]
-template <int MT>
+// The same for bf16 activations: q is exact in fp16, the product q * s is formed in FP32 and rounded once to bf16.
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t q2, float s) {
+  const float2 f = __half22float2(u32_as_h2(q2));
+  const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * s, f.y * s);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint4 dequant8_bf16(uint32_t w, float s) {
+  constexpr uint32_t kMagic = 0x64006400u;
+  const __half2 k1032 = u32_as_h2(0x64086408u);
+  const __half2 kSixteenth = u32_as_h2(0x2C002C00u);
+  const __half2 kMinus72 = u32_as_h2(0xD480D480u);
+  const uint32_t h = w >> 8;
+  uint4 r;
+  r.x = bf2_mul(h2_as_u32(__hsub2(u32_as_h2((w & 0x000F000Fu) | kMagic), k1032)), s);
+  r.y = bf2_mul(h2_as_u32(__hfma2(u32_as_h2((w & 0x00F000F0u) | kMagic), kSixteenth, kMinus72)), s);
+  r.z = bf2_mul(h2_as_u32(__hsub2(u32_as_h2((h & 0x000F000Fu) | kMagic), k1032)), s);
+  r.w = bf2_mul(h2_as_u32(__hfma2(u32_as_h2((h & 0x00F000F0u) | kMagic), kSixteenth, kMinus72)), s);
+  return r;
+}
+
+__device__ __forceinline__ uint16_t round16(float v, bool bf16) {
+  if (bf16) {
+    const __nv_bfloat16 b = __float2bfloat16_rn(v);
+    return *reinterpret_cast<const uint16_t*>(&b);
+  }
+  const __half h = __float2half_rn(v);
+  return *reinterpret_cast<const uint16_t*>(&h);
+}
+
+// out: fp16 (bf16) y [M, N] when splits == 1, else FP32 partial [splits][M][N]
+template <int MT, bool kBf16>
 __global__ void __launch_bounds__(kThreads)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __half* __restrict__ scales, const OutSpec out, float* __restrict__ partial, int M, int N,
@@ -155,7 +185,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_f16(kTileN, MT, 0, 0, 0);
+      constexpr uint32_t idesc = idesc_f16(kTileN, MT, kBf16 ? 1 : 0, 0, 0);
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % S;
         const uint32_t ph = (uint32_t)(i / S) & 1u;
@@ -201,10 +231,18 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const __half2 s2 = __half2half2(sc);
       uint8_t* arow = st + r * 128;
       const int x = r & 7, c = half * 4;
-      *reinterpret_cast<uint4*>(arow + (((c + 0) ^ x) << 4)) = dequant8(w.x, s2);
-      *reinterpret_cast<uint4*>(arow + (((c + 1) ^ x) << 4)) = dequant8(w.y, s2);
-      *reinterpret_cast<uint4*>(arow + (((c + 2) ^ x) << 4)) = dequant8(w.z, s2);
-      *reinterpret_cast<uint4*>(arow + (((c + 3) ^ x) << 4)) = dequant8(w.w, s2);
+      if constexpr (kBf16) {
+        const float sf = __half2float(sc);
+        *reinterpret_cast<uint4*>(arow + (((c + 0) ^ x) << 4)) = dequant8_bf16(w.x, sf);
+        *reinterpret_cast<uint4*>(arow + (((c + 1) ^ x) << 4)) = dequant8_bf16(w.y, sf);
+        *reinterpret_cast<uint4*>(arow + (((c + 2) ^ x) << 4)) = dequant8_bf16(w.z, sf);
+        *reinterpret_cast<uint4*>(arow + (((c + 3) ^ x) << 4)) = dequant8_bf16(w.w, sf);
+      } else {
+        *reinterpret_cast<uint4*>(arow + (((c + 0) ^ x) << 4)) = dequant8(w.x, s2);
+        *reinterpret_cast<uint4*>(arow + (((c + 1) ^ x) << 4)) = dequant8(w.y, s2);
+        *reinterpret_cast<uint4*>(arow + (((c + 2) ^ x) << 4)) = dequant8(w.z, s2);
+        *reinterpret_cast<uint4*>(arow + (((c + 3) ^ x) << 4)) = dequant8(w.w, s2);
+      }
       fence_proxy_async_smem();  // generic-proxy stores -> visible to tcgen05.mma
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_ready[s]);
@@ -243,7 +281,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         } else {
 #pragma unroll
           for (int c = 0; c < kCols; ++c)
-            reinterpret_cast<__half*>(tile)[c * kTileN + r] = __float2half_rn(__uint_as_float(acc[c]));
+            reinterpret_cast<uint16_t*>(tile)[c * kTileN + r] = round16(__uint_as_float(acc[c]), kBf16);
         }
         asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
         const int m_hi = min(kCols, M - (m0 + c0));  // batch rows of this chunk that exist
@@ -305,8 +343,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * elems + i];
     const long long m = i / N;
     const int n = (int)(i - m * N);
-    const __half v = __float2half_rn(acc);
-    for (int p = 0; p < out.count; ++p) out.y[p][m * out.ld + out.col0 + n] = v;
+    const uint16_t v = round16(acc, out.bf16 != 0);
+    for (int p = 0; p < out.count; ++p) reinterpret_cast<uint16_t*>(out.y[p])[m * out.ld + out.col0 + n] = v;
   }
 }
 
@@ -336,11 +374,11 @@ Plan make_plan(int M, int N, int K) {
   return p;
 }
 
-template <int MT>
+template <int MT, bool kBf16>
 int launch(const Plan& p, const CUtensorMap& tw, const CUtensorMap& tx, const void* scales, const OutSpec& out, float* partial,
            int M, int N, int K, int group, unsigned int* status, cudaStream_t stream) {
   using L = Layout<MT>;
-  auto kernel = int4_gemm_kernel<MT>;
+  auto kernel = int4_gemm_kernel<MT, kBf16>;
   static bool configured[64] = {false};
   int dev = 0;
   KFB_CUDA_TRY(cudaGetDevice(&dev));
@@ -402,16 +440,25 @@ int gemm_common(const void* x, const void* packed, const void* scales, const gem
   const uint64_t xd[4] = {(uint64_t)K, (uint64_t)M, 1, 1};
   const uint64_t xs[3] = {(uint64_t)K * 2, (uint64_t)M * K * 2, (uint64_t)M * K * 2};
   const uint32_t xb[4] = {64, (uint32_t)p.mt, 1, 1};
-  if (int rc = make_tmap_4d_sw128(&tx, x, KFB_F16, xd, xs, xb)) return rc;
+  if (int rc = make_tmap_4d_sw128(&tx, x, out.bf16 ? KFB_BF16 : KFB_F16, xd, xs, xb)) return rc;
 
   cudaStream_t s = (cudaStream_t)stream;
   float* partial = static_cast<float*>(ws);
+  if (out.bf16) {
+    switch (p.mt) {
+      case 16: return gemm::launch<16, true>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+      case 32: return gemm::launch<32, true>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+      case 64: return gemm::launch<64, true>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+      case 128: return gemm::launch<128, true>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+      default: return gemm::launch<256, true>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    }
+  }
   switch (p.mt) {
-    case 16: return gemm::launch<16>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
-    case 32: return gemm::launch<32>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
-    case 64: return gemm::launch<64>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
-    case 128: return gemm::launch<128>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
-    default: return gemm::launch<256>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 16: return gemm::launch<16, false>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 32: return gemm::launch<32, false>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 64: return gemm::launch<64, false>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    case 128: return gemm::launch<128, false>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
+    default: return gemm::launch<256, false>(p, tw, tx, scales, out, partial, M, N, K, group, status, s);
   }
 }
 
@@ -424,6 +471,18 @@ extern "C" int kfb_int4_gemm(const void* x, const void* packed, const void* scal
   out.count = 1;
   out.ld = N;
   out.col0 = 0;
+  if (!y) return fail(KFB_ERR_INVALID, "null pointer");
+  return gemm_common(x, packed, scales, out, M, N, K, group, ws, ws_bytes, stream);
+}
+
+extern "C" int kfb_int4_gemm_bf16(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,
+                                  int group, void* ws, size_t ws_bytes, void* stream) {
+  gemm::OutSpec out = {};
+  out.y[0] = static_cast<__half*>(y);
+  out.count = 1;
+  out.ld = N;
+  out.col0 = 0;
+  out.bf16 = 1;
   if (!y) return fail(KFB_ERR_INVALID, "null pointer");
   return gemm_common(x, packed, scales, out, M, N, K, group, ws, ws_bytes, stream);
 }

@@ -38,6 +38,8 @@ _SIGNATURES = {
     "kfb_int4_gemm_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "kfb_int4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                               c_void_p]),
+    "kfb_int4_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                   c_void_p]),
     "kfb_int4_gemm_allgather": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "kfb_peer_signal_wait": (c_int, [ctypes.POINTER(c_void_p), c_int, c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p]),
@@ -55,6 +57,10 @@ _SIGNATURES = {
     "kfb_embed_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "kfb_flash_attn_decode_kvlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_float, ctypes.POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
+    "kfb_flash_attn_decode_partial_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),
+    "kfb_flash_attn_decode_partial": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                              ctypes.POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
+    "kfb_flash_attn_merge_partials": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "kfb_flash_attn_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_float, ctypes.POINTER(c_int64), c_void_p]),
 }

@@ -31,7 +31,8 @@ class KFLinearInt4(nn.Module):
     """INT4 weight-only nn.Linear: y = x W_hat^T + b, W_hat dequantised inside the kernel.
 
     Buffers keep the reference's names (`packed` int32 [N, K/8], `scales` fp16 [N, K/G], `bias` fp16 or
-    None), so state dicts are interchangeable.  4 + 16/G bits per weight.  Activations must be fp16.
+    None), so state dicts are interchangeable.  4 + 16/G bits per weight.  Activations: fp16 (every kernel) or bf16
+    (the tcgen05 GEMM at every M; the reference is fp16 only).
     """
 
     def __init__(self, qw: kq.QuantizedWeight, bias: torch.Tensor | None):
@@ -47,9 +48,10 @@ class KFLinearInt4(nn.Module):
         return cls(kq.quantize_weight(linear.weight.detach(), group_size), linear.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.dtype != torch.float16:
-            raise TypeError(f"KFLinearInt4 takes fp16 activations, got {x.dtype}")
-        return ops.int4_linear(x, self.packed, self.scales, self.group_size, self.bias)
+        if x.dtype not in ops.INT4_ACT_DTYPES:
+            raise TypeError(f"KFLinearInt4 takes fp16 activations (or bf16), got {x.dtype}")
+        bias = self.bias if self.bias is None or x.dtype == torch.float16 else self.bias.to(x.dtype)
+        return ops.int4_linear(x, self.packed, self.scales, self.group_size, bias)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "

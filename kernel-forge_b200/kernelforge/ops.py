@@ -36,9 +36,13 @@ def _resolve_scale(scale: float | None, head_dim: int) -> float:
 # INT4 weight-only linear
 # ---------------------------------------------------------------------------
 
-def _check_int4(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int) -> None:
-    if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.float16 or x.dim() != 2:
-        raise TypeError("x must be a 2-D fp16 CUDA tensor [M, K]")
+INT4_ACT_DTYPES = (torch.float16, torch.bfloat16)   # the reference takes fp16 only (README.md:103); bf16 is served by the GEMM
+
+
+def _check_int4(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int, allow_bf16: bool = False) -> None:
+    ok_dtype = isinstance(x, torch.Tensor) and (x.dtype == torch.float16 or (allow_bf16 and x.dtype == torch.bfloat16))
+    if not isinstance(x, torch.Tensor) or not x.is_cuda or not ok_dtype or x.dim() != 2:
+        raise TypeError("x must be a 2-D fp16 CUDA tensor [M, K]" + (" (or bf16)" if allow_bf16 else ""))
     if not x.is_contiguous():
         raise ValueError("x must be contiguous")
     if packed.dtype != torch.int32 or scales.dtype != torch.float16:
@@ -79,14 +83,15 @@ def _gemv_launch(x, packed, scales, group_size: int, flags: int = 0, small_batch
 def _gemm_launch(x, packed, scales, group_size: int) -> torch.Tensor:
     m, k = x.shape
     n = packed.shape[0]
-    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    y = torch.empty(m, n, dtype=x.dtype, device=x.device)
     if n == 0 or m == 0:
         return y
     lib = _capi.lib()
     ws_bytes = lib.kfb_int4_gemm_ws_bytes(m, n, k, group_size)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    entry = lib.kfb_int4_gemm_bf16 if x.dtype == torch.bfloat16 else lib.kfb_int4_gemm
     with _capi.on_device(x.device):
-        _capi.check(lib.kfb_int4_gemm(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(), m, n, k,
+        _capi.check(entry(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), y.data_ptr(), m, n, k,
                                       group_size, ws.data_ptr(), ws_bytes, _capi.stream_ptr(x.device)))
     return y
 
@@ -178,8 +183,13 @@ def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
     """y = x @ W_hat^T for INT4 weights from kernelforge.quantize, choosing the kernel by M.
 
     M <= GEMV_MAX_M: the bandwidth-bound GEMV (FP32 accumulation); a little above it, where measured faster, the same
-    kernel with more batch columns (int4_small_batch).  Larger M: the tcgen05 GEMM.
+    kernel with more batch columns (int4_small_batch).  Larger M: the tcgen05 GEMM.  bf16 activations (not in the
+    reference, README.md:103) take the GEMM at every M.
     """
+    if x.dtype == torch.bfloat16:
+        _check_int4(x, packed, scales, group_size, allow_bf16=True)
+        _check_int4_storage(x, packed, scales, group_size)
+        return _gemm_launch(x, packed, scales, int(group_size))
     if x.shape[0] <= GEMV_MAX_M:
         return int4_gemv(x, packed, scales, group_size)
     if x.shape[0] <= 16 and _small_batch_wins(x.shape[0], packed.shape[0], x.shape[1]):
@@ -320,6 +330,40 @@ def flash_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     return o
 
 
+def flash_attn_decode_partial(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
+                              kv_len: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
+    """Softmax partials of one decode step over ONE SHARD of the keys (see kfb_flash_attn_decode_partial): a flat fp32
+    buffer holding, per (batch, kv-head slot, key split), the unnormalised output, the running maximum and the sum.
+    q: [B, H, 1, D]; k_shard, v_shard: [B, Hk, Nk_shard, D]; kv_len: optional int32 [B], valid rows of this shard."""
+    _check_attn(q, k_shard, v_shard, False, strided_kv=True)
+    b, h, _, d = q.shape
+    hk, nk = k_shard.shape[1], k_shard.shape[2]
+    lib = _capi.lib()
+    nbytes = lib.kfb_flash_attn_decode_partial_bytes(b, h, hk, nk, d, None)
+    partial = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+    strides = (ctypes.c_int64 * 3)(*k_shard.stride()[:3])
+    with _capi.on_device(q.device):
+        _capi.check(lib.kfb_flash_attn_decode_partial(q.data_ptr(), k_shard.data_ptr(), v_shard.data_ptr(), _capi.dtype_code(q.dtype),
+                                                      b, h, hk, nk, d, _resolve_scale(scale, d), strides,
+                                                      kv_len.data_ptr() if kv_len is not None else None, partial.data_ptr(),
+                                                      nbytes, _capi.stream_ptr(q.device)))
+    return partial
+
+
+def flash_attn_merge_partials(partials: torch.Tensor, like_q: torch.Tensor, hk: int, nk_per_shard: int) -> torch.Tensor:
+    """Merges the partial buffers of several shards ([n_shards, floats_per_shard] fp32, same shard shape each, in shard
+    order) into the attention output [B, H, 1, D]."""
+    b, h, _, d = like_q.shape
+    o = torch.empty_like(like_q)
+    n_sets = partials.shape[0] if partials.dim() == 2 else 1
+    stride = partials.stride(0) * 4 if partials.dim() == 2 else 0
+    with _capi.on_device(like_q.device):
+        _capi.check(_capi.lib().kfb_flash_attn_merge_partials(partials.data_ptr(), n_sets, stride, o.data_ptr(),
+                                                              _capi.dtype_code(like_q.dtype), b, h, hk, nk_per_shard, d,
+                                                              _capi.stream_ptr(like_q.device)))
+    return o
+
+
 # ---------------------------------------------------------------------------
 # int4_linear: the nn.Linear-shaped entry point
 # ---------------------------------------------------------------------------
@@ -331,7 +375,7 @@ def _int4_matmul_op(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
 
 @_int4_matmul_op.register_fake
 def _(x, packed, scales, group_size):
-    return x.new_empty(x.shape[0], packed.shape[0])
+    return x.new_empty(x.shape[0], packed.shape[0])   # fp16 in -> fp16 out, bf16 in -> bf16 out
 
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
@@ -345,7 +389,7 @@ def int4_linear(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
-    _check_int4(x2, packed, scales, group_size)
+    _check_int4(x2, packed, scales, group_size, allow_bf16=True)
     if _plain_eager(x2):
         if bias is not None and x2.shape[0] <= FUSED_GEMV_MAX_M and bias.dtype == torch.float16 and bias.is_contiguous():
             # decode-sized call: the bias goes into the GEMV epilogue (same two roundings as `y + bias`)

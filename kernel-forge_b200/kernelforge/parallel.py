@@ -64,6 +64,27 @@ def shard_attention_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ran
     return q[:, qs].contiguous(), k[:, ks].contiguous(), v[:, ks].contiguous()
 
 
+def sequence_sharded_decode_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, total_len: torch.Tensor | int,
+                                      group: dist.ProcessGroup | None = None) -> torch.Tensor:
+    """One decode step of a sequence whose KV cache is split along the sequence over the ranks of `group` (cross-GPU
+    split-KV for a single long context): rank r holds rows [r * Nk_shard, (r + 1) * Nk_shard) of the cache.
+
+    Each rank runs the split-KV decode kernel on its shard (ops.flash_attn_decode_partial), the FP32 partials --
+    (O, m, l) per head, a few KB -- are all-gathered, and every rank merges them in rank order (deterministic), so all
+    ranks hold the same output.  q: [B, H, 1, D] (replicated); total_len: int or int32 tensor [B], the valid length of
+    the whole cache."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    b = q.shape[0]
+    nk = k_shard.shape[2]
+    if not torch.is_tensor(total_len):
+        total_len = torch.full((b,), int(total_len), dtype=torch.int32, device=q.device)
+    local_len = (total_len.to(torch.int32) - rank * nk).clamp_(0, nk)
+    part = ops.flash_attn_decode_partial(q, k_shard, v_shard, local_len)
+    gathered = torch.empty(world, part.numel(), dtype=torch.float32, device=q.device)
+    dist.all_gather_into_tensor(gathered, part, group=group)
+    return ops.flash_attn_merge_partials(gathered, q, k_shard.shape[1], nk)
+
+
 class ShardedInt4Linear(torch.nn.Module):
     """Output-feature-parallel INT4 linear: local shard compute + one all-gather.
 

@@ -240,3 +240,23 @@ class TestValidation:
         q2 = torch.randn(1, 4, 9, 64, device="cuda", dtype=torch.float16)
         with pytest.raises(ValueError, match="Nq <= Nk"):
             ops.flash_attn(q2, k, k, causal=True)
+
+
+@pytest.mark.parametrize("b,h,hk,nk,d,shards", [(1, 32, 4, 16384, 64, 4), (2, 8, 8, 3000, 128, 3), (3, 16, 2, 1024, 64, 2)])
+def test_decode_over_a_sequence_sharded_cache(b, h, hk, nk, d, shards):
+    """The partial / merge pair that serves a KV cache split along the sequence (one shard per GPU): here every shard
+    is processed on this GPU, one call each, the partial buffers are stacked as an all-gather would leave them, and
+    the merge must reproduce attention over the whole cache -- including a ragged total length that leaves the last
+    shards partly or wholly empty."""
+    q, k, v = qkv_case(b, h, hk, 1, nk, d, torch.float16, seed=nk + shards)
+    per = nk // shards
+    qc = q.cuda()
+    for total in (nk, per + 5, 1):
+        parts = []
+        for r in range(shards):
+            ks, vs = k[:, :, r * per:(r + 1) * per].contiguous().cuda(), v[:, :, r * per:(r + 1) * per].contiguous().cuda()
+            local = torch.full((b,), max(0, min(per, total - r * per)), dtype=torch.int32).cuda()
+            parts.append(ops.flash_attn_decode_partial(qc, ks, vs, local))
+        out = ops.flash_attn_merge_partials(torch.stack(parts), qc, hk, per)
+        ref = attn_oracle(q, k[:, :, :total], v[:, :, :total], True)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= ATTN_ATOL[torch.float16], f"total {total}"

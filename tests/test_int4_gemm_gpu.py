@@ -73,3 +73,20 @@ def test_gemm_rejects_n_not_multiple_of_64():
 
 def test_status_word_clean_after_gemm():
     assert _capi.device_status(torch.device("cuda", 0)) == 0
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 130, 1024])
+@pytest.mark.parametrize("n,k,group", [(2048, 2048, 128), (1536, 8960, 128), (200, 512, 64), (8960, 1536, 128)])
+def test_bf16_activations(m, n, k, group):
+    """bf16 activations (the reference is fp16 only): the tcgen05 GEMM with bf16(q * s) weights, against the FP32
+    oracle on the same bf16 bits.  Bound: 8x the fp16 bound (bf16 carries 3 bits less), as for attention."""
+    from oracle import kf_oracle as ko
+    rng = np.random.default_rng(m + n + k)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    packed, scales = ko.quantize_weight(w, group)
+    x = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).bfloat16()
+    ref = x.float().numpy() @ ko.dequantize(packed, scales, group, np.float32).T
+    out = ops.int4_linear(x.cuda(), torch.from_numpy(packed).cuda(), torch.from_numpy(scales).cuda(), group)
+    assert out.dtype == torch.bfloat16 and out.shape == (m, n)
+    err = float(np.abs(out.float().cpu().numpy() - ref).max())
+    assert err <= 1.6e-2 * float(np.abs(ref).max()), f"bf16 m{m} n{n} k{k}: max abs err {err:.3e}"

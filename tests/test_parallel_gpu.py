@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _worker(rank, world, port):
-    for p in (str(ROOT), str(ROOT / "kernel-forge_b200")):
+    for p in (str(ROOT), str(ROOT / "kernel-forge_b200"), str(ROOT / "tests")):
         if p not in sys.path:
             sys.path.insert(0, p)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -83,6 +83,15 @@ def _worker(rank, world, port):
             torch.cuda.synchronize()
             want = torch.cat([torch.full((4, 500), float(10 * it + r)) for r in range(world)], 1).half()
             assert torch.equal(a_copy.cpu(), want) and torch.equal(b_copy.cpu(), want + 1)
+        # cross-GPU split-KV: a single sequence whose cache is split along the sequence over the two GPUs
+        from helpers import attn_oracle, qkv_case
+        q, k, v = qkv_case(1, 32, 4, 1, 8192, 64, torch.float16, seed=21)   # same seed on both ranks
+        per = 8192 // world
+        ks, vs = k[:, :, rank * per:(rank + 1) * per].contiguous().to(dev), v[:, :, rank * per:(rank + 1) * per].contiguous().to(dev)
+        for total in (8192, per + 77, 100):
+            out = kp.sequence_sharded_decode_attention(q.to(dev), ks, vs, total)
+            ref = attn_oracle(q, k[:, :, :total], v[:, :, :total], True)
+            assert np.abs(out.float().cpu().numpy() - ref).max() <= 2e-3, f"sequence-sharded decode, total {total}"
         from kernelforge import _capi
         assert _capi.device_status(dev) == 0
         torch.cuda.synchronize()
