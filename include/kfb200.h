@@ -137,6 +137,24 @@ int kfb_int4_gemv_fused(const void* x, const void* packed, const void* scales, v
                         int M, int N, int K, int group, int xform, const void* norm_weight, float eps,
                         const void* bias, const void* residual, int flags, void* stream);
 
+/* Two more fused forms of the same M <= 2 GEMV, for weight matrices whose ROWS the caller has put into a private order
+ * when the model was built (rows are quantised independently, so reordering them is exact; the public packed format
+ * of quantize_weight is unchanged).  xform / norm_weight / eps as in kfb_int4_gemv_fused.
+ *   kfb_int4_gemv_silu_pair: rows 2p, 2p+1 = gate row p, up row p of a SiLU MLP; writes
+ *     act_out[M, N/2] = fp16(fp16(silu(gate . x)) * (up . x)) -- the projection and the SiLU * up kernel in one launch.
+ *   kfb_int4_gemv_rope_kv: the fused q / k / v projection of ONE decode position, N = (H + 2 Hk) D rows: for every q
+ *     head, then every k head, rows 2j, 2j+1 = features j, j + D/2 (the pair the rotate-half rotary embedding mixes);
+ *     then the v heads in natural order.  Rotates q and k with cos_table / sin_table [Lmax, D] at position *pos_dev,
+ *     writes q_out [M, H, D] and row pos of k_cache / v_cache [M, Hk, Lmax, D] -- the projection and
+ *     kfb_rope_kv_write in one launch; a position outside [0, Lmax) writes nothing and records 0x701.
+ * No counterpart in the reference (it leaves these steps to Hugging Face / torch kernels). */
+int kfb_int4_gemv_silu_pair(const void* x, const void* packed, const void* scales, void* act_out, int M, int N, int K,
+                            int group, int xform, const void* norm_weight, float eps, int flags, void* stream);
+int kfb_int4_gemv_rope_kv(const void* x, const void* packed, const void* scales, int M, int K, int group, int xform,
+                          const void* norm_weight, float eps, const void* cos_table, const void* sin_table,
+                          const void* pos_dev, void* q_out, void* k_cache, void* v_cache, int H, int Hk, int D, int Lmax,
+                          int flags, void* stream);
+
 /* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
  * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),
  * K % group == 0.  Weights are dequantised into swizzled shared memory and multiplied on

@@ -424,6 +424,22 @@ attn_prefill_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // P(j) overwrites the first 64 columns of S(j) and QK(j+1) is queued behind PV(j) (tcgen05.mma
 // instructions of one thread execute in issue order).
 // Both tiles read the same K/V tiles, so each is brought into shared memory once for 256 query rows.
+//
+// What was measured on the way to this form (B=2 H=16 D=64 non-causal, TFLOP/s at N = 2048 / 8192, A/B on one box):
+//   one issuer thread for both tiles, softmax warpgroups unordered                          485 / 657
+//   one issuer thread per tile (issuing an MMA occupies the thread for about the MMA's duration and a commit for
+//     ~130 clocks: one thread feeding both tiles was the bottleneck; polled with mbarrier.test_wait, because a
+//     try_wait on a barrier that is not ready may suspend the thread)                        472 / 679
+//   + the two warpgroups take turns on the exponential units, baton passed after a block     491 / 695
+//   + baton passed half way through a block (this kernel)                                    534 / 765
+//   a baton per scheduler (32 threads) instead of per warpgroup                              459 / 621
+//   the first TMA loads issued before the set-up barrier                                     459 / 621
+//   two threads per query row (640 threads, maxima exchanged through shared memory)          403 / 618
+//   25 % of the exponentials as a degree-3 polynomial on the FMA pipe                        527 / 753
+// A 128 x 128 score tile costs 1024 clocks of the SM's exponential units; a step timeline of this kernel shows ~1460
+// clocks of exponentials per warp and step and ~1200 of everything else (score load, maxima, P store, barriers), the two
+// tiles alternating: ~1570 clocks per tile and step, 65 % of the unit's rate.  The polynomial does not help because a
+// warp's block of exponentials is bound by its own dependency chain (FMA -> ex2 -> add / convert), not by the unit.
 // ------------------------------------------------------------------------------------------------
 namespace pair {
 

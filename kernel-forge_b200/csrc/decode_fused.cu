@@ -104,8 +104,10 @@ __global__ void rope_kv_write_kernel(const __half* __restrict__ qkv, const float
     const float lo = __half2float(src[d]), hi = __half2float(src[d + half]);
     const float c0 = cos_t[pos * D + d], s0 = sin_t[pos * D + d];
     const float c1 = cos_t[pos * D + d + half], s1 = sin_t[pos * D + d + half];
-    const __half rlo = __float2half_rn(lo * c0 - hi * s0);
-    const __half rhi = __float2half_rn(hi * c1 + lo * s1);
+    // separate FP32 roundings of both products and of the sum (no contraction), like the torch formulation
+    // t * cos + rotate_half(t) * sin; the GEMV epilogue that replaces this kernel at batch <= 2 does the same
+    const __half rlo = __float2half_rn(__fsub_rn(__fmul_rn(lo, c0), __fmul_rn(hi, s0)));
+    const __half rhi = __float2half_rn(__fadd_rn(__fmul_rn(hi, c1), __fmul_rn(lo, s1)));
     __half* dst = head < H ? q_out + ((size_t)b * H + head) * D
                            : k_cache + (((size_t)b * Hk + (head - H)) * Lmax + pos) * D;
     dst[d] = rlo;

@@ -121,12 +121,37 @@ __device__ __forceinline__ void unpack32(const uint4& wv, uint32_t (&q)[16]) {
 // separate torch kernels it replaces.
 enum Xform : int { kXformNone = 0, kXformRmsNorm = 1, kXformSiluMul = 2 };
 
+// Pair epilogues: the weight rows were laid out (by the caller, once, when the model was built -- a private row order of
+// the public packed format; rows are quantised independently, so any row order is exact) so that rows 2p and 2p + 1
+// belong together, and the kernel turns each pair of results into what the next kernel of a decode step needs:
+//   kEpiSiluPair  rows (gate_p, up_p): writes act[m, p] = fp16(fp16(silu(g)) * u), y is [M, N / 2]
+//                 (replaces the separate SiLU * up kernel; same roundings);
+//   kEpiRopeKv    the fused q / k / v projection of one decode position: pairs (d, d + D/2) of a q or k head are rotated
+//                 (rotate-half convention, FP32, one rounding) and written to q_out / row `pos` of the K cache; v pairs
+//                 (d, d + 1) go to row `pos` of the V cache (replaces the separate RoPE + cache-write kernel).
+enum Epilogue : int { kEpiNone = 0, kEpiSiluPair = 1, kEpiRopeKv = 2 };
+
+struct RopeKv {
+  const float* cos_t;       // [Lmax, D]
+  const float* sin_t;
+  const long long* pos;     // device scalar: the position being written
+  __half* q_out;            // [M, H, D]
+  __half* k_cache;          // [M, Hk, Lmax, D]
+  __half* v_cache;
+  int H, Hk, D, Lmax;
+  unsigned int* status;
+};
+
 struct Fusion {
   const __half* norm_w;    // kXformRmsNorm: [K]
   float eps;
   const __half* bias;      // [N] or nullptr
   const __half* residual;  // [M, N] or nullptr
+  int epi;                 // Epilogue
+  RopeKv rope;
 };
+
+constexpr unsigned int kStatusRopePosition = 0x701;  // the position read on the device lies outside [0, Lmax)
 
 // One rounding of the FP32 sum to fp16, then the optional bias and residual as fp16 additions.
 __device__ __forceinline__ __half finish(float acc, const Fusion& fu, int m, int n, int N) {
@@ -136,10 +161,51 @@ __device__ __forceinline__ __half finish(float acc, const Fusion& fu, int m, int
   return v;
 }
 
+// Stores the results of rows n (even) and n + 1 of batch row m.
+template <int EPI>
+__device__ __forceinline__ void store_pair(float a0, float a1, const Fusion& fu, __half* __restrict__ y, int m, int n, int N) {
+  if constexpr (EPI == kEpiNone) {
+    y[(size_t)m * N + n] = finish(a0, fu, m, n, N);
+    if (n + 1 < N) y[(size_t)m * N + n + 1] = finish(a1, fu, m, n + 1, N);
+    return;
+  }
+  const float g = __half2float(__float2half_rn(a0)), u = __half2float(__float2half_rn(a1));   // what the unfused path reads back
+  if constexpr (EPI == kEpiSiluPair) {
+    y[(size_t)m * (N / 2) + (n >> 1)] = __hmul(__float2half_rn(g / (1.0f + __expf(-g))), __float2half_rn(u));
+    return;
+  }
+  const RopeKv& rp = fu.rope;
+  const long long pos = rp.pos[0];
+  if (pos < 0 || pos >= rp.Lmax) {   // nothing is read or written for a position outside the cache
+    if (n == 0 && m == 0) atomicCAS(rp.status, 0u, kStatusRopePosition);
+    return;
+  }
+  const int half = rp.D / 2, p = n >> 1;
+  const int q_pairs = rp.H * half, k_pairs = rp.Hk * half;
+  if (p < q_pairs + k_pairs) {
+    const int head = p < q_pairs ? p / half : (p - q_pairs) / half;
+    const int j = p < q_pairs ? p % half : (p - q_pairs) % half;
+    const float c0 = rp.cos_t[pos * rp.D + j], s0 = rp.sin_t[pos * rp.D + j];
+    const float c1 = rp.cos_t[pos * rp.D + j + half], s1 = rp.sin_t[pos * rp.D + j + half];
+    // the roundings of the separate RoPE kernel: both products and the sum rounded on their own
+    const __half rlo = __float2half_rn(__fsub_rn(__fmul_rn(g, c0), __fmul_rn(u, s0)));
+    const __half rhi = __float2half_rn(__fadd_rn(__fmul_rn(u, c1), __fmul_rn(g, s1)));
+    __half* dst = p < q_pairs ? rp.q_out + ((size_t)m * rp.H + head) * rp.D
+                              : rp.k_cache + (((size_t)m * rp.Hk + head) * rp.Lmax + pos) * rp.D;
+    dst[j] = rlo;
+    dst[j + half] = rhi;
+  } else {
+    const int pv = p - q_pairs - k_pairs, head = pv / half, j = pv % half;
+    __half* dst = rp.v_cache + (((size_t)m * rp.Hk + head) * rp.Lmax + pos) * rp.D;
+    dst[2 * j] = __float2half_rn(a0);
+    dst[2 * j + 1] = __float2half_rn(a1);
+  }
+}
+
 // M: activation rows; R: weight rows per warp; G: group size; XF: the transform above (a transformed x is built once
 // per CTA in shared memory, M * K halfs, and the main loop reads it from there).
 // `ksplit_log2`: 2^ksplit_log2 warps of a CTA share one row tile and split its K chunks.
-template <int M, int R, int G, int XF = kXformNone>
+template <int M, int R, int G, int XF = kXformNone, int EPI = kEpiNone>
 __global__ void __launch_bounds__(kThreads)
 int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed, const __half* __restrict__ scales,
                  __half* __restrict__ y, int N, int K, int ksplit_log2, const Fusion fu) {
@@ -352,9 +418,13 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
     if (lane == 0 && r0 < N) {
 #pragma unroll
       for (int m = 0; m < M; ++m)
+        if constexpr (R == 1) {
+          y[(size_t)m * N + r0] = finish(acc[m][0], fu, m, r0, N);
+        } else {
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-          if (r0 + r < N) y[(size_t)m * N + r0 + r] = finish(acc[m][r], fu, m, r0 + r, N);
+          for (int r = 0; r < R; r += 2)
+            if (r0 + r < N) store_pair<EPI>(acc[m][r], acc[m][r + 1], fu, y, m, r0 + r, N);
+        }
     }
     return;
   }
@@ -365,17 +435,24 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
       for (int r = 0; r < R; ++r) red[warp][m * R + r] = acc[m][r];
   }
   __syncthreads();
-  if (kpart == 0 && lane < M * R && r0 < N) {
+  if (kpart == 0) {   // warp-uniform
+    const bool live = lane < M * R && r0 < N;
     const int m = lane / R, r = lane % R;
     float v = 0.f;
-    for (int p = 0; p < ksplit; ++p) v += red[warp + p][lane];  // fixed order
-    if (r0 + r < N) y[(size_t)m * N + r0 + r] = finish(v, fu, m, r0 + r, N);
+    if (live)
+      for (int p = 0; p < ksplit; ++p) v += red[warp + p][lane];  // fixed order
+    if constexpr (R == 1) {
+      if (live) y[(size_t)m * N + r0] = finish(v, fu, m, r0, N);
+    } else {
+      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);   // row r ^ 1 of the same batch row (R is even)
+      if (live && (r & 1) == 0 && r0 + r < N) store_pair<EPI>(v, partner, fu, y, m, r0 + r, N);
+    }
   }
 }
 
-template <int M, int R, int G, int XF = kXformNone>
+template <int M, int R, int G, int XF = kXformNone, int EPI = kEpiNone>
 int launch(const void* x, const void* packed, const void* scales, void* y, int N, int K, int ksplit_log2, int flags,
-           cudaStream_t stream, const Fusion& fu = Fusion{nullptr, 0.f, nullptr, nullptr}) {
+           cudaStream_t stream, const Fusion& fu = Fusion{}) {
   const int tiles = ceil_div(N, R);
   const int grid = ceil_div(tiles, kWarps >> ksplit_log2);
   cudaLaunchConfig_t cfg = {};
@@ -388,7 +465,7 @@ int launch(const void* x, const void* packed, const void* scales, void* y, int N
     int dev = 0;
     KFB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_kernel<M, R, G, XF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      KFB_CUDA_TRY(cudaFuncSetAttribute(int4_gemv_kernel<M, R, G, XF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
       configured[dev] = true;
     }
   }
@@ -397,14 +474,14 @@ int launch(const void* x, const void* packed, const void* scales, void* y, int N
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ((flags & 1) || pdl_enabled()) ? 1 : 0;
-  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_gemv_kernel<M, R, G, XF>, (const __half*)x, (const uint4*)packed,
+  KFB_CUDA_TRY(cudaLaunchKernelEx(&cfg, int4_gemv_kernel<M, R, G, XF, EPI>, (const __half*)x, (const uint4*)packed,
                                   (const __half*)scales, (__half*)y, N, K, ksplit_log2, fu));
   return KFB_OK;
 }
 
-template <int M, int G, int XF = kXformNone>
+template <int M, int G, int XF = kXformNone, int EPI = kEpiNone>
 int pick_rows(const void* x, const void* packed, const void* scales, void* y, int N, int K, int flags,
-              cudaStream_t stream, const Fusion& fu = Fusion{nullptr, 0.f, nullptr, nullptr}) {
+              cudaStream_t stream, const Fusion& fu = Fusion{}) {
   // K split inside the CTA: aim at about two 16-byte chunks per lane, never less than one.
   const int KC = K / 32;
   int ksplit_log2 = 0;
@@ -414,28 +491,42 @@ int pick_rows(const void* x, const void* packed, const void* scales, void* y, in
   constexpr int kMaxR = (M == 1) ? 8 : (M == 2) ? 4 : 2;
   int R = kMaxR;
   while (R > 1 && ceil_div(ceil_div(N, R), kWarps >> ksplit_log2) < 2 * sms) R >>= 1;
+  if (EPI != kEpiNone && R < 2) R = 2;   // a pair of rows must sit in one warp
   if constexpr (kMaxR == 8) {
-    if (R == 8) return launch<M, 8, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+    if (R == 8) return launch<M, 8, G, XF, EPI>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
   }
   if constexpr (kMaxR >= 4) {
-    if (R == 4) return launch<M, 4, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+    if (R == 4) return launch<M, 4, G, XF, EPI>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
   }
-  if (R == 2) return launch<M, 2, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
-  return launch<M, 1, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+  if (R == 2) return launch<M, 2, G, XF, EPI>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+  if constexpr (EPI == kEpiNone) return launch<M, 1, G, XF>(x, packed, scales, y, N, K, ksplit_log2, flags, stream, fu);
+  return fail(KFB_ERR_INVALID, "a pair epilogue needs two rows per warp");
 }
 
 // The fused entry: M <= 2 only (the batch sizes at which this kernel is the one the dispatcher uses anyway).
+template <int G, int M, int EPI>
+int pick_xform(const void* x, const void* packed, const void* scales, void* y, int N, int K, int xform, int flags,
+               cudaStream_t stream, const Fusion& fu) {
+  if (xform == kXformRmsNorm) return pick_rows<M, G, kXformRmsNorm, EPI>(x, packed, scales, y, N, K, flags, stream, fu);
+  if constexpr (EPI == kEpiNone) {
+    if (xform == kXformSiluMul) return pick_rows<M, G, kXformSiluMul, EPI>(x, packed, scales, y, N, K, flags, stream, fu);
+  } else {
+    if (xform == kXformSiluMul) return fail(KFB_ERR_UNSUPPORTED, "the pair epilogues take no SiLU * up prologue");
+  }
+  return pick_rows<M, G, kXformNone, EPI>(x, packed, scales, y, N, K, flags, stream, fu);
+}
+
 template <int G>
 int pick_fused(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int xform, int flags,
                cudaStream_t stream, const Fusion& fu) {
   if (M == 1) {
-    if (xform == kXformRmsNorm) return pick_rows<1, G, kXformRmsNorm>(x, packed, scales, y, N, K, flags, stream, fu);
-    if (xform == kXformSiluMul) return pick_rows<1, G, kXformSiluMul>(x, packed, scales, y, N, K, flags, stream, fu);
-    return pick_rows<1, G, kXformNone>(x, packed, scales, y, N, K, flags, stream, fu);
+    if (fu.epi == kEpiSiluPair) return pick_xform<G, 1, kEpiSiluPair>(x, packed, scales, y, N, K, xform, flags, stream, fu);
+    if (fu.epi == kEpiRopeKv) return pick_xform<G, 1, kEpiRopeKv>(x, packed, scales, y, N, K, xform, flags, stream, fu);
+    return pick_xform<G, 1, kEpiNone>(x, packed, scales, y, N, K, xform, flags, stream, fu);
   }
-  if (xform == kXformRmsNorm) return pick_rows<2, G, kXformRmsNorm>(x, packed, scales, y, N, K, flags, stream, fu);
-  if (xform == kXformSiluMul) return pick_rows<2, G, kXformSiluMul>(x, packed, scales, y, N, K, flags, stream, fu);
-  return pick_rows<2, G, kXformNone>(x, packed, scales, y, N, K, flags, stream, fu);
+  if (fu.epi == kEpiSiluPair) return pick_xform<G, 2, kEpiSiluPair>(x, packed, scales, y, N, K, xform, flags, stream, fu);
+  if (fu.epi == kEpiRopeKv) return pick_xform<G, 2, kEpiRopeKv>(x, packed, scales, y, N, K, xform, flags, stream, fu);
+  return pick_xform<G, 2, kEpiNone>(x, packed, scales, y, N, K, xform, flags, stream, fu);
 }
 
 template <int G>
@@ -495,25 +586,73 @@ extern "C" int kfb_int4_gemv(const void* x, const void* packed, const void* scal
   return gemv_entry("int4_gemv", 8, x, packed, scales, y, M, N, K, group, flags, stream);
 }
 
-extern "C" int kfb_int4_gemv_fused(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int group,
-                                   int xform, const void* norm_weight, float eps, const void* bias, const void* residual,
-                                   int flags, void* stream) {
+namespace {
+
+int fused_common(const char* what, const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int group,
+                 int xform, int flags, void* stream, const gemv::Fusion& fu) {
   if (int rc = require_sm100()) return rc;
-  if (M < 1 || M > 2) return fail(KFB_ERR_UNSUPPORTED, "int4_gemv_fused handles M in [1, 2], got M=%d", M);
+  if (M < 1 || M > 2) return fail(KFB_ERR_UNSUPPORTED, "%s handles M in [1, 2], got M=%d", what, M);
   if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
   if (N < 1 || K < group || K % group) return fail(KFB_ERR_INVALID, "K=%d is not a multiple of group_size=%d", K, group);
   if (xform < 0 || xform > 2) return fail(KFB_ERR_INVALID, "unknown activation transform %d", xform);
   if (xform != gemv::kXformNone && K > 8192) return fail(KFB_ERR_UNSUPPORTED, "fused transforms handle K <= 8192, got %d", K);
-  if (xform == gemv::kXformRmsNorm && !norm_weight) return fail(KFB_ERR_INVALID, "the RMSNorm transform needs its weight");
-  if (!x || !packed || !scales || !y) return fail(KFB_ERR_INVALID, "null pointer");
-  if (!aligned16(x) || !aligned16(packed) || (norm_weight && !aligned16(norm_weight)))
+  if (xform == gemv::kXformRmsNorm && !fu.norm_w) return fail(KFB_ERR_INVALID, "the RMSNorm transform needs its weight");
+  if (!x || !packed || !scales) return fail(KFB_ERR_INVALID, "null pointer");
+  if (!aligned16(x) || !aligned16(packed) || (fu.norm_w && !aligned16(fu.norm_w)))
     return fail(KFB_ERR_ALIGNMENT, "x, packed and the norm weight must be 16-byte aligned");
   if (flags & ~1) return fail(KFB_ERR_INVALID, "unknown flags 0x%x", flags);
-  const gemv::Fusion fu{static_cast<const __half*>(norm_weight), eps, static_cast<const __half*>(bias),
-                        static_cast<const __half*>(residual)};
   cudaStream_t s = (cudaStream_t)stream;
   return group == 128 ? gemv::pick_fused<128>(x, packed, scales, y, M, N, K, xform, flags, s, fu)
                       : gemv::pick_fused<64>(x, packed, scales, y, M, N, K, xform, flags, s, fu);
+}
+
+}  // namespace
+
+extern "C" int kfb_int4_gemv_fused(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K, int group,
+                                   int xform, const void* norm_weight, float eps, const void* bias, const void* residual,
+                                   int flags, void* stream) {
+  if (!y) return fail(KFB_ERR_INVALID, "null pointer");
+  gemv::Fusion fu = {};
+  fu.norm_w = static_cast<const __half*>(norm_weight);
+  fu.eps = eps;
+  fu.bias = static_cast<const __half*>(bias);
+  fu.residual = static_cast<const __half*>(residual);
+  return fused_common("int4_gemv_fused", x, packed, scales, y, M, N, K, group, xform, flags, stream, fu);
+}
+
+extern "C" int kfb_int4_gemv_silu_pair(const void* x, const void* packed, const void* scales, void* act_out, int M, int N, int K,
+                                       int group, int xform, const void* norm_weight, float eps, int flags, void* stream) {
+  if (!act_out) return fail(KFB_ERR_INVALID, "null pointer");
+  if (N % 2) return fail(KFB_ERR_INVALID, "int4_gemv_silu_pair needs an even number of rows (gate, up interleaved), got N=%d", N);
+  gemv::Fusion fu = {};
+  fu.norm_w = static_cast<const __half*>(norm_weight);
+  fu.eps = eps;
+  fu.epi = gemv::kEpiSiluPair;
+  return fused_common("int4_gemv_silu_pair", x, packed, scales, act_out, M, N, K, group, xform, flags, stream, fu);
+}
+
+extern "C" int kfb_int4_gemv_rope_kv(const void* x, const void* packed, const void* scales, int M, int K, int group, int xform,
+                                     const void* norm_weight, float eps, const void* cos_table, const void* sin_table,
+                                     const void* pos_dev, void* q_out, void* k_cache, void* v_cache, int H, int Hk, int D,
+                                     int Lmax, int flags, void* stream) {
+  if (H < 1 || Hk < 1 || Lmax < 1 || (D != 64 && D != 128))
+    return fail(KFB_ERR_INVALID, "int4_gemv_rope_kv: bad shape H=%d Hk=%d D=%d Lmax=%d", H, Hk, D, Lmax);
+  if (!cos_table || !sin_table || !pos_dev || !q_out || !k_cache || !v_cache) return fail(KFB_ERR_INVALID, "null pointer");
+  gemv::Fusion fu = {};
+  fu.norm_w = static_cast<const __half*>(norm_weight);
+  fu.eps = eps;
+  fu.epi = gemv::kEpiRopeKv;
+  fu.rope.cos_t = static_cast<const float*>(cos_table);
+  fu.rope.sin_t = static_cast<const float*>(sin_table);
+  fu.rope.pos = static_cast<const long long*>(pos_dev);
+  fu.rope.q_out = static_cast<__half*>(q_out);
+  fu.rope.k_cache = static_cast<__half*>(k_cache);
+  fu.rope.v_cache = static_cast<__half*>(v_cache);
+  fu.rope.H = H; fu.rope.Hk = Hk; fu.rope.D = D; fu.rope.Lmax = Lmax;
+  fu.rope.status = device_status_word();
+  if (!fu.rope.status) return fail(KFB_ERR_CUDA, "cannot resolve the device status word");
+  // y is not written by this epilogue: q_out stands in for the pointer checks of the common path
+  return fused_common("int4_gemv_rope_kv", x, packed, scales, q_out, M, (H + 2 * Hk) * D, K, group, xform, flags, stream, fu);
 }
 
 extern "C" int kfb_int4_small_batch(const void* x, const void* packed, const void* scales, void* y, int M, int N, int K,

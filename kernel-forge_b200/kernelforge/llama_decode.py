@@ -120,6 +120,11 @@ class LlamaInt4Decoder:
         self.h_loc = s.heads if self.plan is None else self.plan["q_heads"][1] - self.plan["q_heads"][0]
         self.hk_loc = s.kv_heads if self.plan is None else self.plan["kv_heads"][1] - self.plan["kv_heads"][0]
         self.inter_loc = s.intermediate if self.plan is None else self.plan["inter"][1] - self.plan["inter"][0]
+        # Batch <= 2 on one GPU: the rows of the fused qkv and gate_up matrices are stored in the order the pair
+        # epilogues of the GEMV want (ops.interleave_qkv_for_rope / interleave_gate_up), so RoPE + cache write and
+        # SiLU * up happen in the epilogue of the projection (8 kernels per layer instead of 10).  Rows are quantised
+        # independently, so this is exact; prefill reads the same matrices and undoes the order with a view.
+        self.pair_rows = self.plan is None and batch <= ops.FUSED_GEMV_MAX_M
         f16 = lambda t: t.to(self.dev, torch.float16).contiguous()
         self.embed = f16(weights["embed"])
         self.lm_head = f16(weights["lm_head"])
@@ -135,11 +140,15 @@ class LlamaInt4Decoder:
                 o, down, gate, up = o[r0:r1], down[r0:r1], gate[i0:i1], up[i0:i1]
             # q/k/v and gate/up share their input, so they are stored as ONE quantised matrix each (rows
             # concatenated: groups run along K, so this is bit-identical to quantising them separately)
+            if self.pair_rows:
+                qkv_rows, gate_up_rows = ops.interleave_qkv_for_rope(f16(q), f16(k), f16(v), d), ops.interleave_gate_up(f16(gate), f16(up))
+            else:
+                qkv_rows, gate_up_rows = torch.cat([f16(q), f16(k), f16(v)], 0), torch.cat([f16(gate), f16(up)], 0)
             self.layers.append({
                 "in_norm": f16(lw["in_norm"]), "post_norm": f16(lw["post_norm"]),
-                "qkv": _Int4(torch.cat([f16(q), f16(k), f16(v)], 0), group),
+                "qkv": _Int4(qkv_rows, group),
                 "o": _Int4(f16(o), group),
-                "gate_up": _Int4(torch.cat([f16(gate), f16(up)], 0), group),
+                "gate_up": _Int4(gate_up_rows, group),
                 "down": _Int4(f16(down), group),
             })
         self.k_cache = torch.zeros(s.layers, batch, self.hk_loc, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
@@ -223,7 +232,11 @@ class LlamaInt4Decoder:
         h = self._rms(x, L["post_norm"])
         gu = L["gate_up"](h)
         inter = self.inter_loc
-        act = torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:]
+        if self.pair_rows:
+            gu = gu.view(*gu.shape[:-1], inter, 2)
+            act = torch.nn.functional.silu(gu[..., 0]) * gu[..., 1]
+        else:
+            act = torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:]
         lead = act.shape[:-1]
         act = self._gather(act.reshape(-1, inter), "inter_bounds").reshape(*lead, self.s.intermediate)
         down = L["down"](act)
@@ -244,8 +257,13 @@ class LlamaInt4Decoder:
             h = self._rms(x, L["in_norm"])
             qkv = L["qkv"](h)
             nq, nkv = self.h_loc * s.head_dim, self.hk_loc * s.head_dim
-            q = qkv[..., :nq].reshape(b, t, self.h_loc, s.head_dim).transpose(1, 2)
-            k = qkv[..., nq:nq + nkv].reshape(b, t, self.hk_loc, s.head_dim).transpose(1, 2)
+            if self.pair_rows:   # features (j, j + D/2) sit side by side: back to the natural order
+                unpair = lambda z, heads: z.reshape(b, t, heads, s.head_dim // 2, 2).transpose(-1, -2).reshape(b, t, heads, s.head_dim)
+                q = unpair(qkv[..., :nq], self.h_loc).transpose(1, 2)
+                k = unpair(qkv[..., nq:nq + nkv], self.hk_loc).transpose(1, 2)
+            else:
+                q = qkv[..., :nq].reshape(b, t, self.h_loc, s.head_dim).transpose(1, 2)
+                k = qkv[..., nq:nq + nkv].reshape(b, t, self.hk_loc, s.head_dim).transpose(1, 2)
             v = qkv[..., nq + nkv:].reshape(b, t, self.hk_loc, s.head_dim).transpose(1, 2)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
             self.k_cache[li, :, :, :t] = k
@@ -265,28 +283,29 @@ class LlamaInt4Decoder:
     # ------------------------------------------------------------------ one decode step (graph body)
     @torch.no_grad()
     def _step_fused(self):
-        """The step for batch <= 2 on one GPU: 6 kernels per layer.  Both RMSNorms run in the prologue of the GEMV that
-        consumes them, SiLU * up in the prologue of down_proj, both residual adds in the epilogues of o_proj and
-        down_proj (ops.int4_gemv_fused); what stays separate is RoPE + cache write and the attention itself."""
+        """The step for batch <= 2 on one GPU with everything fused: 5 kernels per layer.  Both RMSNorms run in the
+        prologue of the GEMV that consumes them, RoPE + cache write and SiLU * up in the epilogue of the GEMV that
+        produces their input, both residual adds in the epilogues of o_proj and down_proj; only the attention itself
+        stays a kernel of its own."""
         s, b = self.s, self.b
         _, x = ops.embed_rmsnorm(self.tok, self.embed, self.layers[0]["in_norm"], s.rms_eps)   # x: the residual stream
         for li, L in enumerate(self.layers):
-            qkv = ops.int4_gemv_fused(x, L["qkv"].packed, L["qkv"].scales, L["qkv"].group, ops.XFORM_RMSNORM, L["in_norm"], s.rms_eps)
-            q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
+            q = ops.int4_gemv_rope_kv(x, L["qkv"].packed, L["qkv"].scales, L["qkv"].group, self.cos, self.sin, self.pos,
+                                      self.k_cache[li], self.v_cache[li], self.h_loc, L["in_norm"], s.rms_eps)
             a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len).view(b, self.h_loc * s.head_dim)
             x = ops.int4_gemv_fused(a, L["o"].packed, L["o"].scales, L["o"].group, residual=x)
-            gu = ops.int4_gemv_fused(x, L["gate_up"].packed, L["gate_up"].scales, L["gate_up"].group, ops.XFORM_RMSNORM,
-                                     L["post_norm"], s.rms_eps)
-            x = ops.int4_gemv_fused(gu, L["down"].packed, L["down"].scales, L["down"].group, ops.XFORM_SILU_MUL, residual=x)
+            act = ops.int4_gemv_silu_pair(x, L["gate_up"].packed, L["gate_up"].scales, L["gate_up"].group, L["post_norm"], s.rms_eps)
+            x = ops.int4_gemv_fused(act, L["down"].packed, L["down"].scales, L["down"].group, residual=x)
         h, _ = ops.add_rmsnorm(x, self.final_norm, s.rms_eps)
         ops.lm_head_argmax(h, self.lm_head, self.step_logits, self.best)
         ops.decode_finalize(self.best, self.tok, self.pos, self.kv_len)
 
     @torch.no_grad()
     def _step(self):
-        """One decode step: 10 or 11 kernels per layer (norm, qkv, rope + cache write, attention (+ merge when the keys
-        are split), o, add + norm, gate_up, silu * up, down; the last residual add is fused into the next layer's
-        norm; the embedding gather is fused into the first norm), then final norm, lm_head with fused argmax, and
+        """One decode step: 9 or 10 kernels per layer (add + norm, qkv, rope + cache write, attention (+ merge when the
+        keys are split), o, add + norm, gate_up, silu * up, down; the last residual add is fused into the next layer's
+        norm; the embedding gather is fused into the first norm) -- 7 or 8 at batch <= 2 on one GPU, where rope +
+        cache write and silu * up run in the epilogues of the qkv and gate_up GEMVs -- then final norm, lm_head with fused argmax, and
         one kernel that publishes the token and advances position and KV length.  Every kernel of the step is one
         of this library's: no torch or cuBLAS kernel is left in the graph."""
         if self.plan is None and self.b <= ops.FUSED_GEMV_MAX_M and self.fused:
@@ -298,13 +317,20 @@ class LlamaInt4Decoder:
                 h, x = ops.embed_rmsnorm(self.tok, self.embed, L["in_norm"], s.rms_eps)   # [B, hidden] each
             else:
                 h, x = ops.add_rmsnorm(x, L["in_norm"], s.rms_eps, res)
-            qkv = L["qkv"](h)
-            q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
+            if self.pair_rows:
+                q = ops.int4_gemv_rope_kv(h, L["qkv"].packed, L["qkv"].scales, L["qkv"].group, self.cos, self.sin, self.pos,
+                                          self.k_cache[li], self.v_cache[li], self.h_loc)
+            else:
+                qkv = L["qkv"](h)
+                q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
             a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len)
             a = self._gather(a.view(b, self.h_loc * s.head_dim), "attn_bounds")
             o = self._gather(L["o"](a), "hidden_bounds")
             h, x = ops.add_rmsnorm(x, L["post_norm"], s.rms_eps, o)
-            act = self._gather(ops.silu_mul(L["gate_up"](h)), "inter_bounds")
+            if self.pair_rows:
+                act = ops.int4_gemv_silu_pair(h, L["gate_up"].packed, L["gate_up"].scales, L["gate_up"].group)
+            else:
+                act = self._gather(ops.silu_mul(L["gate_up"](h)), "inter_bounds")
             res = self._gather(L["down"](act), "hidden_bounds")
         h, x = ops.add_rmsnorm(x, self.final_norm, s.rms_eps, res)
         ops.lm_head_argmax(h, self.lm_head, self.step_logits, self.best)

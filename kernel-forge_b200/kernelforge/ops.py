@@ -132,6 +132,60 @@ def int4_gemv_fused(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
     return y
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Rows (gate_0, up_0, gate_1, up_1, ...): the row order int4_gemv_silu_pair expects (quantise the result)."""
+    return torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1])
+
+
+def interleave_qkv_for_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """The row order int4_gemv_rope_kv expects: per q head, then per k head, rows (j, j + D/2) adjacent; v unchanged."""
+    def pairs(w):
+        heads = w.shape[0] // head_dim
+        w4 = w.reshape(heads, 2, head_dim // 2, w.shape[1])          # [head, lo / hi half, j, K]
+        return w4.transpose(1, 2).reshape(w.shape[0], w.shape[1])    # [head, j, lo / hi, K]
+    return torch.cat([pairs(q), pairs(k), v], dim=0)
+
+
+def int4_gemv_silu_pair(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
+                        norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> torch.Tensor:
+    """act[M, N/2] = silu(gate . x) * (up . x) for a weight whose rows were interleaved with interleave_gate_up (M <= 2).
+    With `norm_weight`, x is RMS-normalised in the kernel's prologue first."""
+    _check_int4(x, packed, scales, group_size)
+    m, k = x.shape
+    n = packed.shape[0]
+    act = torch.empty(m, n // 2, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_silu_pair(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), act.data_ptr(), m, n, k,
+                                                        int(group_size), XFORM_NONE if norm_weight is None else XFORM_RMSNORM,
+                                                        None if norm_weight is None else norm_weight.data_ptr(), float(eps), 0,
+                                                        _capi.stream_ptr(x.device)))
+    return act
+
+
+def int4_gemv_rope_kv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int, cos: torch.Tensor,
+                      sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int,
+                      norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> torch.Tensor:
+    """The fused q/k/v projection of one decode position with RoPE and the KV-cache write in its epilogue (weight rows in
+    the order of interleave_qkv_for_rope, M <= 2).  Returns the rotated q [B, H, 1, D]; row `pos` of the caches is written.
+    With `norm_weight`, x is RMS-normalised in the kernel's prologue first."""
+    _check_int4(x, packed, scales, group_size)
+    b, k = x.shape
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape and k_cache.shape[0] == b):
+        raise ValueError("k_cache / v_cache must be contiguous [B, Hk, Lmax, D] tensors of the same shape")
+    if packed.shape[0] != (heads + 2 * k_cache.shape[1]) * k_cache.shape[3]:
+        raise ValueError(f"the fused qkv weight has {packed.shape[0]} rows, expected (H + 2 Hk) * D")
+    hk, lmax, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    q = torch.empty(b, heads, 1, d, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_rope_kv(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), b, k, int(group_size),
+                                                      XFORM_NONE if norm_weight is None else XFORM_RMSNORM,
+                                                      None if norm_weight is None else norm_weight.data_ptr(), float(eps),
+                                                      cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
+                                                      q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), heads, hk, d, lmax, 0,
+                                                      _capi.stream_ptr(x.device)))
+    return q
+
+
 def int4_small_batch(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
     """The GEMV's weight-streaming kernel for M in [1, SMALL_BATCH_MAX_M]: every block of 8 batch rows is one more
     MMA on the already unpacked weight fragment.  Not in the reference (its GEMV stops at M = 8)."""

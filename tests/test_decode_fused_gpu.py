@@ -179,3 +179,77 @@ def test_int4_linear_bias_goes_through_the_fused_epilogue():
             assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
         else:
             assert torch.equal(got, want)
+
+
+def _cuda_core_gemv(x, qw, group=128):
+    from kernelforge import _capi
+    n, k = qw.packed.shape[0], x.shape[1]
+    y = torch.empty(x.shape[0], n, dtype=torch.float16, device="cuda")
+    _capi.check(_capi.lib().kfb_int4_gemv(x.data_ptr(), qw.packed.data_ptr(), qw.scales.data_ptr(), y.data_ptr(),
+                                          x.shape[0], n, k, group, 2, _capi.stream_ptr(torch.device("cuda", 0))))
+    return y
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("inter,k,group", [(5632, 2048, 128), (8960, 1536, 128), (50, 256, 64)])
+def test_silu_pair_epilogue_matches_gemv_then_silu_mul(m, inter, k, group):
+    """The gate_up GEMV with SiLU * up in its epilogue (rows interleaved gate_p, up_p) against the plain GEMV on the
+    concatenated matrix followed by the separate kernel: bit for bit."""
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(inter + k + m)
+    gate, up = (torch.randn(inter, k, generator=g) * 0.05).half().cuda(), (torch.randn(inter, k, generator=g) * 0.05).half().cuda()
+    x = torch.randn(m, k, generator=g).half().cuda()
+    natural = kq.quantize_weight(torch.cat([gate, up], 0), group)
+    paired = kq.quantize_weight(ops.interleave_gate_up(gate, up), group)
+    want = ops.silu_mul(_cuda_core_gemv(x, natural, group))
+    got = ops.int4_gemv_silu_pair(x, paired.packed, paired.scales, group)
+    assert got.shape == (m, inter) and torch.equal(got, want)
+    # with the RMSNorm prologue: equal up to the summation order of mean(x^2)
+    w = (1 + 0.1 * torch.randn(k, generator=g)).half().cuda()
+    normed, _ = ops.add_rmsnorm(x, w, 1e-5)
+    want = ops.silu_mul(_cuda_core_gemv(normed, natural, group)).float()
+    got = ops.int4_gemv_silu_pair(x, paired.packed, paired.scales, group, w, 1e-5).float()
+    assert (got - want).abs().max().item() <= 4e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("b", [1, 2])
+@pytest.mark.parametrize("h,hk,d,k", [(32, 4, 64, 2048), (12, 2, 128, 1536), (2, 1, 64, 256)])
+def test_rope_kv_epilogue_matches_gemv_then_rope_kv_write(b, h, hk, d, k):
+    """The fused q/k/v GEMV with RoPE + cache write in its epilogue against the plain GEMV followed by
+    ops.rope_kv_write: q, the written cache row and the untouched rest of the caches, bit for bit."""
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(h + d + b)
+    lmax, pos = 24, 9
+    wq, wk, wv = ((torch.randn(n, k, generator=g) * 0.05).half().cuda() for n in (h * d, hk * d, hk * d))
+    x = torch.randn(b, k, generator=g).half().cuda()
+    ang = torch.outer(torch.arange(lmax, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d)))
+    ang = torch.cat([ang, ang], -1)
+    cos, sin = ang.cos().cuda(), ang.sin().cuda()
+    pos_dev = torch.tensor([pos], dtype=torch.long, device="cuda")
+    natural = kq.quantize_weight(torch.cat([wq, wk, wv], 0), 128)
+    paired = kq.quantize_weight(ops.interleave_qkv_for_rope(wq, wk, wv, d), 128)
+    base = torch.randn(b, hk, lmax, d, generator=g).half().cuda()
+    kc0, vc0, kc1, vc1 = base.clone(), base.clone() * 2, base.clone(), base.clone() * 2
+    q_want = ops.rope_kv_write(_cuda_core_gemv(x, natural), cos, sin, pos_dev, kc0, vc0, h)
+    q_got = ops.int4_gemv_rope_kv(x, paired.packed, paired.scales, 128, cos, sin, pos_dev, kc1, vc1, h)
+    assert torch.equal(q_got, q_want) and torch.equal(kc1, kc0) and torch.equal(vc1, vc0)
+    assert not torch.equal(kc1[:, :, pos], base[:, :, pos])
+
+
+def test_rope_kv_epilogue_stays_inside_the_cache():
+    """A position outside the cache: nothing is written, code 0x701 in the status word (then reset)."""
+    from kernelforge import _capi, quantize as kq
+    h, hk, d, k, lmax = 2, 1, 64, 256, 8
+    g = torch.Generator().manual_seed(1)
+    w = kq.quantize_weight((torch.randn((h + 2 * hk) * d, k, generator=g) * 0.05).half().cuda(), 128)
+    x = torch.randn(1, k, generator=g).half().cuda()
+    cos = torch.ones(lmax, d, device="cuda"); sin = torch.zeros(lmax, d, device="cuda")
+    kc = torch.zeros(1, hk, lmax, d, dtype=torch.float16, device="cuda"); vc = torch.zeros_like(kc)
+    dev = torch.device("cuda", 0)
+    for bad in (lmax, -1):
+        ops.int4_gemv_rope_kv(x, w.packed, w.scales, 128, cos, sin, torch.tensor([bad], dtype=torch.long, device="cuda"), kc, vc, h)
+        torch.cuda.synchronize()
+        assert _capi.device_status(dev) == 0x701
+        assert not kc.any() and not vc.any()
+        _capi.device_status_reset(dev)
+        assert _capi.device_status(dev) == 0
