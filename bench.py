@@ -514,7 +514,7 @@ def bench_decode_e2e(args, device, batch: int, weights, prompt_len=512, new_toke
     static KV cache, one CUDA graph per decode step.  Prompt = uniform random token ids (stands in for the
     reference's WikiText-2 prompt, which is not available offline).  tok/s = batch * steps / device time."""
     from kernelforge.llama_decode import TINYLLAMA_1B, LlamaInt4Decoder
-    dec = LlamaInt4Decoder(TINYLLAMA_1B, weights, device, batch, prompt_len + new_tokens + 8, tp_group=tp_group)
+    dec = LlamaInt4Decoder(TINYLLAMA_1B, weights, device, batch, prompt_len + new_tokens + 48, tp_group=tp_group)
     ids = torch.randint(0, TINYLLAMA_1B.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(0))
     t0 = time.perf_counter()
     dec.prefill(ids)
@@ -532,6 +532,22 @@ def bench_decode_e2e(args, device, batch: int, weights, prompt_len=512, new_toke
     b.record()
     b.synchronize()
     ms = a.elapsed_time(b)
+    persistent_ms = None
+    if getattr(dec, "persistent_ok", False) and not dec.persistent:
+        # the same step as ONE persistent cooperative kernel (kfb_decode_step_persistent), for comparison
+        n_p = 32   # (the cache was sized with 48 spare rows)
+        if True:
+            dec.persistent = True
+            dec.capture()
+            for _ in range(3):
+                dec.graph.replay()
+            a.record()
+            for _ in range(n_p - 3):
+                dec.graph.replay()
+            b.record()
+            b.synchronize()
+            persistent_ms = a.elapsed_time(b) / (n_p - 3)
+            dec.persistent = False
     s = TINYLLAMA_1B
     weight_bytes = s.layers * (2 * s.hidden * s.heads * s.head_dim + 2 * s.hidden * s.kv_heads * s.head_dim
                                + 3 * s.hidden * s.intermediate) * (0.5 + 2 / 128) + s.vocab * s.hidden * 2
@@ -540,6 +556,8 @@ def bench_decode_e2e(args, device, batch: int, weights, prompt_len=512, new_toke
            "steps_timed": steps, "prefill_s": prefill_s, "bytes_per_step": weight_bytes + kv_bytes,
            "hbm_gbs": (weight_bytes + kv_bytes) / (ms / steps * 1e-3) / 1e9,
            "kernels_per_step": getattr(dec, "kernels_per_step", None)}
+    if persistent_ms is not None:
+        out["persistent_kernel_ms_per_step"] = persistent_ms
     dec.release()   # the graph holds captured NCCL work when tensor-parallel: free it before any process-group teardown
     del dec
     torch.cuda.empty_cache()

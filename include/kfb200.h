@@ -155,6 +155,42 @@ int kfb_int4_gemv_rope_kv(const void* x, const void* packed, const void* scales,
                           const void* pos_dev, void* q_out, void* k_cache, void* v_cache, int H, int Hk, int D, int Lmax,
                           int flags, void* stream);
 
+/* One greedy decode step of a Llama-architecture model (INT4 decoder linears of kfb_quantize_pack's format, fp16
+ * lm_head, RMSNorm, rotate-half RoPE, SiLU MLP, grouped-query attention over a static KV cache) as ONE persistent
+ * cooperative kernel: batch 1 or 2, head_dim 64, one GPU.  It replaces the whole body of the reference's decode step
+ * (bench/e2e_model.py:97-141: ~50 kernels per layer there) up to and including the lm_head and the argmax keys;
+ * kfb_decode_finalize publishes the token afterwards.  No counterpart in the reference.
+ *   layer_table: DEVICE array of `layers` entries of 12 pointers each, in this order: qkv packed, qkv scales, o packed,
+ *     o scales, gate_up packed, gate_up scales, down packed, down scales, input RMSNorm weight, post-attention RMSNorm
+ *     weight, K cache, V cache ([batch, kv_heads, max_len, head_dim] fp16).  The fused qkv matrix has its rows in the
+ *     order of kfb_int4_gemv_rope_kv, the fused gate_up matrix in the order of kfb_int4_gemv_silu_pair (a private row
+ *     order of the public packed format, chosen when the model is built).
+ *   tok [batch] int64, pos [1] int64 (the cache row this step writes), kv_len [batch] int32 (valid keys including that
+ *     row) are read on the device; logits [batch, vocab] fp16 and best [batch] (the argmax keys of kfb_fp16_gemv_argmax,
+ *     which must be 0 before the call) are written.
+ *   workspace: kfb_decode_step_ws_bytes bytes, 16-byte aligned, contents irrelevant; calls that share it must not overlap.
+ * Every in-kernel wait is bounded: an expired wait records 0x901 (grid barrier) or 0x902 (weight ring) in the device
+ * status word and the kernel returns; a position outside [0, max_len) records 0x701 and nothing is written. */
+typedef struct kfb_decode_step_t {
+  const void* layer_table;
+  int layers, batch, hidden, heads, kv_heads, head_dim, intermediate, vocab, max_len, group;
+  float rms_eps;
+  const void* embed;       /* fp16 [vocab, hidden] */
+  const void* final_norm;  /* fp16 [hidden] */
+  const void* lm_head;     /* fp16 [vocab, hidden] */
+  const void* cos_table;   /* fp32 [max_len, head_dim] */
+  const void* sin_table;
+  const void* tok;
+  const void* pos;
+  const void* kv_len;
+  void* logits;
+  void* best;
+  void* workspace;
+  size_t workspace_bytes;
+} kfb_decode_step_t;
+size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate);
+int kfb_decode_step_persistent(const kfb_decode_step_t* step, void* stream);
+
 /* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
  * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),
  * K % group == 0.  Weights are dequantised into swizzled shared memory and multiplied on

@@ -20,6 +20,19 @@ _load_error: Exception | None = None
 KFB_F16, KFB_BF16, KFB_F32 = 0, 1, 2
 _DTYPE_CODE = {torch.float16: KFB_F16, torch.bfloat16: KFB_BF16, torch.float32: KFB_F32}
 
+
+
+class DecodeStep(ctypes.Structure):
+    """kfb_decode_step_t of include/kfb200.h."""
+    _fields_ = [("layer_table", c_void_p),
+                ("layers", c_int), ("batch", c_int), ("hidden", c_int), ("heads", c_int), ("kv_heads", c_int),
+                ("head_dim", c_int), ("intermediate", c_int), ("vocab", c_int), ("max_len", c_int), ("group", c_int),
+                ("rms_eps", c_float),
+                ("embed", c_void_p), ("final_norm", c_void_p), ("lm_head", c_void_p), ("cos_table", c_void_p),
+                ("sin_table", c_void_p), ("tok", c_void_p), ("pos", c_void_p), ("kv_len", c_void_p),
+                ("logits", c_void_p), ("best", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+
+
 _SIGNATURES = {
     "kfb_version": (c_int, []),
     "kfb_last_error": (c_char_p, []),
@@ -59,6 +72,8 @@ _SIGNATURES = {
     "kfb_fp16_gemv_argmax": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "kfb_decode_finalize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "kfb_embed_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
+    "kfb_decode_step_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "kfb_decode_step_persistent": (c_int, [ctypes.POINTER(DecodeStep), c_void_p]),
     "kfb_flash_attn_decode_kvlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_float, ctypes.POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
     "kfb_flash_attn_decode_partial_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]),

@@ -52,6 +52,32 @@ def test_prefill_and_graph_decode_logits_match_fp32_model(batch):
     assert torch.equal(toks[:, 0].cpu(), pre[:, -1].argmax(-1))
 
 
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("prompt_len", [1, 24, 200])
+def test_persistent_step_matches_the_step_of_separate_kernels(batch, prompt_len):
+    """The one-kernel decode step against the step of separate kernels on the same weights and cache: same arithmetic up
+    to summation order (and FP32 instead of fp16 attention probabilities), so the logits agree far inside the bound
+    against the FP32 model, and both choose the same tokens."""
+    base, _ = build()
+    steps = 10
+    ids = torch.randint(0, 320, (batch, prompt_len), generator=torch.Generator().manual_seed(5 + prompt_len))
+    a = LlamaInt4Decoder.from_hf(base, "cuda", batch, max_len=prompt_len + steps + 3)
+    assert a.persistent_ok
+    a.persistent = True
+    b = LlamaInt4Decoder.from_hf(base, "cuda", batch, max_len=prompt_len + steps + 3)
+    assert not b.persistent
+    a.prefill(ids); b.prefill(ids)
+    ta, la = a.decode(steps, keep_logits=True)
+    tb, lb = b.decode(steps, keep_logits=True)
+    scale = lb.float().abs().max().item()
+    assert (la.float() - lb.float()).abs().max().item() <= 4e-3 * scale
+    assert torch.equal(ta, tb)
+    assert torch.equal(a.pos, b.pos) and torch.equal(a.kv_len, b.kv_len)
+    # the cache rows written by the two paths agree to fp16 rounding of the same projections
+    assert (a.k_cache.float() - b.k_cache.float()).abs().max().item() <= 4e-3 * b.k_cache.float().abs().max().item()
+    assert (a.v_cache.float() - b.v_cache.float()).abs().max().item() <= 4e-3 * b.v_cache.float().abs().max().item()
+
+
 def test_graph_tokens_equal_eager_tokens():
     base, _ = build(layers=2)
     ids = torch.randint(0, 320, (2, 16), generator=torch.Generator().manual_seed(4))
@@ -115,3 +141,26 @@ def test_tinyllama_architecture_logits_at_size():
     print(f"PARITY tinyllama-arch 22 layers, 768 tokens: logit scale {scale:.3f}  max_abs_err prefill {err_pre:.3e} "
           f"decode {err_dec:.3e}  bound {2e-2 * scale:.3e}  greedy-token agreement {agree:.4f}")
     assert err_pre <= 2e-2 * scale and err_dec <= 2e-2 * scale
+
+
+def test_persistent_step_at_tinyllama_size():
+    """The persistent step on the TinyLlama-1.1B shape (22 layers, 148 CTAs with 2-chunk gate_up slices, 32 key splits)
+    against the step of separate kernels: logits within 4e-3 of the logit scale, same tokens, over 12 steps from a
+    300-token prompt."""
+    from kernelforge.llama_decode import TINYLLAMA_1B
+    ids = torch.randint(0, 32000, (1, 300), generator=torch.Generator().manual_seed(11))
+    outs = []
+    for persistent in (True, False):
+        dec = LlamaInt4Decoder.random_init(TINYLLAMA_1B, "cuda", 1, 320, seed=1)
+        dec.persistent = persistent
+        dec.prefill(ids)
+        outs.append(dec.decode(12, keep_logits=True))
+        dec.release()
+        del dec
+        torch.cuda.empty_cache()
+    (ta, la), (tb, lb) = outs
+    scale = lb.float().abs().max().item()
+    err = (la.float() - lb.float()).abs().max().item()
+    print(f"PARITY persistent step vs separate kernels, tinyllama-arch: max_abs_diff {err:.3e} logit scale {scale:.3f}")
+    assert err <= 4e-3 * scale
+    assert torch.equal(ta, tb)
