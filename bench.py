@@ -479,6 +479,21 @@ def bench_int4(args, world, device, m, n, k, group=128, stack=1, pdl=True) -> di
                 out[name] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
             except Exception as exc:  # report, never hide
                 out[name] = {"error": repr(exc)[:200]}
+        if stack == 1 and n % 16 == 0 and k % 64 == 0 and k <= 12288:
+            # the same product on the private fragment-order copy of the weight (kfb_int4_gemv_prepacked)
+            pre = [ops.prepack_int4(pw) for pw in packed]
+            for name, use_pdl in (("prepacked_graph", False), ("prepacked_graph_pdl", True)) if pdl else (("prepacked_graph", False),):
+                def launch_all(stream, use_pdl=use_pdl):
+                    with _capi.programmatic_launch(use_pdl):
+                        for i in range(copies):
+                            _capi.check(lib.kfb_int4_gemv_prepacked(x.data_ptr(), pre[i].data_ptr(), scales[i].data_ptr(), ys[i].data_ptr(),
+                                                                    m, n, k, group, None, None, stream.cuda_stream))
+                try:
+                    us = time_graph_calls(launch_all, copies, max(5, args.steps // 4), args.warmup, world, device)
+                    out[name] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
+                except Exception as exc:  # report, never hide
+                    out[name] = {"error": repr(exc)[:200]}
+            del pre
     else:
         keep = []
 

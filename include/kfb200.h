@@ -191,6 +191,30 @@ typedef struct kfb_decode_step_t {
 size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate);
 int kfb_decode_step_persistent(const kfb_decode_step_t* step, void* stream);
 
+/* A PRIVATE, PREPACKED copy of a weight in MMA-fragment order, and the M <= 8 GEMV that runs on it -- the reference's
+ * stated next step for the INT4 path (docs/phase4-notes.md:59, README.md:104: "reorder the packed weights offline so each
+ * thread loads its own MMA fragment nibbles"); nothing of it exists in the reference.  The public format stays what
+ * callers exchange; the copy has the same size (N K / 2 bytes) and is built once per weight.
+ *   kfb_int4_prepack: packed int32 [N, K/8] -> out (kfb_int4_prepack_bytes(N, K) bytes; 0 = shape not supported:
+ *     N % 16 == 0 and K % 64 == 0 are required).  Rows in blocks of 16, K in blocks of 64; block (rb, kb) is 512
+ *     contiguous bytes, lane 4 g + t of a warp owning 16 of them: the two words of row 16 rb + g and the two of row
+ *     16 rb + g + 8 that cover k in [64 kb + 16 t, 64 kb + 16 t + 16).
+ *   kfb_int4_gemv_prepacked: y[M, N] = x[M, K] W^T with the scales in the public layout (fp16 [N, K/group]); 1 <= M <= 8,
+ *     K <= 12288.  Same arithmetic contract as kfb_int4_gemv (exact integer weights, FP32 accumulation, FP32 group
+ *     scale, one rounding to fp16).
+ *     bias [N] / residual [M, N] (fp16, or NULL) are added in the epilogue like kfb_int4_gemv_fused does.
+ *   kfb_int4_gemv_prepacked_silu_pair / _rope_kv: the pair epilogues of kfb_int4_gemv_silu_pair / kfb_int4_gemv_rope_kv
+ *     (same row orders of the weight, same arguments, same roundings) for every M <= 8. */
+size_t kfb_int4_prepack_bytes(int N, int K);
+int kfb_int4_prepack(const void* packed, int N, int K, void* out, void* stream);
+int kfb_int4_gemv_prepacked(const void* x, const void* prepacked, const void* scales, void* y, int M, int N, int K,
+                            int group, const void* bias, const void* residual, void* stream);
+int kfb_int4_gemv_prepacked_silu_pair(const void* x, const void* prepacked, const void* scales, void* act_out, int M, int N,
+                                      int K, int group, void* stream);
+int kfb_int4_gemv_prepacked_rope_kv(const void* x, const void* prepacked, const void* scales, int M, int K, int group,
+                                    const void* cos_table, const void* sin_table, const void* pos_dev, void* q_out,
+                                    void* k_cache, void* v_cache, int H, int Hk, int D, int Lmax, void* stream);
+
 /* int4_gemm (csrc/gemm/dequant_gemm_tc.cu:7-28, kernels csrc/gemm/dequant_gemm_tc_kernel.cuh:55-162):
  * any M >= 1, any N >= 1 (the reference needs N % 64 == 0; N-sharding needs ragged N),
  * K % group == 0.  Weights are dequantised into swizzled shared memory and multiplied on

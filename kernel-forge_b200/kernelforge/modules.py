@@ -53,6 +53,14 @@ class KFLinearInt4(nn.Module):
         bias = self.bias if self.bias is None or x.dtype == torch.float16 else self.bias.to(x.dtype)
         return ops.int4_linear(x, self.packed, self.scales, self.group_size, bias)
 
+    def prepack_(self) -> "KFLinearInt4":
+        """Builds the private fragment-order copy of the weight (ops.prepack_weight_, keyed on the `packed` buffer; the
+        reference's stated next step, docs/phase4-notes.md:59): batches of up to 8 rows then run on it.  Costs as much
+        memory again as `packed`; state dicts are unaffected.  A no-op for shapes the copy does not support."""
+        if self.packed.is_cuda and ops.prepack_supported(self.packed) and self.in_features <= 12288:
+            ops.prepack_weight_(self.packed)
+        return self
+
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "
                 f"group_size={self.group_size}, int4")

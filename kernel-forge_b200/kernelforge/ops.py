@@ -132,6 +132,106 @@ def int4_gemv_fused(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
     return y
 
 
+# ----------------------------------------------------------------------------------------------------------------
+# private prepacked weight cache (the reference's stated next step, docs/phase4-notes.md:59): a copy of the packed words
+# in MMA-fragment order, keyed on the public tensor, which stays the format callers exchange
+# ----------------------------------------------------------------------------------------------------------------
+PREPACKED_GEMV_MAX_M = 8
+_PREPACKED: dict[int, tuple[int, torch.Tensor]] = {}
+
+
+def prepack_supported(packed: torch.Tensor) -> bool:
+    return packed.dim() == 2 and packed.shape[0] % 16 == 0 and (packed.shape[1] * 8) % 64 == 0 and packed.shape[0] >= 16
+
+
+def prepack_int4(packed: torch.Tensor) -> torch.Tensor:
+    """The fragment-order copy of a packed weight (kfb_int4_prepack): uint8 [N * K / 2], same size as `packed`."""
+    if packed.dtype != torch.int32 or not packed.is_cuda or not packed.is_contiguous() or not prepack_supported(packed):
+        raise ValueError("prepack_int4 takes a contiguous int32 CUDA tensor [N, K/8] with N % 16 == 0 and K % 64 == 0")
+    n, k = packed.shape[0], packed.shape[1] * 8
+    out = torch.empty(n * k // 2, dtype=torch.uint8, device=packed.device)
+    with _capi.on_device(packed.device):
+        _capi.check(_capi.lib().kfb_int4_prepack(packed.data_ptr(), n, k, out.data_ptr(), _capi.stream_ptr(packed.device)))
+    return out
+
+
+def prepack_weight_(packed: torch.Tensor) -> torch.Tensor:
+    """Builds (once) and caches the private fragment-order copy of `packed`; afterwards int4_linear / int4_matmul run
+    batches of up to PREPACKED_GEMV_MAX_M rows on it.  The cache entry is keyed on the public tensor (identity and
+    version counter: an in-place change of the weight rebuilds the copy) and dies with it.  Costs as much memory again
+    as the packed weight."""
+    import weakref
+    key = id(packed)
+    hit = _PREPACKED.get(key)
+    if hit is not None and hit[0] == packed._version and hit[1].device == packed.device:
+        return hit[1]
+    copy = prepack_int4(packed)
+    if hit is None:
+        weakref.finalize(packed, _PREPACKED.pop, key, None)
+    _PREPACKED[key] = (packed._version, copy)
+    return copy
+
+
+def _prepacked_for(packed: torch.Tensor):
+    hit = _PREPACKED.get(id(packed))
+    if hit is None:
+        return None
+    if hit[0] != packed._version:   # the public weight was modified in place: rebuild
+        return prepack_weight_(packed)
+    return hit[1]
+
+
+def _check_prepacked(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Tensor, group_size: int) -> tuple[int, int, int]:
+    if x.dtype != torch.float16 or not x.is_cuda or not x.is_contiguous() or x.dim() != 2:
+        raise TypeError("x must be a contiguous 2-D fp16 CUDA tensor [M, K]")
+    m, k = x.shape
+    n = scales.shape[0]
+    if prepacked.numel() * prepacked.element_size() != n * k // 2 or tuple(scales.shape) != (n, k // group_size):
+        raise ValueError("prepacked / scales do not match x: expected N * K / 2 bytes and scales [N, K / group_size]")
+    return m, n, k
+
+
+def int4_gemv_prepacked(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
+                        bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """y[M, N] = x W^T (+ bias, + residual, fp16 adds) for 1 <= M <= 8 on the fragment-order copy of the weight."""
+    m, n, k = _check_prepacked(x, prepacked, scales, group_size)
+    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_prepacked(x.data_ptr(), prepacked.data_ptr(), scales.data_ptr(), y.data_ptr(), m, n, k,
+                                                        int(group_size), None if bias is None else bias.data_ptr(),
+                                                        None if residual is None else residual.data_ptr(),
+                                                        _capi.stream_ptr(x.device)))
+    return y
+
+
+def int4_gemv_prepacked_silu_pair(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """int4_gemv_silu_pair on the fragment-order copy of the (gate/up-interleaved) weight, for M <= 8."""
+    m, n, k = _check_prepacked(x, prepacked, scales, group_size)
+    act = torch.empty(m, n // 2, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_prepacked_silu_pair(x.data_ptr(), prepacked.data_ptr(), scales.data_ptr(), act.data_ptr(),
+                                                                  m, n, k, int(group_size), _capi.stream_ptr(x.device)))
+    return act
+
+
+def int4_gemv_prepacked_rope_kv(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Tensor, group_size: int, cos: torch.Tensor,
+                                sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int) -> torch.Tensor:
+    """int4_gemv_rope_kv on the fragment-order copy of the (RoPE-pair-ordered) fused qkv weight, for M <= 8."""
+    b, n, k = _check_prepacked(x, prepacked, scales, group_size)
+    hk, lmax, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape and k_cache.shape[0] == b):
+        raise ValueError("k_cache / v_cache must be contiguous [B, Hk, Lmax, D] tensors of the same shape")
+    if n != (heads + 2 * hk) * d:
+        raise ValueError(f"the fused qkv weight has {n} rows, expected (H + 2 Hk) * D")
+    q = torch.empty(b, heads, 1, d, dtype=torch.float16, device=x.device)
+    with _capi.on_device(x.device):
+        _capi.check(_capi.lib().kfb_int4_gemv_prepacked_rope_kv(x.data_ptr(), prepacked.data_ptr(), scales.data_ptr(), b, k, int(group_size),
+                                                                cos.data_ptr(), sin.data_ptr(), pos.data_ptr(), q.data_ptr(),
+                                                                k_cache.data_ptr(), v_cache.data_ptr(), heads, hk, d, lmax,
+                                                                _capi.stream_ptr(x.device)))
+    return q
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Rows (gate_0, up_0, gate_1, up_1, ...): the row order int4_gemv_silu_pair expects (quantise the result)."""
     return torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1])
@@ -244,6 +344,12 @@ def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
         _check_int4(x, packed, scales, group_size, allow_bf16=True)
         _check_int4_storage(x, packed, scales, group_size)
         return _gemm_launch(x, packed, scales, int(group_size))
+    if x.shape[0] <= PREPACKED_GEMV_MAX_M and x.dtype == torch.float16:
+        private = _prepacked_for(packed)          # set by prepack_weight_(packed)
+        if private is not None:
+            _check_int4(x, packed, scales, group_size)
+            _check_int4_storage(x, packed, scales, group_size)
+            return int4_gemv_prepacked(x, private, scales, group_size)
     if x.shape[0] <= GEMV_MAX_M:
         return int4_gemv(x, packed, scales, group_size)
     if x.shape[0] <= 16 and _small_batch_wins(x.shape[0], packed.shape[0], x.shape[1]):

@@ -253,3 +253,42 @@ def test_rope_kv_epilogue_stays_inside_the_cache():
         assert not kc.any() and not vc.any()
         _capi.device_status_reset(dev)
         assert _capi.device_status(dev) == 0
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+def test_prepacked_gemv_epilogues_match_the_separate_kernels(m):
+    """The fragment-order GEMV with bias / residual, SiLU-pair and RoPE + cache-write epilogues (M <= 8) against the
+    plain GEMV followed by the separate kernels; the projections differ only in summation order, so the comparison
+    carries the GEMV tolerance."""
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(40 + m)
+    k, inter, h, hk, d, lmax, pos = 512, 704, 8, 2, 64, 24, 5
+    def close(a, b, what):
+        assert (a.float() - b.float()).abs().max().item() <= 4e-3 * b.float().abs().max().item(), what
+    x = torch.randn(m, k, generator=g).half().cuda()
+    # bias + residual
+    w = kq.quantize_weight((torch.randn(1024, k, generator=g) * 0.05).cuda(), 128)
+    bias, res = torch.randn(1024, generator=g).half().cuda(), torch.randn(m, 1024, generator=g).half().cuda()
+    pre = ops.prepack_int4(w.packed)
+    close(ops.int4_gemv_prepacked(x, pre, w.scales, 128, bias, res), (_cuda_core_gemv(x, w) + bias) + res, "bias + residual")
+    # SiLU pair
+    gate, up = ((torch.randn(inter, k, generator=g) * 0.05).half().cuda() for _ in range(2))
+    natural = kq.quantize_weight(torch.cat([gate, up], 0), 128)
+    paired = kq.quantize_weight(ops.interleave_gate_up(gate, up), 128)
+    close(ops.int4_gemv_prepacked_silu_pair(x, ops.prepack_int4(paired.packed), paired.scales, 128),
+          ops.silu_mul(_cuda_core_gemv(x, natural)), "silu pair")
+    # RoPE + cache write
+    wq, wk, wv = ((torch.randn(n, k, generator=g) * 0.05).half().cuda() for n in (h * d, hk * d, hk * d))
+    ang = torch.outer(torch.arange(lmax, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d)))
+    ang = torch.cat([ang, ang], -1)
+    cos, sin = ang.cos().cuda(), ang.sin().cuda()
+    pos_dev = torch.tensor([pos], dtype=torch.long, device="cuda")
+    natural = kq.quantize_weight(torch.cat([wq, wk, wv], 0), 128)
+    paired = kq.quantize_weight(ops.interleave_qkv_for_rope(wq, wk, wv, d), 128)
+    base = torch.randn(m, hk, lmax, d, generator=g).half().cuda()
+    kc0, vc0, kc1, vc1 = base.clone(), base.clone() * 2, base.clone(), base.clone() * 2
+    q_want = ops.rope_kv_write(_cuda_core_gemv(x, natural), cos, sin, pos_dev, kc0, vc0, h)
+    q_got = ops.int4_gemv_prepacked_rope_kv(x, ops.prepack_int4(paired.packed), paired.scales, 128, cos, sin, pos_dev, kc1, vc1, h)
+    close(q_got, q_want, "rope q"); close(kc1, kc0, "k cache"); close(vc1, vc0, "v cache")
+    untouched = [i for i in range(lmax) if i != pos]
+    assert torch.equal(kc1[:, :, untouched], base[:, :, untouched]) and torch.equal(vc1[:, :, untouched], (base * 2)[:, :, untouched])

@@ -186,3 +186,63 @@ def test_gemv_one_signed_activations(n, k, kind, m, group):
         err, peak, rms, floor = assert_int4_close(y, ref, f"{kind} flags{flags}")
         bias = float((y.float().cpu().numpy() - ref).mean())
         assert abs(bias) <= 0.1 * floor + 1e-6, f"systematic bias {bias:.3e} (fp16 floor {floor:.3e}) with flags {flags}"
+
+
+def test_prepack_layout_is_the_documented_permutation():
+    """kfb_int4_prepack against the layout stated in the header: block (rb, kb) = 32 lanes x 16 bytes, lane 4g + t =
+    words (row 16rb+g: 2), (row 16rb+g+8: 2) covering k in [64kb + 16t, +16).  Bit-exact."""
+    rng = np.random.default_rng(5)
+    n, k = 48, 192
+    packed = rng.integers(-2**31, 2**31 - 1, size=(n, k // 8), dtype=np.int64).astype(np.int32)
+    got = ops.prepack_int4(torch.from_numpy(packed).cuda()).cpu().numpy().view(np.int32)
+    want = packed.reshape(n // 16, 2, 8, k // 64, 4, 2).transpose(0, 3, 2, 4, 1, 5).reshape(-1)   # [rb, kb, g, t, half, word]
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("n,k", [(5632, 2048), (2048, 5632), (1536, 8960), (8960, 1536), (256, 1536), (16, 64 * 2), (48, 128 * 3),
+                                 (32000, 2048)])
+def test_prepacked_gemv_against_the_oracle(n, k, m, group):
+    """The M <= 8 GEMV on the fragment-order copy of the weight: same bound as the other GEMV kernels, against the FP32
+    oracle, including one-signed activations (no systematic bias: the weights enter the MMA as exact integers)."""
+    if k % group:
+        pytest.skip("K is not a multiple of the group size")
+    for kind in ("randn", "abs"):
+        rng = np.random.default_rng(n + k + m + group)
+        w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+        from oracle import kf_oracle as ko
+        packed, scales = ko.quantize_weight(w, group)
+        x = rng.standard_normal((m, k), dtype=np.float32)
+        x = (np.abs(x) if kind == "abs" else x).astype(np.float16)
+        ref = x.astype(np.float32) @ ko.dequantize(packed, scales, group, np.float32).T
+        ps, ss, xs = torch.from_numpy(packed).cuda(), torch.from_numpy(scales).cuda(), torch.from_numpy(x).cuda()
+        y = ops.int4_gemv_prepacked(xs, ops.prepack_int4(ps), ss, group)
+        err, peak, rms, floor = assert_int4_close(y, ref, f"prepacked {kind} n{n} k{k} m{m} g{group}")
+        if n * m >= 4096:   # (the mean of a handful of rounding errors says nothing)
+            bias = float((y.float().cpu().numpy() - ref).mean())
+            assert abs(bias) <= 0.1 * floor + 1e-6
+
+
+def test_prepacked_cache_follows_the_public_tensor():
+    """ops.prepack_weight_ keys the private copy on the public tensor: int4_linear then runs small batches on it, an
+    in-place change of the weight rebuilds it, and the entry dies with the tensor."""
+    from kernelforge import quantize as kq
+    g = torch.Generator().manual_seed(2)
+    qw = kq.quantize_weight((torch.randn(512, 256, generator=g) * 0.02).cuda(), 128)
+    x = torch.randn(3, 256, generator=g).half().cuda()
+    before = ops.int4_linear(x, qw.packed, qw.scales, 128)
+    ops.prepack_weight_(qw.packed)
+    assert id(qw.packed) in ops._PREPACKED
+    after = ops.int4_linear(x, qw.packed, qw.scales, 128)
+    assert (after.float() - before.float()).abs().max().item() <= 2e-3 * before.float().abs().max().item()
+    other = kq.quantize_weight((torch.randn(512, 256, generator=g) * 0.02).cuda(), 128)
+    qw.packed.copy_(other.packed)   # the version counter moves: the copy is rebuilt on the next call
+    changed = ops.int4_linear(x, qw.packed, other.scales, 128)
+    want = ops.int4_gemv(x, other.packed, other.scales, 128)
+    assert (changed.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
+    key = id(qw.packed)
+    del qw
+    import gc
+    gc.collect()
+    assert key not in ops._PREPACKED
