@@ -479,21 +479,6 @@ def bench_int4(args, world, device, m, n, k, group=128, stack=1, pdl=True) -> di
                 out[name] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
             except Exception as exc:  # report, never hide
                 out[name] = {"error": repr(exc)[:200]}
-        if stack == 1 and n % 16 == 0 and k % 64 == 0 and k <= 12288:
-            # the same product on the private fragment-order copy of the weight (kfb_int4_gemv_prepacked)
-            pre = [ops.prepack_int4(pw) for pw in packed]
-            for name, use_pdl in (("prepacked_graph", False), ("prepacked_graph_pdl", True)) if pdl else (("prepacked_graph", False),):
-                def launch_all(stream, use_pdl=use_pdl):
-                    with _capi.programmatic_launch(use_pdl):
-                        for i in range(copies):
-                            _capi.check(lib.kfb_int4_gemv_prepacked(x.data_ptr(), pre[i].data_ptr(), scales[i].data_ptr(), ys[i].data_ptr(),
-                                                                    m, n, k, group, None, None, stream.cuda_stream))
-                try:
-                    us = time_graph_calls(launch_all, copies, max(5, args.steps // 4), args.warmup, world, device)
-                    out[name] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
-                except Exception as exc:  # report, never hide
-                    out[name] = {"error": repr(exc)[:200]}
-            del pre
     else:
         keep = []
 
@@ -503,6 +488,23 @@ def bench_int4(args, world, device, m, n, k, group=128, stack=1, pdl=True) -> di
                 keep.append(ops.int4_matmul(x, packed[i], scales[i], group))
         us = time_graph_calls(launch_all, copies, max(5, args.steps // 4), args.warmup, world, device)
         out["graph"] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
+    if m <= ops.PREPACKED_GEMV_MAX_M and stack == 1 and n % 16 == 0 and k % 64 == 0 and k <= 12288:
+        # the same product on the private fragment-order copy of the weight (kfb_int4_gemv_prepacked, what int4_linear
+        # runs once ops.prepack_weight_ has been called on the packed tensor)
+        pre = [ops.prepack_int4(pw) for pw in packed]
+        yp = [torch.empty(m, n, dtype=torch.float16, device=device) for _ in range(copies)]
+        for name, use_pdl in (("prepacked_graph", False), ("prepacked_graph_pdl", True)) if pdl else (("prepacked_graph", False),):
+            def launch_pre(stream, use_pdl=use_pdl):
+                with _capi.programmatic_launch(use_pdl):
+                    for i in range(copies):
+                        _capi.check(lib.kfb_int4_gemv_prepacked(x.data_ptr(), pre[i].data_ptr(), scales[i].data_ptr(), yp[i].data_ptr(),
+                                                                m, n, k, group, None, None, stream.cuda_stream))
+            try:
+                us = time_graph_calls(launch_pre, copies, max(5, args.steps // 4), args.warmup, world, device)
+                out[name] = {"gbs": nbytes / (us * 1e-6) / 1e9, "us_per_call": us}
+            except Exception as exc:  # report, never hide
+                out[name] = {"error": repr(exc)[:200]}
+        del pre, yp
     best = min((v["us_per_call"] for v in out.values() if isinstance(v, dict) and "us_per_call" in v), default=None)
     out["us_per_call"] = best
     if best:

@@ -191,7 +191,7 @@ typedef struct kfb_decode_step_t {
 size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate);
 int kfb_decode_step_persistent(const kfb_decode_step_t* step, void* stream);
 
-/* A PRIVATE, PREPACKED copy of a weight in MMA-fragment order, and the M <= 8 GEMV that runs on it -- the reference's
+/* A PRIVATE, PREPACKED copy of a weight in MMA-fragment order, and the M <= 32 GEMV that runs on it -- the reference's
  * stated next step for the INT4 path (docs/phase4-notes.md:59, README.md:104: "reorder the packed weights offline so each
  * thread loads its own MMA fragment nibbles"); nothing of it exists in the reference.  The public format stays what
  * callers exchange; the copy has the same size (N K / 2 bytes) and is built once per weight.
@@ -199,12 +199,12 @@ int kfb_decode_step_persistent(const kfb_decode_step_t* step, void* stream);
  *     N % 16 == 0 and K % 64 == 0 are required).  Rows in blocks of 16, K in blocks of 64; block (rb, kb) is 512
  *     contiguous bytes, lane 4 g + t of a warp owning 16 of them: the two words of row 16 rb + g and the two of row
  *     16 rb + g + 8 that cover k in [64 kb + 16 t, 64 kb + 16 t + 16).
- *   kfb_int4_gemv_prepacked: y[M, N] = x[M, K] W^T with the scales in the public layout (fp16 [N, K/group]); 1 <= M <= 8,
- *     K <= 12288.  Same arithmetic contract as kfb_int4_gemv (exact integer weights, FP32 accumulation, FP32 group
+ *   kfb_int4_gemv_prepacked: y[M, N] = x[M, K] W^T with the scales in the public layout (fp16 [N, K/group]); 1 <= M <= 32
+ *     (flat in M up to 8, then 2 or 4 MMAs per unpacked fragment), K <= 12288.  Same arithmetic contract as kfb_int4_gemv (exact integer weights, FP32 accumulation, FP32 group
  *     scale, one rounding to fp16).
  *     bias [N] / residual [M, N] (fp16, or NULL) are added in the epilogue like kfb_int4_gemv_fused does.
  *   kfb_int4_gemv_prepacked_silu_pair / _rope_kv: the pair epilogues of kfb_int4_gemv_silu_pair / kfb_int4_gemv_rope_kv
- *     (same row orders of the weight, same arguments, same roundings) for every M <= 8. */
+ *     (same row orders of the weight, same arguments, same roundings) for M <= 32. */
 size_t kfb_int4_prepack_bytes(int N, int K);
 int kfb_int4_prepack(const void* packed, int N, int K, void* out, void* stream);
 int kfb_int4_gemv_prepacked(const void* x, const void* prepacked, const void* scales, void* y, int M, int N, int K,

@@ -1,4 +1,4 @@
-// INT4 GEMV for M <= 8 on a PRIVATE, PREPACKED copy of the weights in MMA-fragment order.
+// INT4 GEMV for M <= 32 on a PRIVATE, PREPACKED copy of the weights in MMA-fragment order.
 //
 // The reference names this as its next step for the INT4 path: reorder the packed weights offline so that every thread
 // loads exactly the nibbles of its own MMA fragment and no shared-memory tile is needed (docs/phase4-notes.md:59,
@@ -21,7 +21,8 @@
 // Arithmetic: nibble pairs become exact fp16 integers ((w >> 4s) & 0x000F000F) | 0x64006400 = 1024 + u, minus 1032 in
 // fp16 (exact) = q; mma.sync m16n8k16 with FP32 accumulation, one accumulator per scale group, scaled in FP32 (one
 // fp16 scale per row and group), K split over the warps of a CTA with a fixed-order shared-memory reduction, one
-// rounding to fp16.  The batch is the N = 8 of the MMA (rows past M are zero), so 1 <= M <= 8 cost the same.
+// rounding to fp16.  The batch is the N = 8 of the MMA (rows past M are zero), so 1 <= M <= 8 cost the same; 9 <= M <= 32
+// run 2 or 4 MMAs per unpacked fragment.
 #include "common.cuh"
 #include "int4_epilogue.cuh"
 
@@ -68,13 +69,14 @@ __global__ void prepack_kernel(const uint32_t* __restrict__ packed, uint4* __res
 // One CTA = kWarps warps = RB row blocks x KS splits of K (RB * KS = kWarps).  G: group size.  NB: the k blocks a warp
 // holds in registers (its whole share of K: every weight byte of the call is requested before the first is used).
 // EPI: what becomes of each pair of adjacent result rows (int4_epilogue.cuh); kEpiNone stores them (+ bias, + residual).
-template <int KS, int G, int NB, int EPI>
+// MB: blocks of 8 batch rows (the N of the MMA): every unpacked A fragment feeds MB MMAs.
+template <int KS, int G, int NB, int EPI, int MB>
 __global__ void __launch_bounds__(kThreads)
 int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf, const __half* __restrict__ scales,
                       __half* __restrict__ y, int M, int N, int K, const gemv::Fusion fu) {
   constexpr int RB = kWarps / KS;
   constexpr int kBlocksPerGroup = G / 64;
-  __shared__ float red[kWarps][16][8];
+  __shared__ float red[kWarps][16][8 * MB];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -97,44 +99,62 @@ int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf
   pdl_wait();
   pdl_launch_dependents();
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc[MB][4];
+#pragma unroll
+  for (int j = 0; j < MB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   if (live) {
     const __half* srow0 = scales + (size_t)(rb * 16 + g) * SG;
     const __half* srow1 = srow0 + (size_t)8 * SG;
-    const __half* xrow = x + (size_t)g * K + 16 * t;   // batch row g of the B fragment (valid when g < M)
-    const bool has_x = g < M;
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    const __half* xrow = x + (size_t)g * K + 16 * t;   // batch row 8 j + g of B fragment j (valid when 8 j + g < M)
+    float c[MB][4];
+#pragma unroll
+    for (int j = 0; j < MB; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
       const int kb = kb0 + i;
       if (kb < kb1) {
-        uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
-        if (has_x) {
-          xa = *reinterpret_cast<const uint4*>(xrow + (size_t)kb * 64);        // k = 64 kb + 16 t + [0, 8)
-          xb = *reinterpret_cast<const uint4*>(xrow + (size_t)kb * 64 + 8);    // k = 64 kb + 16 t + [8, 16)
+        uint32_t xs0[MB][4], xs1[MB][4];
+#pragma unroll
+        for (int j = 0; j < MB; ++j) {
+          uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+          if (8 * j + g < M) {
+            const __half* xp = xrow + (size_t)(8 * j) * K + (size_t)kb * 64;
+            xa = *reinterpret_cast<const uint4*>(xp);        // k = 64 kb + 16 t + [0, 8)
+            xb = *reinterpret_cast<const uint4*>(xp + 8);    // k = 64 kb + 16 t + [8, 16)
+          }
+          xs0[j][0] = xa.x; xs0[j][1] = xa.y; xs0[j][2] = xa.z; xs0[j][3] = xa.w;
+          xs1[j][0] = xb.x; xs1[j][1] = xb.y; xs1[j][2] = xb.z; xs1[j][3] = xb.w;
         }
-        const uint32_t xs0[4] = {xa.x, xa.y, xa.z, xa.w}, xs1[4] = {xb.x, xb.y, xb.z, xb.w};
         const uint4 w = wbuf[i];
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
-          mma16816(c, pair_q(w.x, s), pair_q(w.z, s), pair_q(w.y, s), pair_q(w.w, s), xs0[s], xs1[s]);
+        for (int s = 0; s < 4; ++s) {
+          const uint32_t a0 = pair_q(w.x, s), a1 = pair_q(w.z, s), a2 = pair_q(w.y, s), a3 = pair_q(w.w, s);
+#pragma unroll
+          for (int j = 0; j < MB; ++j) mma16816(c[j], a0, a1, a2, a3, xs0[j][s], xs1[j][s]);
+        }
         if ((kb + 1) % kBlocksPerGroup == 0) {   // end of a scale group
           const int grp = kb / kBlocksPerGroup;
           const float s0 = __half2float(srow0[grp]), s1 = __half2float(srow1[grp]);
-          acc[0] = fmaf(s0, c[0], acc[0]); acc[1] = fmaf(s0, c[1], acc[1]);
-          acc[2] = fmaf(s1, c[2], acc[2]); acc[3] = fmaf(s1, c[3], acc[3]);
-          c[0] = c[1] = c[2] = c[3] = 0.f;
+#pragma unroll
+          for (int j = 0; j < MB; ++j) {
+            acc[j][0] = fmaf(s0, c[j][0], acc[j][0]); acc[j][1] = fmaf(s0, c[j][1], acc[j][1]);
+            acc[j][2] = fmaf(s1, c[j][2], acc[j][2]); acc[j][3] = fmaf(s1, c[j][3], acc[j][3]);
+            c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+          }
         }
       }
     }
   }
-  // (rows g, g + 8) x (batch 2t, 2t + 1) of this warp's share of K
-  red[warp][g][2 * t] = acc[0]; red[warp][g][2 * t + 1] = acc[1];
-  red[warp][g + 8][2 * t] = acc[2]; red[warp][g + 8][2 * t + 1] = acc[3];
+  // (rows g, g + 8) x (batch 8 j + 2t, + 1) of this warp's share of K
+#pragma unroll
+  for (int j = 0; j < MB; ++j) {
+    red[warp][g][8 * j + 2 * t] = acc[j][0]; red[warp][g][8 * j + 2 * t + 1] = acc[j][1];
+    red[warp][g + 8][8 * j + 2 * t] = acc[j][2]; red[warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+  }
   __syncthreads();
   // fixed-order sum over the K splits; thread -> (row block of the CTA, pair of rows, batch column)
-  for (int idx = threadIdx.x; idx < RB * 8 * 8; idx += kThreads) {
-    const int b = idx >> 6, pr = (idx >> 3) & 7, n = idx & 7;
+  for (int idx = threadIdx.x; idx < RB * 8 * 8 * MB; idx += kThreads) {
+    const int n = idx % (8 * MB), pr = (idx / (8 * MB)) & 7, b = idx / (64 * MB);
     const int row_block = blockIdx.x * RB + b;
     if (row_block < n_rb && n < M) {
       float v0 = 0.f, v1 = 0.f;
@@ -148,13 +168,23 @@ int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf
   }
 }
 
-template <int KS, int G, int NB, int EPI>
-int launch(const void* x, const void* wf, const void* scales, void* y, int M, int N, int K, cudaStream_t stream, const gemv::Fusion& fu) {
+template <int KS, int G, int NB, int EPI, int MB>
+int launch_mb(const void* x, const void* wf, const void* scales, void* y, int M, int N, int K, cudaStream_t stream, const gemv::Fusion& fu) {
   constexpr int RB = kWarps / KS;
   const int grid = ceil_div(N / 16, RB);
-  return launch_kernel("int4_gemv_frag_kernel", int4_gemv_frag_kernel<KS, G, NB, EPI>, dim3(grid), dim3(kThreads), 0, stream,
+  return launch_kernel("int4_gemv_frag_kernel", int4_gemv_frag_kernel<KS, G, NB, EPI, MB>, dim3(grid), dim3(kThreads), 0, stream,
                        pdl_enabled(), static_cast<const __half*>(x), static_cast<const uint4*>(wf),
                        static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, fu);
+}
+
+template <int KS, int G, int NB, int EPI>
+int launch(const void* x, const void* wf, const void* scales, void* y, int M, int N, int K, cudaStream_t stream, const gemv::Fusion& fu) {
+  if (M <= 8) return launch_mb<KS, G, NB, EPI, 1>(x, wf, scales, y, M, N, K, stream, fu);
+  if constexpr (EPI == gemv::kEpiNone || (KS == 8 && NB <= 12)) {   // (pair epilogues above M = 8: the shapes a decode step has)
+    if (M <= 16) return launch_mb<KS, G, NB, EPI, 2>(x, wf, scales, y, M, N, K, stream, fu);
+    return launch_mb<KS, G, NB, EPI, 4>(x, wf, scales, y, M, N, K, stream, fu);
+  }
+  return fail(KFB_ERR_UNSUPPORTED, "this shape is supported for M <= 8 only");
 }
 
 template <int G, int EPI>
@@ -180,7 +210,7 @@ int pick(const void* x, const void* wf, const void* scales, void* y, int M, int 
 int run(const char* what, const void* x, const void* prepacked, const void* scales, void* y, int M, int N, int K, int group,
         void* stream, const gemv::Fusion& fu) {
   if (int rc = require_sm100()) return rc;
-  if (M < 1 || M > 8) return fail(KFB_ERR_INVALID, "%s handles M in [1, 8], got M=%d", what, M);
+  if (M < 1 || M > 32) return fail(KFB_ERR_INVALID, "%s handles M in [1, 32], got M=%d", what, M);
   if (group != 64 && group != 128) return fail(KFB_ERR_INVALID, "group_size must be one of (64, 128), got %d", group);
   if (N < 16 || N % 16 || K < group || K % group || K % 64)
     return fail(KFB_ERR_UNSUPPORTED, "the fragment-order copy needs N %% 16 == 0 and K %% 64 == 0, got N=%d K=%d", N, K);

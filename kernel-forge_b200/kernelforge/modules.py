@@ -66,6 +66,17 @@ class KFLinearInt4(nn.Module):
                 f"group_size={self.group_size}, int4")
 
 
+def prepack_linears_(model: nn.Module) -> int:
+    """Calls KFLinearInt4.prepack_() on every INT4 linear of `model` (after the model is on its CUDA device: the private
+    copies are keyed on the buffers' identity).  Returns the number of layers that got a private copy."""
+    done = 0
+    for mod in model.modules():
+        if isinstance(mod, KFLinearInt4) and mod.packed.is_cuda and ops.prepack_supported(mod.packed) and mod.in_features <= 12288:
+            mod.prepack_()
+            done += 1
+    return done
+
+
 @torch.no_grad()
 def quantize_linears_(model: nn.Module, group_size: int = kq.DEFAULT_GROUP_SIZE,
                       names: tuple[str, ...] = DECODER_LINEARS) -> int:

@@ -136,7 +136,7 @@ def int4_gemv_fused(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
 # private prepacked weight cache (the reference's stated next step, docs/phase4-notes.md:59): a copy of the packed words
 # in MMA-fragment order, keyed on the public tensor, which stays the format callers exchange
 # ----------------------------------------------------------------------------------------------------------------
-PREPACKED_GEMV_MAX_M = 8
+PREPACKED_GEMV_MAX_M = 32   # measured against the dispatcher's kernels on the public format: faster at every M <= 32
 _PREPACKED: dict[int, tuple[int, torch.Tensor]] = {}
 
 
@@ -157,7 +157,7 @@ def prepack_int4(packed: torch.Tensor) -> torch.Tensor:
 
 def prepack_weight_(packed: torch.Tensor) -> torch.Tensor:
     """Builds (once) and caches the private fragment-order copy of `packed`; afterwards int4_linear / int4_matmul run
-    batches of up to PREPACKED_GEMV_MAX_M rows on it.  The cache entry is keyed on the public tensor (identity and
+    batches of up to PREPACKED_GEMV_MAX_M rows on it (M = 1: only where it measured faster, see _prepacked_wins).  The cache entry is keyed on the public tensor (identity and
     version counter: an in-place change of the weight rebuilds the copy) and dies with it.  Costs as much memory again
     as the packed weight."""
     import weakref
@@ -170,6 +170,13 @@ def prepack_weight_(packed: torch.Tensor) -> torch.Tensor:
         weakref.finalize(packed, _PREPACKED.pop, key, None)
     _PREPACKED[key] = (packed._version, copy)
     return copy
+
+
+def _prepacked_wins(m: int, n: int, k: int) -> bool:
+    """Measured (B200, graph of L2-cold calls): the fragment-order GEMV is flat in M and wins from M = 2 on at every
+    shape tried; at M = 1 it loses where N is small and K long (1536 x 8960: 8.2 against 5.3 us -- 96 CTAs of 18 K
+    blocks per warp) and is within 0.3 us elsewhere."""
+    return m >= 2 or n * 8 >= k * 5
 
 
 def _prepacked_for(packed: torch.Tensor):
@@ -193,7 +200,7 @@ def _check_prepacked(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Ten
 
 def int4_gemv_prepacked(x: torch.Tensor, prepacked: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
                         bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
-    """y[M, N] = x W^T (+ bias, + residual, fp16 adds) for 1 <= M <= 8 on the fragment-order copy of the weight."""
+    """y[M, N] = x W^T (+ bias, + residual, fp16 adds) for 1 <= M <= 32 on the fragment-order copy of the weight."""
     m, n, k = _check_prepacked(x, prepacked, scales, group_size)
     y = torch.empty(m, n, dtype=torch.float16, device=x.device)
     with _capi.on_device(x.device):
@@ -346,7 +353,7 @@ def int4_matmul(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, gro
         return _gemm_launch(x, packed, scales, int(group_size))
     if x.shape[0] <= PREPACKED_GEMV_MAX_M and x.dtype == torch.float16:
         private = _prepacked_for(packed)          # set by prepack_weight_(packed)
-        if private is not None:
+        if private is not None and _prepacked_wins(x.shape[0], packed.shape[0], x.shape[1]):
             _check_int4(x, packed, scales, group_size)
             _check_int4_storage(x, packed, scales, group_size)
             return int4_gemv_prepacked(x, private, scales, group_size)

@@ -200,11 +200,11 @@ def test_prepack_layout_is_the_documented_permutation():
 
 
 @pytest.mark.parametrize("group", [64, 128])
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(5632, 2048), (2048, 5632), (1536, 8960), (8960, 1536), (256, 1536), (16, 64 * 2), (48, 128 * 3),
                                  (32000, 2048)])
 def test_prepacked_gemv_against_the_oracle(n, k, m, group):
-    """The M <= 8 GEMV on the fragment-order copy of the weight: same bound as the other GEMV kernels, against the FP32
+    """The M <= 32 GEMV on the fragment-order copy of the weight: same bound as the other GEMV kernels, against the FP32
     oracle, including one-signed activations (no systematic bias: the weights enter the MMA as exact integers)."""
     if k % group:
         pytest.skip("K is not a multiple of the group size")

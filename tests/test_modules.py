@@ -89,3 +89,24 @@ def test_decode_with_dynamic_cache_uses_the_kernel():
     assert km.ATTN_STATS["sdpa_fallback_calls"] == before["sdpa_fallback_calls"]
     assert km.ATTN_STATS["kernelforge_calls"] == before["kernelforge_calls"] + 3
     assert (full.float() - step.float()).abs().max().item() <= 3e-2 * full.float().abs().max().item()
+
+
+@pytest.mark.gpu
+def test_prepacked_linears_give_the_same_decode_logits():
+    """modules.prepack_linears_: every INT4 linear gets its private fragment-order copy (keyed on the `packed` buffer);
+    small-batch calls then run on it and the logits agree with the public-format kernels; state dicts are unchanged."""
+    from kernelforge import ops
+    model = tiny_llama(layers=2).half().cuda()
+    km.quantize_linears_(model, 128)
+    km.enable_kf_attention(model)
+    ids = torch.randint(0, 320, (3, 1), generator=torch.Generator().manual_seed(5)).cuda()   # 3 rows: a small-batch call
+    with torch.no_grad():
+        before = model(ids).logits.float()
+    keys = set(model.state_dict().keys())
+    assert km.prepack_linears_(model) == 14
+    lin = model.model.layers[0].mlp.down_proj
+    assert id(lin.packed) in ops._PREPACKED
+    with torch.no_grad():
+        after = model(ids).logits.float()
+    assert set(model.state_dict().keys()) == keys
+    assert (after - before).abs().max().item() <= 5e-3 * before.abs().max().item()
