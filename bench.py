@@ -731,10 +731,11 @@ def single_kernel_main(args):
     torch.cuda.set_device(device)
     peaks, kind = measured_peaks()
     if args.workload == "int4_gemv":
-        n, k = (int(v) for v in args.shape.split(",")) if args.shape else (5632, 2048)
-        r = bench_int4(args, 1, device, 1, n, k)
-        print(json.dumps({"metric": "int4_linear M=1 HBM GB/s (% peak)", "unit": "GB/s", "value": r["gbs"], "n_gpus": 1,
-                          "config": {"workload": f"int4_gemv M=1 N={n} K={k} g128"}, "detail": r,
+        dims = [int(v) for v in args.shape.split(",")] if args.shape else [5632, 2048]
+        n, k, m = dims[0], dims[1], (dims[2] if len(dims) > 2 else 1)
+        r = bench_int4(args, 1, device, m, n, k)
+        print(json.dumps({"metric": f"int4_linear M={m} HBM GB/s (% peak)", "unit": "GB/s", "value": r["gbs"], "n_gpus": 1,
+                          "config": {"workload": f"int4_gemv M={m} N={n} K={k} g128"}, "detail": r,
                           "roofline": roofline("hbm", r["gbs"], peaks, kind)}))
     elif args.workload == "int4_gemm":
         m, n, k = (int(v) for v in args.shape.split(",")) if args.shape else (1024, 8960, 1536)
@@ -781,7 +782,7 @@ def main():
     ap.add_argument("--workload", default="flash_attn", choices=["flash_attn", "flash_attn_only", "int4_gemv", "int4_gemm", "decode_attn", "decode_step"],
                     help="flash_attn = headline + every other part of the metric under `also`; the others run one kernel only "
                          "(few launches, for profiler captures)")
-    ap.add_argument("--shape", default=None, help="override: B,H,N,D (flash_attn_only) / N,K (int4_gemv) / M,N,K (int4_gemm) / B,NK (decode_attn) / B (decode_step)")
+    ap.add_argument("--shape", default=None, help="override: B,H,N,D (flash_attn_only) / N,K[,M] (int4_gemv) / M,N,K (int4_gemm) / B,NK (decode_attn) / B (decode_step)")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` groups")

@@ -161,6 +161,12 @@ class LlamaInt4Decoder:
                 "gate_up": _Int4(gate_up_rows, group, self.prepacked),
                 "down": _Int4(f16(down), group, self.prepacked),
             })
+        if prepack and self.plan is not None and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M:
+            # tensor-parallel shards: the decode-sized calls go through int4_linear, which picks the private copy up
+            for L in self.layers:
+                for name in ("qkv", "o", "gate_up", "down"):
+                    if ops.prepack_supported(L[name].packed) and L[name].packed.shape[1] * 8 <= 12288:
+                        ops.prepack_weight_(L[name].packed)
         self.k_cache = torch.zeros(s.layers, batch, self.hk_loc, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) / s.head_dim))
