@@ -26,12 +26,16 @@ using namespace sm100;
 constexpr int kTileKeys = 64;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kStages = 4;
+// Depth of the K/V tile ring.  A grid that fills the SMs (large batches) runs 3 CTAs per SM with 4 stages each; a grid
+// smaller than the GPU (decode at batch 1-8: B * Hk CTAs) is bound by the bytes ONE SM keeps in flight, so there the ring
+// takes (nearly) the whole shared memory and every tile of a short cache is requested at once.
+constexpr int kStagesShallow = 4;
+template <int D> constexpr int deep_stages() { return D == 64 ? 12 : 6; }
 constexpr int kRows = 16;  // query heads per CTA (MMA M)
 
 enum WaitCode : uint32_t { kWaitFull = 0x201, kWaitEmpty };
 
-template <int D>
+template <int D, int kStages>
 struct Layout {
   static constexpr int kHalf = kTileKeys * 128;       // 64 keys x 64 columns
   static constexpr int kTile = kTileKeys * D * 2;     // one K or V tile
@@ -101,13 +105,13 @@ __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 12
 template <int D>
 __host__ __device__ constexpr int partial_floats() { return kRows * (D + 2); }
 
-template <int D, bool kBf16>
+template <int D, bool kBf16, int kStages>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const uint16_t* __restrict__ q, uint16_t* __restrict__ o, float* __restrict__ partial, int H, int Hk,
                    int Nk, int keys_per_split, float scale_log2, unsigned int* status, const int* __restrict__ kv_len,
                    int force_partial) {
-  using L = Layout<D>;
+  using L = Layout<D, kStages>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -399,11 +403,25 @@ SplitPlan plan_splits(int B, int H, int Hk, int Nk, int D) {
   return p;
 }
 
+template <int D, bool kBf16, int kStages>
+int launch_stages(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const CUtensorMap& tv, float* partial,
+                  unsigned int* status, cudaStream_t stream, bool partial_only);
+
 template <int D, bool kBf16>
 int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const CUtensorMap& tv, float* partial,
            unsigned int* status, cudaStream_t stream, bool partial_only = false) {
-  using L = Layout<D>;
-  auto kernel = attn_decode_kernel<D, kBf16>;
+  const dim3 grid_probe(plan.splits, p.Hk * plan.chunks, p.B);
+  const long long ctas = (long long)grid_probe.x * grid_probe.y * grid_probe.z;
+  if (ctas <= sm_count() && ceil_div(plan.keys_per_split, kTileKeys) > kStagesShallow)
+    return launch_stages<D, kBf16, deep_stages<D>()>(p, plan, tk, tv, partial, status, stream, partial_only);
+  return launch_stages<D, kBf16, kStagesShallow>(p, plan, tk, tv, partial, status, stream, partial_only);
+}
+
+template <int D, bool kBf16, int kStages>
+int launch_stages(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const CUtensorMap& tv, float* partial,
+                  unsigned int* status, cudaStream_t stream, bool partial_only) {
+  using L = Layout<D, kStages>;
+  auto kernel = attn_decode_kernel<D, kBf16, kStages>;
   static bool configured[64] = {false};
   int dev = 0;
   KFB_CUDA_TRY(cudaGetDevice(&dev));
