@@ -328,15 +328,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
 }
 
-// Combines the per-split partials of one (batch, query head) in split order.  `sets` > 1: several partial buffers of
-// the same layout, `set_stride` floats apart (one per rank of a cache sharded along the sequence), combined in set
-// order, splits in order inside a set.
+// Combines the per-split partials of one (batch, query head).  `sets` > 1: several partial buffers of the same layout,
+// `set_stride` floats apart (one per rank of a cache sharded along the sequence).  The block is D x kMergeLanes threads:
+// lane j of a column folds partials j, j + kMergeLanes, ... (sets outer, splits inner) into a running (m, acc, l), four
+// independent loads in flight, and the kMergeLanes running triples are merged in lane order through shared memory -- a
+// fixed order, so the result does not depend on timing.  (One thread per column walking 100+ splits in two serial
+// passes was the whole cost of long-context decode at small batch: 31 us at Nk = 16384, batch 1.)
+constexpr int kMergeLanes = 8;
+
 template <int D, bool kBf16>
-__global__ void __launch_bounds__(D)
+__global__ void __launch_bounds__(D * kMergeLanes)
 attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ o, int H, int Hk, int splits, int sets,
                          long long set_stride) {
   constexpr int kPer = kRows * (D + 2);
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  __shared__ float sm_m[kMergeLanes][D], sm_a[kMergeLanes][D], sm_l[kMergeLanes][D];
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x % D, j = threadIdx.x / D;
   pdl_wait();
   pdl_launch_dependents();
   const int G = H / Hk;
@@ -344,19 +350,38 @@ attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict
   const int hk = h / G, within = h % G;
   const int slot = hk * chunks + within / kRows, r = within % kRows;
   const float* base_ptr = partial + ((size_t)b * (Hk * chunks) + slot) * splits * kPer;
-  float m_all = -INFINITY;
-  for (int t = 0; t < sets; ++t)
-    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, base_ptr[(size_t)t * set_stride + (size_t)s * kPer + kRows * D + r]);
-  const float base = (m_all == -INFINITY) ? 0.f : m_all;
-  float acc = 0.f, l_all = 0.f;
-  for (int t = 0; t < sets; ++t)
-    for (int s = 0; s < splits; ++s) {
-      const float* ps = base_ptr + (size_t)t * set_stride + (size_t)s * kPer;
-      const float f = ex2(ps[kRows * D + r] - base);
-      acc = fmaf(f, ps[r * D + d], acc);
-      l_all = fmaf(f, ps[kRows * D + kRows + r], l_all);
+  float m_run = -INFINITY, acc = 0.f, l_run = 0.f;
+  const int total = sets * splits;
+#pragma unroll 4
+  for (int i = j; i < total; i += kMergeLanes) {
+    const int t = i / splits, sp = i - t * splits;
+    const float* ps = base_ptr + (size_t)t * set_stride + (size_t)sp * kPer;
+    const float m_s = ps[kRows * D + r], l_s = ps[kRows * D + kRows + r], o_s = ps[r * D + d];
+    const float m_new = fmaxf(m_run, m_s);
+    if (m_new > -INFINITY) {
+      const float keep = ex2(m_run - m_new), f = ex2(m_s - m_new);   // ex2(-inf) = 0
+      acc = fmaf(f, o_s, acc * keep);
+      l_run = fmaf(f, l_s, l_run * keep);
+      m_run = m_new;
     }
-  o[((size_t)b * H + h) * D + d] = pack1<kBf16>(l_all > 0.f ? acc / l_all : 0.f);  // no valid key: zeros
+  }
+  sm_m[j][d] = m_run; sm_a[j][d] = acc; sm_l[j][d] = l_run;
+  __syncthreads();
+  if (j == 0) {
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kMergeLanes; ++k) m_all = fmaxf(m_all, sm_m[k][d]);
+    float a = 0.f, l = 0.f;
+    if (m_all > -INFINITY) {
+#pragma unroll
+      for (int k = 0; k < kMergeLanes; ++k) {
+        const float f = ex2(sm_m[k][d] - m_all);
+        a = fmaf(f, sm_a[k][d], a);
+        l = fmaf(f, sm_l[k][d], l);
+      }
+    }
+    o[((size_t)b * H + h) * D + d] = pack1<kBf16>(l > 0.f ? a / l : 0.f);  // no valid key: zeros
+  }
 }
 
 struct SplitPlan {
@@ -435,7 +460,7 @@ int launch_stages(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk
                              p.scale * 1.4426950408889634f, status, p.kv_len_dev, partial_only ? 1 : 0))
     return rc;
   if (plan.splits > 1 && !partial_only)
-    return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16>, dim3(p.H, p.B), dim3(D), 0, stream,
+    return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16>, dim3(p.H, p.B), dim3(D * kMergeLanes), 0, stream,
                          pdl_enabled(), (const float*)partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits, 1, 0LL);
   return KFB_OK;
 }
@@ -460,13 +485,13 @@ int launch_merge(const float* partial, void* o, int dtype, int B, int H, int Hk,
   const bool bf16 = dtype == KFB_BF16;
   const dim3 grid(H, B);
   if (D == 64)
-    return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, true>, grid, dim3(64), 0, stream, pdl_enabled(),
+    return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, true>, grid, dim3(64 * kMergeLanes), 0, stream, pdl_enabled(),
                                 partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
-                : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, false>, grid, dim3(64), 0, stream, pdl_enabled(),
+                : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, false>, grid, dim3(64 * kMergeLanes), 0, stream, pdl_enabled(),
                                 partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
-  return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, true>, grid, dim3(128), 0, stream, pdl_enabled(),
+  return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, true>, grid, dim3(128 * kMergeLanes), 0, stream, pdl_enabled(),
                               partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
-              : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, false>, grid, dim3(128), 0, stream, pdl_enabled(),
+              : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, false>, grid, dim3(128 * kMergeLanes), 0, stream, pdl_enabled(),
                               partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
 }
 
