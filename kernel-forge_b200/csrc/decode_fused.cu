@@ -30,10 +30,18 @@ __global__ void __launch_bounds__(kRmsThreads)
 add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ res, const __half* __restrict__ w,
                    __half* __restrict__ y, __half* __restrict__ sum_out, int hidden, float eps) {
   __shared__ float warp_part[kRmsThreads / 32];
+  const int nvec = hidden / 8;
+  // The norm weight is a constant of the model (and cold in HBM: every layer has its own): it is requested before the
+  // wait for the kernel in front, so its round trip overlaps that kernel's tail instead of following the reduction.
+  uint4 wreg[kMaxVec];
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int v = threadIdx.x + i * kRmsThreads;
+    if (v < nvec) wreg[i] = reinterpret_cast<const uint4*>(w)[v];
+  }
   pdl_wait();
   pdl_launch_dependents();
   const size_t base = (size_t)blockIdx.x * hidden;
-  const int nvec = hidden / 8;
   __half2 vals[kMaxVec][4];
   float ss = 0.f;
 #pragma unroll
@@ -68,8 +76,7 @@ add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ res,
   for (int i = 0; i < kMaxVec; ++i) {
     const int v = threadIdx.x + i * kRmsThreads;
     if (v < nvec) {
-      const uint4 wv = reinterpret_cast<const uint4*>(w)[v];
-      const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wreg[i]);
       uint4 o;
       __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll

@@ -96,6 +96,16 @@ int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf
 #pragma unroll
   for (int i = 0; i < NB; ++i)
     if (live && kb0 + i < kb1) wbuf[i] = ldg_stream(wp + (size_t)(kb0 + i) * 32);
+  // ... and so are the scales: the (at most NB) group scales of rows g and g + 8 of this warp's share of K
+  constexpr int kMaxGroups = (NB + kBlocksPerGroup - 1) / kBlocksPerGroup;
+  __half sc0[kMaxGroups], sc1[kMaxGroups];
+  {
+    const __half* srow0 = scales + (size_t)((live ? rb : 0) * 16 + g) * SG;
+    const __half* srow1 = srow0 + (size_t)8 * SG;
+#pragma unroll
+    for (int i = 0; i < kMaxGroups; ++i)
+      if (live && g0 + i < g1) { sc0[i] = srow0[g0 + i]; sc1[i] = srow1[g0 + i]; }
+  }
   pdl_wait();
   pdl_launch_dependents();
 
@@ -103,8 +113,6 @@ int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf
 #pragma unroll
   for (int j = 0; j < MB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   if (live) {
-    const __half* srow0 = scales + (size_t)(rb * 16 + g) * SG;
-    const __half* srow1 = srow0 + (size_t)8 * SG;
     const __half* xrow = x + (size_t)g * K + 16 * t;   // batch row 8 j + g of B fragment j (valid when 8 j + g < M)
     float c[MB][4];
 #pragma unroll
@@ -133,8 +141,8 @@ int4_gemv_frag_kernel(const __half* __restrict__ x, const uint4* __restrict__ wf
           for (int j = 0; j < MB; ++j) mma16816(c[j], a0, a1, a2, a3, xs0[j][s], xs1[j][s]);
         }
         if ((kb + 1) % kBlocksPerGroup == 0) {   // end of a scale group
-          const int grp = kb / kBlocksPerGroup;
-          const float s0 = __half2float(srow0[grp]), s1 = __half2float(srow1[grp]);
+          const int gi = (i + 1) / kBlocksPerGroup - 1;   // group index inside this warp's share (static after unrolling)
+          const float s0 = __half2float(sc0[gi]), s1 = __half2float(sc1[gi]);
 #pragma unroll
           for (int j = 0; j < MB; ++j) {
             acc[j][0] = fmaf(s0, c[j][0], acc[j][0]); acc[j][1] = fmaf(s0, c[j][1], acc[j][1]);

@@ -79,10 +79,11 @@ def prepack_linears_(model: nn.Module) -> int:
 
 @torch.no_grad()
 def quantize_linears_(model: nn.Module, group_size: int = kq.DEFAULT_GROUP_SIZE,
-                      names: tuple[str, ...] = DECODER_LINEARS) -> int:
+                      names: tuple[str, ...] = DECODER_LINEARS, prepack: bool = False) -> int:
     """Replace, in place, every nn.Linear whose attribute name is in `names` by KFLinearInt4.
 
-    Embeddings and lm_head keep their dtype.  Returns the number of layers replaced.
+    Embeddings and lm_head keep their dtype.  Returns the number of layers replaced.  `prepack` (not in the reference):
+    also build the private fragment-order copies (prepack_linears_) when the model already sits on a CUDA device.
     """
     todo = []
     for parent in model.modules():
@@ -92,6 +93,8 @@ def quantize_linears_(model: nn.Module, group_size: int = kq.DEFAULT_GROUP_SIZE,
     for parent, name, child in todo:
         setattr(parent, name, KFLinearInt4.from_linear(child, group_size))
     replaced = len(todo)
+    if prepack:
+        prepack_linears_(model)
     del todo  # drop the last references to the fp16 weights before returning their memory
     if torch.cuda.is_available():
         torch.cuda.empty_cache()
