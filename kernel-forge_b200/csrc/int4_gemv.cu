@@ -130,7 +130,10 @@ __global__ void __launch_bounds__(kThreads)
 int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed, const __half* __restrict__ scales,
                  __half* __restrict__ y, int N, int K, int ksplit_log2, const Fusion fu) {
   __shared__ float red[kWarps][M * R];
-  extern __shared__ uint4 xs_raw[];   // XF != 0: the transformed activations
+  // XF != 0: the transformed activations.  The four 16-byte vectors of a 32-activation chunk are stored KC vectors apart
+  // (vector v = 4 c + j sits at j * KC + c), so that lanes, which walk consecutive chunks c, read consecutive vectors:
+  // in the natural order a warp's 16-byte loads were 64 bytes apart, a four-way bank conflict on every load.
+  extern __shared__ uint4 xs_raw[];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksplit = 1 << ksplit_log2;
@@ -175,7 +178,6 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
   fetch(1, c_first + stride);
   if constexpr (XF == kXformNone) pdl_wait();   // (with a transform the wait opens the prologue below)
   if constexpr (XF != kXformNone) {
-    __half* xs = reinterpret_cast<__half*>(xs_raw);
     pdl_wait();   // x is the previous kernel's output
     const int nvec = K / 8;
     if constexpr (XF == kXformRmsNorm) {
@@ -223,7 +225,7 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
               const float2 f = __half22float2(h[j]);
               oh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
             }
-            reinterpret_cast<uint4*>(xs + (size_t)m * K)[v] = o;
+            xs_raw[(size_t)m * nvec + (v & 3) * KC + (v >> 2)] = o;   // chunk-major: see the main loop
           }
         }
       }
@@ -242,7 +244,7 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
             const float2 gf = __half22float2(gh[j]);
             oh[j] = __hmul2(__floats2half2_rn(gf.x / (1.0f + __expf(-gf.x)), gf.y / (1.0f + __expf(-gf.y))), uh[j]);
           }
-          reinterpret_cast<uint4*>(xs + (size_t)m * K)[v] = o;
+          xs_raw[(size_t)m * nvec + (v & 3) * KC + (v >> 2)] = o;   // chunk-major: see the main loop
         }
     }
     __syncthreads();
@@ -264,7 +266,7 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
       for (int m = 0; m < M; ++m) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if constexpr (XF != kXformNone) xv[m][j] = xs_raw[(size_t)m * (K / 8) + (size_t)c * 4 + j];
+          if constexpr (XF != kXformNone) xv[m][j] = xs_raw[(size_t)m * (K / 8) + (size_t)j * KC + c];
           else xv[m][j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
         }
         const uint32_t* xs = reinterpret_cast<const uint32_t*>(xv[m]);
@@ -307,7 +309,7 @@ int4_gemv_kernel(const __half* __restrict__ x, const uint4* __restrict__ packed,
         uint4 xv[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if constexpr (XF != kXformNone) xv[j] = xs_raw[(size_t)m * (K / 8) + (size_t)c * 4 + j];
+          if constexpr (XF != kXformNone) xv[j] = xs_raw[(size_t)m * (K / 8) + (size_t)j * KC + c];
           else xv[j] = ldg_cached(xc + (size_t)m * (K / 8) + j);
         }
 #pragma unroll

@@ -100,11 +100,11 @@ class LlamaInt4Decoder:
         # predecessor before touching activations); with tensor parallelism only when the gathers are this library's
         # peer-memory kernels too (NCCL kernels in between know nothing of the protocol)
         self.pdl = programmatic_launch and (tp_group is None or peer_gather)
-        # The 6-kernels-per-layer step (_step_fused, batch <= 2) is available but not the default: with programmatic
-        # dependent launch the separate small kernels hide their launch behind their predecessor, while a fused prologue
-        # (norm / SiLU over the whole row, two block barriers) sits on every GEMV's critical path.  Measured, ms per
-        # step at batch 1 / 2 on the TinyLlama-1.1B shape: separate kernels + PDL 0.70 / 0.79, fused + PDL 0.89 / 0.99,
-        # fused without PDL 0.78 / 1.03, separate without PDL 0.79 / 0.84.
+        # The 5-kernels-per-layer step (_step_fused, batch <= 2: RMSNorm in the prologue of the consuming GEMV, residual adds
+        # and pair epilogues in the producing ones) is available but not the default: a fused prologue (norm over the whole
+        # row, two block barriers) sits on every GEMV's critical path and costs what the two launches it removes would have.
+        # Measured, ms per step on the TinyLlama-1.1B shape with programmatic dependent launch: batch 1 0.624 fused against
+        # 0.620 separate, batch 2 0.80 against 0.64 (the separate step runs on the prepacked GEMV there).
         self.fused = False
         s = shape
         self.tp_group = tp_group
