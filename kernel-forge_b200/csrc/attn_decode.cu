@@ -331,12 +331,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 // Combines the per-split partials of one (batch, query head).  `sets` > 1: several partial buffers of the same layout,
 // `set_stride` floats apart (one per rank of a cache sharded along the sequence).  The block is D x kMergeLanes threads:
 // lane j of a column folds partials j, j + kMergeLanes, ... (sets outer, splits inner) into a running (m, acc, l), four
-// independent loads in flight, and the kMergeLanes running triples are merged in lane order through shared memory -- a
+// independent loads in flight, and the kMergeLanes (8, or 1) running triples are merged in lane order through shared memory -- a
 // fixed order, so the result does not depend on timing.  (One thread per column walking 100+ splits in two serial
 // passes was the whole cost of long-context decode at small batch: 31 us at Nk = 16384, batch 1.)
-constexpr int kMergeLanes = 8;
-
-template <int D, bool kBf16>
+// A handful of splits (large batches) is folded by one lane per column: the wide block only costs there.
+template <int D, bool kBf16, int kMergeLanes>
 __global__ void __launch_bounds__(D * kMergeLanes)
 attn_decode_merge_kernel(const float* __restrict__ partial, uint16_t* __restrict__ o, int H, int Hk, int splits, int sets,
                          long long set_stride) {
@@ -433,6 +432,17 @@ int launch_stages(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk
                   unsigned int* status, cudaStream_t stream, bool partial_only);
 
 template <int D, bool kBf16>
+int launch_merge_lanes(const float* partial, uint16_t* o, int B, int H, int Hk, int splits, int sets, long long set_stride,
+                       cudaStream_t stream) {
+  const dim3 grid(H, B);
+  if ((long long)splits * sets >= 8)
+    return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16, 8>, grid, dim3(D * 8), 0, stream, pdl_enabled(),
+                         partial, o, H, Hk, splits, sets, set_stride);
+  return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16, 1>, grid, dim3(D), 0, stream, pdl_enabled(),
+                       partial, o, H, Hk, splits, sets, set_stride);
+}
+
+template <int D, bool kBf16>
 int launch(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk, const CUtensorMap& tv, float* partial,
            unsigned int* status, cudaStream_t stream, bool partial_only = false) {
   const dim3 grid_probe(plan.splits, p.Hk * plan.chunks, p.B);
@@ -460,8 +470,7 @@ int launch_stages(const Problem& p, const SplitPlan& plan, const CUtensorMap& tk
                              p.scale * 1.4426950408889634f, status, p.kv_len_dev, partial_only ? 1 : 0))
     return rc;
   if (plan.splits > 1 && !partial_only)
-    return launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<D, kBf16>, dim3(p.H, p.B), dim3(D * kMergeLanes), 0, stream,
-                         pdl_enabled(), (const float*)partial, (uint16_t*)p.o, p.H, p.Hk, plan.splits, 1, 0LL);
+    return launch_merge_lanes<D, kBf16>((const float*)partial, (uint16_t*)p.o, p.B, p.H, p.Hk, plan.splits, 1, 0LL, stream);
   return KFB_OK;
 }
 
@@ -483,16 +492,11 @@ int launch_merge(const float* partial, void* o, int dtype, int B, int H, int Hk,
                  cudaStream_t stream) {
   if (H > 65535 || B > 65535) return fail(KFB_ERR_INVALID, "B and H must each be <= 65535");
   const bool bf16 = dtype == KFB_BF16;
-  const dim3 grid(H, B);
   if (D == 64)
-    return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, true>, grid, dim3(64 * kMergeLanes), 0, stream, pdl_enabled(),
-                                partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
-                : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<64, false>, grid, dim3(64 * kMergeLanes), 0, stream, pdl_enabled(),
-                                partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
-  return bf16 ? launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, true>, grid, dim3(128 * kMergeLanes), 0, stream, pdl_enabled(),
-                              partial, (uint16_t*)o, H, Hk, splits, sets, set_stride)
-              : launch_kernel("attn_decode_merge_kernel", attn_decode_merge_kernel<128, false>, grid, dim3(128 * kMergeLanes), 0, stream, pdl_enabled(),
-                              partial, (uint16_t*)o, H, Hk, splits, sets, set_stride);
+    return bf16 ? launch_merge_lanes<64, true>(partial, (uint16_t*)o, B, H, Hk, splits, sets, set_stride, stream)
+                : launch_merge_lanes<64, false>(partial, (uint16_t*)o, B, H, Hk, splits, sets, set_stride, stream);
+  return bf16 ? launch_merge_lanes<128, true>(partial, (uint16_t*)o, B, H, Hk, splits, sets, set_stride, stream)
+              : launch_merge_lanes<128, false>(partial, (uint16_t*)o, B, H, Hk, splits, sets, set_stride, stream);
 }
 
 int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t stream, bool partial_only) {
