@@ -378,7 +378,29 @@ def bench_flash_attn(args, world, device, causal: bool, cfg=HEADLINE, sampler=No
            "n_sets": n_sets, "timing": r}
     if e2e:
         out["e2e"] = bench_flash_attn_e2e(args, world, device, causal, cfg, sets[0], flops)
+        out["parity"] = attn_parity_sample(sets[0], causal)
     return out
+
+
+def attn_parity_sample(first_set, causal: bool, heads=2) -> dict:
+    """The result of the timed kernel on the first input set against an FP32 torch formulation of the same attention on
+    the GPU (softmax(q k^T / sqrt(D)) v on `heads` heads of batch item 0): maximum absolute error, the fp16 rounding floor
+    of the same reference tensor, and the reference's own bound (tests/test_attention.py:17: 2e-3 for fp16)."""
+    from kernelforge import ops
+    q, k, v = first_set
+    o = ops.flash_attn(q, k, v, causal=causal)
+    g = q.shape[1] // k.shape[1]
+    qs, ks, vs = q[:1, :heads].float(), k[:1, :max(1, heads // g)].float(), v[:1, :max(1, heads // g)].float()
+    ks, vs = ks.repeat_interleave(g, dim=1)[:, :heads], vs.repeat_interleave(g, dim=1)[:, :heads]
+    sc = qs @ ks.transpose(-1, -2) / math.sqrt(q.shape[-1])
+    if causal:
+        nq, nk = sc.shape[-2:]
+        sc = sc.masked_fill(torch.ones(nq, nk, dtype=torch.bool, device=sc.device).triu(1 + nk - nq), float("-inf"))
+    ref = torch.softmax(sc, dim=-1) @ vs
+    err = (o[:1, :heads].float() - ref).abs().max().item()
+    floor = (ref.half().float() - ref).abs().max().item()
+    return {"max_abs_err": err, "fp16_rounding_floor": floor, "bound": 2e-3, "heads_checked": heads,
+            "reference": "FP32 torch attention on the GPU, same inputs"}
 
 
 def bench_flash_attn_e2e(args, world, device, causal, cfg, first_set, flops) -> dict:
@@ -840,7 +862,7 @@ def main():
     line = dict(base)
     line.update({
         "value": fa["tflops"], "ms_per_step": fa["ms_per_step"], "blocks": t["blocks"], "block_ms": t["block_ms"],
-        "per_rank_ms": t["per_rank_ms"], "e2e": fa["e2e"], "gpu_launches": args.steps,
+        "per_rank_ms": t["per_rank_ms"], "e2e": fa["e2e"], "parity": fa["parity"], "gpu_launches": args.steps,
         "clocks": clocks.summary(),
         "roofline": roofline("tensor", fa["tflops"] / world, peaks, kind,
                              # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload from an ncu capture
