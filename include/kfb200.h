@@ -171,6 +171,13 @@ int kfb_int4_gemv_rope_kv(const void* x, const void* packed, const void* scales,
  *   workspace: kfb_decode_step_ws_bytes bytes, 16-byte aligned, contents irrelevant; calls that share it must not overlap.
  * Every in-kernel wait is bounded: an expired wait records 0x901 (grid barrier) or 0x902 (weight ring) in the device
  * status word and the kernel returns; a position outside [0, max_len) records 0x701 and nothing is written. */
+/* Self-test of the decode step's bounded grid barrier: 4 CTAs run one barrier that expects 5 arrivals; every wait runs
+ * out after timeout_ns (1 us .. 100 ms), outcome_dev[cta] (4 uint32) becomes 2 (1 would mean the barrier completed), the
+ * status word gets 0x901 and the kernel returns normally.  scratch: 1 KiB of device memory.  Follow it with
+ * kfb_device_status_reset. */
+int kfb_selftest_grid_barrier_expiry(unsigned long long timeout_ns, unsigned int* outcome_dev, void* scratch,
+                                     size_t scratch_bytes, void* stream);
+
 typedef struct kfb_decode_step_t {
   const void* layer_table;
   int layers, batch, hidden, heads, kv_heads, head_dim, intermediate, vocab, max_len, group;

@@ -901,6 +901,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   }
 }
 
+// Self-test of the bounded grid barrier: `launched` CTAs run one barrier that expects `launched + 1` arrivals, so it
+// can never complete; every CTA's wait runs out after timeout_ns, records 0x901, and the kernel returns through the same
+// give-up path as the decode step (poisoned flags).  outcome[cta] = 1 barrier passed (never), 2 gave up.
+__global__ void __launch_bounds__(kThreads, 1)
+grid_barrier_selftest_kernel(const __grid_constant__ Params p, unsigned int* __restrict__ outcome) {
+  __shared__ Shared sh_store;
+  Shared* sh = &sh_store;
+  Ctx c{p, nullptr, nullptr, sh, AbortCtx{&sh->abort_word, p.status, p.timeout_ns},
+        (int)blockIdx.x, (int)gridDim.x + 1, (int)(threadIdx.x >> 5), (int)(threadIdx.x & 31), (int)threadIdx.x, 0u, 0ull};
+  if (threadIdx.x == 0) { sh->abort_word = 0; sh->go = 0; }
+  __syncthreads();
+  if (c.warp < kConsumerWarps) {
+    const bool passed = grid_barrier(c);
+    if (c.tid == 0) outcome[blockIdx.x] = passed ? 1u : 2u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && sh->abort_word != 0)
+    for (int i = 0; i < (int)gridDim.x; ++i) st_release_gpu(p.flags + (size_t)i * kFlagStride, kPoison);
+}
+
 }  // namespace persist
 }  // namespace kfb
 
@@ -978,6 +998,29 @@ extern "C" void kfb_debug_set_step_trace(void* device_buffer, int cta) {
   cudaMemcpyToSymbol(kfb::persist::g_step_trace_cta, &cta, sizeof(int));
 }
 #endif
+
+extern "C" int kfb_selftest_grid_barrier_expiry(unsigned long long timeout_ns, unsigned int* outcome_dev, void* scratch,
+                                                size_t scratch_bytes, void* stream) {
+  if (int rc = require_sm100()) return rc;
+  if (!outcome_dev || !scratch) return fail(KFB_ERR_INVALID, "null pointer");
+  if (timeout_ns < 1000ull || timeout_ns > 100000000ull)
+    return fail(KFB_ERR_INVALID, "the self-test takes a limit between 1 us and 100 ms, got %llu ns", timeout_ns);
+  constexpr int kCtas = 4;
+  const size_t need = 256 + (size_t)kCtas * persist::kFlagStride * 8;
+  if (scratch_bytes < need || !aligned16(scratch)) return fail(KFB_ERR_WORKSPACE, "the self-test needs %zu bytes of 16-byte aligned scratch", need);
+  unsigned int* status = device_status_word();
+  if (!status) return fail(KFB_ERR_CUDA, "cannot resolve the device status word");
+  cudaStream_t st = (cudaStream_t)stream;
+  KFB_CUDA_TRY(cudaMemsetAsync(scratch, 0, need, st));
+  persist::Params p = {};
+  p.bar = static_cast<unsigned long long*>(scratch);
+  p.flags = reinterpret_cast<unsigned long long*>(static_cast<char*>(scratch) + 256);
+  p.status = status;
+  p.timeout_ns = timeout_ns;
+  persist::grid_barrier_selftest_kernel<<<kCtas, persist::kThreads, 0, st>>>(p, outcome_dev);
+  KFB_LAUNCH_CHECK("grid_barrier_selftest_kernel");
+  return KFB_OK;
+}
 
 extern "C" size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate) {
   if (batch < 1 || hidden < 1 || heads < 1 || kv_heads < 1 || head_dim < 1 || intermediate < 1 || heads % kv_heads) return 0;

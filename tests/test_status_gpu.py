@@ -77,3 +77,24 @@ def test_peer_wait_gives_up_when_an_arrival_never_comes():
         _capi.device_status_reset(dev)
         torch.cuda.synchronize()
     assert _capi.device_status(dev) == 0
+
+
+def test_grid_barrier_of_the_persistent_step_gives_up():
+    """The grid-wide barrier of the persistent decode step, through the library's self-test: 4 CTAs run one barrier that
+    expects 5 arrivals, every wait runs out after its limit (2 ms), each CTA reports that it gave up, the status word
+    holds 0x901, and after a reset the persistent step itself runs normally."""
+    dev = torch.device("cuda", 0)
+    lib = _capi.lib()
+    assert _capi.device_status(dev) == 0
+    outcome = torch.zeros(4, dtype=torch.int32, device=dev)
+    scratch = torch.empty(1024, dtype=torch.uint8, device=dev)
+    try:
+        with _capi.on_device(dev):
+            _capi.check(lib.kfb_selftest_grid_barrier_expiry(2_000_000, outcome.data_ptr(), scratch.data_ptr(), 1024, _capi.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        assert outcome.tolist() == [2, 2, 2, 2], "every CTA must give the barrier up, none may pass it"
+        assert _capi.device_status(dev) == 0x901
+    finally:
+        _capi.device_status_reset(dev)
+        torch.cuda.synchronize()
+    assert _capi.device_status(dev) == 0
