@@ -130,11 +130,14 @@ class LlamaInt4Decoder:
         # (ops.prepack_int4; as much memory again as the packed weights), with the same pair epilogues.  Measured,
         # ms per step on the TinyLlama-1.1B shape, dispatcher kernels -> prepacked: batch 1 0.675 -> 0.681 (a tie: the
         # CUDA-core GEMV stays, and the memory is saved), batch 2 0.80 -> 0.70, batch 8 1.01 -> 0.75.
+        # With tensor parallelism the same holds for the rank's own rows (local heads, local share of the hidden and
+        # intermediate features); only the four gathers per layer are added.
+        hidden_loc = s.hidden if self.plan is None else self.plan["hidden_rows"][1] - self.plan["hidden_rows"][0]
         kdims = (s.hidden, s.heads * s.head_dim, s.intermediate)
-        ndims = ((s.heads + 2 * s.kv_heads) * s.head_dim, s.hidden, 2 * s.intermediate)
-        self.prepacked = (prepack and self.plan is None and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M
+        ndims = ((self.h_loc + 2 * self.hk_loc) * s.head_dim, hidden_loc, 2 * self.inter_loc)
+        self.prepacked = (prepack and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M
                           and all(k % 64 == 0 and k % group == 0 and k <= 12288 for k in kdims) and all(n % 16 == 0 for n in ndims))
-        self.pair_rows = self.plan is None and (batch <= ops.FUSED_GEMV_MAX_M or self.prepacked)
+        self.pair_rows = batch <= ops.FUSED_GEMV_MAX_M or self.prepacked
         f16 = lambda t: t.to(self.dev, torch.float16).contiguous()
         self.embed = f16(weights["embed"])
         self.lm_head = f16(weights["lm_head"])
@@ -161,12 +164,6 @@ class LlamaInt4Decoder:
                 "gate_up": _Int4(gate_up_rows, group, self.prepacked),
                 "down": _Int4(f16(down), group, self.prepacked),
             })
-        if prepack and self.plan is not None and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M:
-            # tensor-parallel shards: the decode-sized calls go through int4_linear, which picks the private copy up
-            for L in self.layers:
-                for name in ("qkv", "o", "gate_up", "down"):
-                    if ops.prepack_supported(L[name].packed) and L[name].packed.shape[1] * 8 <= 12288:
-                        ops.prepack_weight_(L[name].packed)
         self.k_cache = torch.zeros(s.layers, batch, self.hk_loc, max_len, s.head_dim, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) / s.head_dim))
@@ -184,7 +181,7 @@ class LlamaInt4Decoder:
         # measured on the TinyLlama-1.1B shape it takes 0.98 ms per step at batch 1 against 0.68 ms for the step of
         # separate kernels chained by programmatic dependent launch -- five grid-wide barriers per layer at ~2 us each
         # plus the L2 round trip that re-reads the activations after each of them cost more than the launches they replace.
-        self.persistent_ok = self.pair_rows and batch <= 2 and s.head_dim == 64
+        self.persistent_ok = self.pair_rows and self.plan is None and batch <= 2 and s.head_dim == 64
         self.persistent = False
         self._step_desc = self._persistent_descriptor() if self.persistent_ok else None
         self.graph = None
@@ -385,20 +382,18 @@ class LlamaInt4Decoder:
                 q = ops.rope_kv_write(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self.h_loc)
             a = ops.flash_attn_decode(q, self.k_cache[li], self.v_cache[li], self.kv_len)
             a = self._gather(a.view(b, self.h_loc * s.head_dim), "attn_bounds")
-            if self.prepacked:
-                o = ops.int4_gemv_prepacked(a, L["o"].pre, L["o"].scales, L["o"].group)
-            else:
-                o = self._gather(L["o"](a), "hidden_bounds")
+            o = ops.int4_gemv_prepacked(a, L["o"].pre, L["o"].scales, L["o"].group) if self.prepacked else L["o"](a)
+            o = self._gather(o, "hidden_bounds")
             h, x = ops.add_rmsnorm(x, L["post_norm"], s.rms_eps, o)
             if self.prepacked:
                 act = ops.int4_gemv_prepacked_silu_pair(h, L["gate_up"].pre, L["gate_up"].scales, L["gate_up"].group)
-                res = ops.int4_gemv_prepacked(act, L["down"].pre, L["down"].scales, L["down"].group)
-                continue
-            if self.pair_rows:
+            elif self.pair_rows:
                 act = ops.int4_gemv_silu_pair(h, L["gate_up"].packed, L["gate_up"].scales, L["gate_up"].group)
             else:
-                act = self._gather(ops.silu_mul(L["gate_up"](h)), "inter_bounds")
-            res = self._gather(L["down"](act), "hidden_bounds")
+                act = ops.silu_mul(L["gate_up"](h))
+            act = self._gather(act, "inter_bounds")
+            res = ops.int4_gemv_prepacked(act, L["down"].pre, L["down"].scales, L["down"].group) if self.prepacked else L["down"](act)
+            res = self._gather(res, "hidden_bounds")
         h, x = ops.add_rmsnorm(x, self.final_norm, s.rms_eps, res)
         ops.lm_head_argmax(h, self.lm_head, self.step_logits, self.best)
         ops.decode_finalize(self.best, self.tok, self.pos, self.kv_len)
