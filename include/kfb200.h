@@ -196,6 +196,12 @@ typedef struct kfb_decode_step_t {
   size_t workspace_bytes;
 } kfb_decode_step_t;
 size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate);
+/* The static schedule of the persistent step, for inspection (host only, no device needed): the rows of an [n_rows, K]
+ * matrix that CTA `cta` of `n_ctas` owns, and how many of them go through one shared-memory ring slot at a time.
+ * group > 0: an INT4 matrix with that group size (rows dealt out in the smallest even unit whose scale rows are a multiple
+ * of 16 bytes, or in `unit_rows` when > 0); group == 0: an fp16 matrix (the lm_head), unit 1. */
+int kfb_decode_step_slice(int n_rows, int K, int group, int unit_rows, int cta, int n_ctas, int* first_row, int* rows,
+                          int* rows_per_chunk);
 int kfb_decode_step_persistent(const kfb_decode_step_t* step, void* stream);
 
 /* A PRIVATE, PREPACKED copy of a weight in MMA-fragment order, and the M <= 32 GEMV that runs on it -- the reference's

@@ -1022,6 +1022,18 @@ extern "C" int kfb_selftest_grid_barrier_expiry(unsigned long long timeout_ns, u
   return KFB_OK;
 }
 
+extern "C" int kfb_decode_step_slice(int n_rows, int K, int group, int unit_rows, int cta, int n_ctas, int* first_row, int* rows,
+                                     int* rows_per_chunk) {
+  if (n_rows < 1 || K < 32 || n_ctas < 1 || cta < 0 || cta >= n_ctas || !first_row || !rows || !rows_per_chunk)
+    return fail(KFB_ERR_INVALID, "bad argument");
+  const int row_bytes = group > 0 ? K / 2 + K / group * 2 : K * 2;   // INT4 row + its scales, or an fp16 row
+  const int unit = unit_rows > 0 ? unit_rows : (group > 0 ? persist::int4_unit(K, group) : 1);
+  if (n_rows % unit) return fail(KFB_ERR_UNSUPPORTED, "a matrix of %d rows cannot be dealt out in units of %d rows", n_rows, unit);
+  const persist::Slice sl = persist::slice_of(n_rows, unit, row_bytes, cta, n_ctas);
+  *first_row = sl.r0; *rows = sl.rows; *rows_per_chunk = sl.rows_per_chunk;
+  return KFB_OK;
+}
+
 extern "C" size_t kfb_decode_step_ws_bytes(int batch, int hidden, int heads, int kv_heads, int head_dim, int intermediate) {
   if (batch < 1 || hidden < 1 || heads < 1 || kv_heads < 1 || head_dim < 1 || intermediate < 1 || heads % kv_heads) return 0;
   return ws_layout(batch, hidden, heads, kv_heads, head_dim, intermediate, persist::kMaxSplits).total;

@@ -80,6 +80,8 @@ _SIGNATURES = {
     "kfb_decode_finalize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "kfb_embed_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "kfb_selftest_grid_barrier_expiry": (c_int, [ctypes.c_ulonglong, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "kfb_decode_step_slice": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                                      ctypes.POINTER(c_int)]),
     "kfb_decode_step_ws_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "kfb_decode_step_persistent": (c_int, [ctypes.POINTER(DecodeStep), c_void_p]),
     "kfb_flash_attn_decode_kvlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,

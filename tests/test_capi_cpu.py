@@ -131,3 +131,28 @@ def test_decoder_refuses_steps_that_do_not_fit_the_cache():
     dec._host_pos = 8
     with pytest.raises(ValueError, match="full"):
         dec.capture()
+
+
+@pytest.mark.parametrize("n_rows,k,group", [(2560, 2048, 128), (2048, 2048, 128), (11264, 2048, 128), (2048, 5632, 128),
+                                            (32000, 2048, 0), (512, 256, 128), (1024, 256, 64), (320, 256, 0)])
+@pytest.mark.parametrize("n_ctas", [148, 132, 7])
+def test_persistent_step_schedule_covers_every_row_once(n_rows, k, group, n_ctas):
+    """kfb_decode_step_slice (host only): the row slices of the CTAs tile the matrix without gap or overlap, start on the
+    16-byte boundaries the bulk copies need (weights and scales), and a ring slot's worth of rows fits its 44 KB."""
+    import ctypes
+    from kernelforge import _capi
+    lib = _capi.lib()
+    r0, rows, rpc = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    nxt = 0
+    row_w = k // 2 if group else k * 2
+    row_s = (k // group) * 2 if group else 0
+    for cta in range(n_ctas):
+        _capi.check(lib.kfb_decode_step_slice(n_rows, k, group, 0, cta, n_ctas, ctypes.byref(r0), ctypes.byref(rows), ctypes.byref(rpc)))
+        assert r0.value == nxt and rows.value >= 0
+        nxt += rows.value
+        assert (r0.value * row_w) % 16 == 0 and (r0.value * row_s) % 16 == 0
+        assert rpc.value >= 1 and rpc.value * (row_w + row_s) <= 45056
+        if group:
+            assert rows.value % 2 == 0 and rpc.value % 2 == 0      # pairs of rows stay together
+            assert (rpc.value * row_s) % 16 == 0
+    assert nxt == n_rows
