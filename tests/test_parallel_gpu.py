@@ -123,6 +123,7 @@ def _tp_decode_worker(rank, world, port):
         ids = torch.randint(0, 320, (batch, prompt_len), generator=torch.Generator().manual_seed(3))
         tp = LlamaInt4Decoder.from_hf(base, dev, batch, max_len=64, tp_group=dist.group.WORLD)
         assert tp.h_loc == 2 and tp.hk_loc == 1 and tp.inter_loc == 256
+        assert tp.pair_rows and tp.prepacked       # the rank's rows in pair order, on the fragment-order GEMV
         pre = tp.prefill(ids).float().cpu()
         toks, logs = tp.decode(steps, keep_logits=True)      # CUDA graph with the four all-gathers per layer captured
         torch.cuda.synchronize()
