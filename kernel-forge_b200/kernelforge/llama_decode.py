@@ -135,7 +135,9 @@ class LlamaInt4Decoder:
         hidden_loc = s.hidden if self.plan is None else self.plan["hidden_rows"][1] - self.plan["hidden_rows"][0]
         kdims = (s.hidden, s.heads * s.head_dim, s.intermediate)
         ndims = ((self.h_loc + 2 * self.hk_loc) * s.head_dim, hidden_loc, 2 * self.inter_loc)
-        self.prepacked = (prepack and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M
+        groups = s.hidden // group     # (the pair epilogues above 8 batch rows exist for K split 8 ways, <= 12 blocks of 64 per warp)
+        wide_ok = batch <= 8 or (groups >= 8 and -(-groups // 8) * (group // 64) <= 12)
+        self.prepacked = (prepack and 2 <= batch <= ops.PREPACKED_GEMV_MAX_M and wide_ok
                           and all(k % 64 == 0 and k % group == 0 and k <= 12288 for k in kdims) and all(n % 16 == 0 for n in ndims))
         self.pair_rows = batch <= ops.FUSED_GEMV_MAX_M or self.prepacked
         f16 = lambda t: t.to(self.dev, torch.float16).contiguous()
