@@ -141,13 +141,15 @@ _PREPACKED: dict[int, tuple[int, torch.Tensor]] = {}
 
 
 def prepack_supported(packed: torch.Tensor) -> bool:
-    return packed.dim() == 2 and packed.shape[0] % 16 == 0 and (packed.shape[1] * 8) % 64 == 0 and packed.shape[0] >= 16
+    """Shapes the fragment-order GEMV runs: N % 16 == 0, K % 64 == 0, K <= 12288 (a warp holds its share of K in registers)."""
+    k = packed.shape[1] * 8 if packed.dim() == 2 else 0
+    return packed.dim() == 2 and packed.shape[0] % 16 == 0 and packed.shape[0] >= 16 and k % 64 == 0 and 64 <= k <= 12288
 
 
 def prepack_int4(packed: torch.Tensor) -> torch.Tensor:
     """The fragment-order copy of a packed weight (kfb_int4_prepack): uint8 [N * K / 2], same size as `packed`."""
     if packed.dtype != torch.int32 or not packed.is_cuda or not packed.is_contiguous() or not prepack_supported(packed):
-        raise ValueError("prepack_int4 takes a contiguous int32 CUDA tensor [N, K/8] with N % 16 == 0 and K % 64 == 0")
+        raise ValueError("prepack_int4 takes a contiguous int32 CUDA tensor [N, K/8] with N % 16 == 0, K % 64 == 0 and K <= 12288")
     n, k = packed.shape[0], packed.shape[1] * 8
     out = torch.empty(n * k // 2, dtype=torch.uint8, device=packed.device)
     with _capi.on_device(packed.device):
