@@ -156,3 +156,20 @@ def test_persistent_step_schedule_covers_every_row_once(n_rows, k, group, n_ctas
             assert rows.value % 2 == 0 and rpc.value % 2 == 0      # pairs of rows stay together
             assert (rpc.value * row_s) % 16 == 0
     assert nxt == n_rows
+
+
+def test_prepack_shape_rules_and_routing_rule():
+    """Host-side rules of the private prepacked weight cache: which shapes get a fragment-order copy, and where the
+    measured M = 1 exception applies (small N with long K stays on the public-format kernel)."""
+    import torch
+    from kernelforge import ops
+    ok = lambda n, k: ops.prepack_supported(torch.empty(n, k // 8, dtype=torch.int32))
+    assert ok(5632, 2048) and ok(16, 64) and ok(1536, 8960) and ok(32000, 2048)
+    assert not ok(5630, 2048)        # N % 16
+    assert not ok(64, 96)            # K % 64
+    assert not ok(64, 12288 + 64)    # a warp's share of K must fit its registers
+    assert not ops.prepack_supported(torch.empty(8, dtype=torch.int32))
+    assert ops._prepacked_wins(2, 1536, 8960) and ops._prepacked_wins(32, 256, 1536)
+    assert ops._prepacked_wins(1, 5632, 2048) and not ops._prepacked_wins(1, 1536, 8960)
+    with pytest.raises(ValueError):
+        ops.prepack_int4(torch.empty(64, 8, dtype=torch.int32))   # not on a CUDA device: no CPU fallback
