@@ -173,3 +173,27 @@ def test_prepack_shape_rules_and_routing_rule():
     assert ops._prepacked_wins(1, 5632, 2048) and not ops._prepacked_wins(1, 1536, 8960)
     with pytest.raises(ValueError):
         ops.prepack_int4(torch.empty(64, 8, dtype=torch.int32))   # not on a CUDA device: no CPU fallback
+
+
+def test_private_row_orders_are_permutations_prefill_can_undo():
+    """ops.interleave_qkv_for_rope / interleave_gate_up only permute rows: the projection of the permuted matrix, read back
+    the way LlamaInt4Decoder.prefill and _mlp read it, equals the projection of the natural matrix (pure torch, on CPU)."""
+    import torch
+    from kernelforge import ops
+    g = torch.Generator().manual_seed(0)
+    h, hk, d, k, inter, b, t = 4, 2, 64, 96, 40, 2, 3
+    wq, wk, wv = (torch.randn(n, k, generator=g, dtype=torch.float64) for n in (h * d, hk * d, hk * d))
+    x = torch.randn(b, t, k, generator=g, dtype=torch.float64)
+    nat = x @ torch.cat([wq, wk, wv], 0).T
+    qkv = x @ ops.interleave_qkv_for_rope(wq, wk, wv, d).T
+    nq, nkv = h * d, hk * d
+    unpair = lambda z, heads: z.reshape(b, t, heads, d // 2, 2).transpose(-1, -2).reshape(b, t, heads * d)
+    back = torch.cat([unpair(qkv[..., :nq], h), unpair(qkv[..., nq:nq + nkv], hk), qkv[..., nq + nkv:]], -1)
+    assert torch.equal(back, nat)
+    # the pair (2j, 2j + 1) of a q / k head holds features (j, j + D/2): what the rotate-half embedding mixes
+    perm = ops.interleave_qkv_for_rope(torch.arange(h * d, dtype=torch.float64)[:, None], torch.zeros(hk * d, 1, dtype=torch.float64),
+                                       torch.zeros(hk * d, 1, dtype=torch.float64), d)[:h * d, 0].reshape(h, d // 2, 2)
+    assert torch.equal(perm[..., 1] - perm[..., 0], torch.full((h, d // 2), float(d // 2), dtype=torch.float64))
+    gate, up = (torch.randn(inter, k, generator=g, dtype=torch.float64) for _ in range(2))
+    gu = (x @ ops.interleave_gate_up(gate, up).T).view(b, t, inter, 2)
+    assert torch.equal(gu[..., 0], x @ gate.T) and torch.equal(gu[..., 1], x @ up.T)
